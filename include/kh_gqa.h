@@ -1,0 +1,493 @@
+/*
+ * kh_gqa.h -- C ABI of libkhcuda_gqa: paged GQA split-KV scaled-dot-product attention for
+ * NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a Rust `inference-backend-cuda` crate (or any other host) binds. It
+ * replaces, for the attention path only, what the reference reaches through its Metal backend:
+ * device / buffer / stream objects, the SDPA capability registry, the SDPA selector and its
+ * batch metadata, the request page table, and the SlicedKv / SlicedQ `Compute` objects with
+ * their map / reduce / direct invocations. Every entry point cites the reference interface it
+ * stands in for; paths are relative to the reference project root, with
+ *   BM = crates/inference-backend-metal/src,  EM = crates/inference-executor-metal/src,
+ *   EC = crates/inference-executor-core/src.
+ *
+ * Conventions
+ *  - Every function returns a kh_status. On failure a thread-local message is available from
+ *    kh_last_error(). Nothing unwinds across this boundary: each `assert!` of the reference's
+ *    `validate()` functions is a checked KH_INVALID_ARGUMENT here.
+ *  - Device buffers are passed as (pointer, byte length) pairs (kh_buffer_ref). The library
+ *    never allocates inside a map / reduce / direct call and never synchronises the stream, so
+ *    the calls can be captured into a CUDA graph (the analogue of the reference's recorded
+ *    replay program).
+ *  - Handles are not thread-safe; one owner thread per handle, as in the reference executor.
+ *  - All metadata arrays are little-endian u32 and bit-identical to the reference's
+ *    GQAMetadataBuffers (EM/attn/gqa/batch_metadata.rs:100-253).
+ */
+#ifndef KH_GQA_H_
+#define KH_GQA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define KH_API
+#else
+#define KH_API __attribute__((visibility("default")))
+#endif
+
+/* ---- status codes: variant names of crates/inference-error/src/lib.rs:4-28 ---------------- */
+typedef int32_t kh_status;
+enum {
+    KH_OK = 0,
+    KH_INVALID_ARGUMENT = 1,
+    KH_RESOURCE_EXHAUSTED = 2,
+    KH_CANCELLED = 3,
+    KH_DEADLINE_EXCEEDED = 4,
+    KH_ABORTED = 5,
+    KH_EVICTED = 6,
+    KH_UNAVAILABLE = 7,
+    KH_INTERNAL = 8
+};
+
+/* Copies the calling thread's last error message (NUL terminated) into buf; returns its length. */
+KH_API size_t kh_last_error(char* buf, size_t len);
+/* Library version string; also proves the library and its CUDA objects loaded. */
+KH_API const char* kh_version(void);
+
+/* ---- element types: the subset of BM/metal/dtype.rs:1-16 this path uses -------------------- */
+typedef uint32_t kh_dtype;
+enum {
+    KH_DTYPE_FLOAT16 = 9,   /* Dtype::Float16 (ordinal in the reference enum) */
+    KH_DTYPE_FLOAT32 = 10,  /* Dtype::Float32 */
+    KH_DTYPE_BFLOAT16 = 12, /* Dtype::Bfloat16 */
+    KH_DTYPE_FP8_E4M3FN = 100 /* KV-cache only; the reference's native cache format (BM/components/gqa/fp8.rs) */
+};
+
+/* ---- device, buffers, streams (stand in for BM/metal/{device,buffer,stream}) --------------- */
+typedef struct kh_device kh_device;
+typedef struct kh_stream kh_stream;
+
+typedef struct kh_buffer_ref {
+    void* ptr;      /* device pointer */
+    uint64_t bytes; /* usable byte length starting at ptr */
+} kh_buffer_ref;
+
+/* Device::system_default (BM/metal/device.rs:12-15): opens CUDA device `ordinal`. */
+KH_API kh_status kh_device_open(int32_t ordinal, kh_device** out);
+KH_API kh_status kh_device_close(kh_device* device);
+KH_API kh_status kh_device_sm_count(const kh_device* device, int32_t* out);
+/* Buffer::new_zeroed (BM/metal/buffer.rs): device allocation, zero filled. */
+KH_API kh_status kh_buffer_alloc(kh_device* device, uint64_t bytes, kh_buffer_ref* out);
+KH_API kh_status kh_buffer_free(kh_device* device, kh_buffer_ref buffer);
+/* Buffer::write_typed / read_typed / zero_bytes: synchronous host <-> device copies. */
+KH_API kh_status kh_buffer_write(kh_device* device, kh_buffer_ref buffer, uint64_t offset, const void* src,
+                                 uint64_t bytes);
+KH_API kh_status kh_buffer_read(kh_device* device, kh_buffer_ref buffer, uint64_t offset, void* dst, uint64_t bytes);
+KH_API kh_status kh_buffer_zero(kh_device* device, kh_buffer_ref buffer, uint64_t offset, uint64_t bytes);
+/* Stream::new (BM/metal/stream/mod.rs); kh_stream_wrap adopts an existing cudaStream_t. */
+KH_API kh_status kh_stream_create(kh_device* device, kh_stream** out);
+KH_API kh_status kh_stream_wrap(kh_device* device, void* cuda_stream, kh_stream** out);
+KH_API kh_status kh_stream_destroy(kh_stream* stream);
+/* ReplaySubmission::wait (BM/metal/stream/submission.rs:88). */
+KH_API kh_status kh_stream_synchronize(kh_stream* stream);
+/* Stream-ordered host <-> device copies (pinned host memory recommended). */
+KH_API kh_status kh_stream_write(kh_stream* stream, kh_buffer_ref buffer, uint64_t offset, const void* src,
+                                 uint64_t bytes);
+KH_API kh_status kh_stream_read(kh_stream* stream, kh_buffer_ref buffer, uint64_t offset, void* dst, uint64_t bytes);
+KH_API kh_status kh_host_alloc_pinned(uint64_t bytes, void** out);
+KH_API kh_status kh_host_free_pinned(void* ptr);
+
+/* ---- SDPA capability registry: BM/components/gqa/sdpa.rs ----------------------------------- */
+/* sdpa::Config (sdpa.rs:219-241). */
+typedef struct kh_sdpa_config {
+    kh_dtype io_dtype;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t tokens_per_page;
+} kh_sdpa_config;
+
+/* MapKernelKind (sdpa.rs:22-28). */
+typedef uint32_t kh_map_kernel_kind;
+enum { KH_MAP_SLICED_KV = 0, KH_MAP_Q_TOKENS_PER_HEAD = 1, KH_MAP_Q_HEADS_PER_TOKEN = 2, KH_MAP_Q_TOKENS_AND_HEADS = 3 };
+
+/* ExecutionVariant flattened (sdpa.rs:7-57): map.kind, map.thread_block.*, map.kv_cache.*, reduce.thread_block.*. */
+typedef struct kh_execution_variant {
+    kh_map_kernel_kind kind;
+    uint32_t max_q_tokens;
+    uint32_t max_q_heads;
+    uint32_t kv_tokens_per_iteration;
+    uint32_t required_threads;
+    uint32_t tokens_per_page;
+    uint32_t reduce_max_q_tokens;
+    uint32_t reduce_max_q_heads;
+    uint32_t reduce_required_threads;
+} kh_execution_variant;
+
+/* Config::validate (sdpa.rs:229-236). */
+KH_API kh_status kh_sdpa_config_validate(const kh_sdpa_config* config);
+/* ExecutionVariant::sliced_kv (sdpa.rs:60-88). */
+KH_API kh_status kh_variant_sliced_kv(const kh_sdpa_config* config, uint32_t kv_tokens_per_iteration,
+                                      uint32_t required_threads, uint32_t max_q_heads, kh_execution_variant* out);
+/* ExecutionVariant::sliced_q / sliced_q_per_head (sdpa.rs:90-160). */
+KH_API kh_status kh_variant_sliced_q(const kh_sdpa_config* config, kh_map_kernel_kind kind, uint32_t max_q_tokens,
+                                     uint32_t kv_tokens_per_iteration, uint32_t max_q_heads,
+                                     kh_execution_variant* out);
+/* ExecutionVariant::supports (sdpa.rs:162-215): *out = 1 when the variant is legal for config. */
+KH_API kh_status kh_variant_supports(const kh_execution_variant* variant, const kh_sdpa_config* config,
+                                     int32_t* out);
+/* Registry::new(config).variants() (sdpa.rs:255-271): writes up to `capacity` variants, sets *count. */
+KH_API kh_status kh_registry_variants(const kh_sdpa_config* config, kh_execution_variant* out, uint32_t capacity,
+                                      uint32_t* count);
+
+/* ---- page table: EM/attn/gqa/request_page_table.rs, BM/components/gqa/kv_page_write.rs:33-57 */
+typedef struct kh_page_table_layout {
+    uint32_t num_req_slots;
+    uint32_t num_gqa_layers;
+    uint32_t num_blocks;
+    uint32_t num_page_ids_per_block;
+} kh_page_table_layout;
+
+/* PageTableLayout::bytes (kv_page_write.rs:49-56). */
+KH_API kh_status kh_page_table_bytes(const kh_page_table_layout* layout, uint64_t* out);
+/* GQARequestPageTable::page_ids_start_index (request_page_table.rs:151-156): u32 element index of
+ * page_ids[req_slot][layer][block][0]. */
+KH_API kh_status kh_page_table_index(const kh_page_table_layout* layout, uint32_t req_slot, uint32_t layer_index,
+                                     uint32_t block_index, uint64_t* out);
+/* write_page_ids / read_page_ids / reset_req_slot (request_page_table.rs:86-122) on a device table. */
+KH_API kh_status kh_page_table_write(kh_device* device, kh_buffer_ref page_ids, const kh_page_table_layout* layout,
+                                     uint32_t req_slot, uint32_t layer_index, uint32_t block_index,
+                                     const uint32_t* ids, uint32_t count);
+KH_API kh_status kh_page_table_read(kh_device* device, kh_buffer_ref page_ids, const kh_page_table_layout* layout,
+                                    uint32_t req_slot, uint32_t layer_index, uint32_t block_index, uint32_t* ids,
+                                    uint32_t count);
+KH_API kh_status kh_page_table_reset_req_slot(kh_device* device, kh_buffer_ref page_ids,
+                                              const kh_page_table_layout* layout, uint32_t req_slot);
+
+/* ---- replay buckets: EC/replay.rs:4-88, EM/attn/gqa/batch_metadata.rs:68-96 ---------------- */
+/* ReplayBucketPolicy::new(max).buckets(): writes up to `capacity` buckets, sets *count to the total. */
+KH_API kh_status kh_replay_buckets(uint32_t max_capacity, uint32_t* out, uint32_t capacity, uint32_t* count);
+/* ReplayBucketPolicy::new(max).capacity(active). */
+KH_API kh_status kh_replay_capacity(uint32_t max_capacity, uint32_t active, uint32_t* out);
+
+/* GQAReplayShape (batch_metadata.rs:11-61). */
+typedef struct kh_replay_shape {
+    uint32_t num_tokens;
+    uint32_t num_total_tokens;
+    uint32_t num_q_token_tiles;
+    uint32_t num_total_q_token_tiles;
+    uint32_t num_sdpa_map_task_templates;
+    uint32_t num_total_sdpa_map_task_templates;
+    uint32_t reduce_sdpa_partial_outputs; /* bool */
+} kh_replay_shape;
+
+/* ---- selector: EM/attn/gqa/sdpa.rs ---------------------------------------------------------- */
+/* RequestShape (sdpa.rs:15-19). */
+typedef struct kh_request_shape {
+    uint32_t num_history_tokens;
+    uint32_t num_q_tokens;
+} kh_request_shape;
+
+/* SelectorLimits (sdpa.rs:43-48). */
+typedef struct kh_selector_limits {
+    uint32_t max_tokens;
+    uint32_t max_map_task_templates;
+    uint64_t partial_state_group_capacity;
+} kh_selector_limits;
+
+/* SelectionMetrics (sdpa.rs:64-77). */
+typedef struct kh_selection_metrics {
+    uint64_t num_scheduled_qk_token_pairs;
+    uint64_t num_active_qk_token_pairs;
+    uint64_t num_map_threadblocks_per_kv_head;
+    uint64_t num_map_simdgroup_waves_per_kv_head;
+    uint64_t num_active_partial_state_groups;
+    uint64_t num_active_partial_states;
+    uint64_t num_reserved_partial_state_groups;
+    uint64_t num_replay_reserved_partial_state_groups;
+    uint64_t num_logical_qk_token_pairs;
+    uint32_t max_kv_iterations_per_split;
+    uint32_t reserved;
+} kh_selection_metrics;
+
+/* QTokenRange (sdpa.rs:50-56). */
+typedef struct kh_q_token_range {
+    uint32_t request_index;
+    uint32_t flat_q_token_begin;
+    uint32_t flat_q_token_end;
+    uint32_t num_visible_kv_tokens;
+} kh_q_token_range;
+
+/* MapTaskTemplate (sdpa.rs:58-62): the three-u32 record the kernels read. */
+typedef struct kh_map_task_template {
+    uint32_t q_token_range_index;
+    uint32_t kv_token_begin;
+    uint32_t kv_token_end;
+} kh_map_task_template;
+
+typedef struct kh_selector kh_selector;
+typedef struct kh_selection kh_selection;
+
+/* Which routing policy `kh_selector_select` applies. */
+typedef uint32_t kh_selector_policy;
+enum {
+    KH_POLICY_REFERENCE = 0, /* the reference's rules, bit for bit (calibrated for a 40-core Apple GPU) */
+    KH_POLICY_B200 = 1       /* same route table, KV slice re-derived for `sm_count` SMs */
+};
+
+/* Selector::new(Registry::from_variants(config, variants), ...) (sdpa.rs:137-165, sdpa.rs:276-285).
+ * Pass num_variants = 0 to use Registry::new(config). */
+KH_API kh_status kh_selector_create(const kh_sdpa_config* config, const kh_execution_variant* variants,
+                                    uint32_t num_variants, uint32_t max_tokens, uint32_t max_map_task_templates,
+                                    uint64_t partial_state_group_capacity, kh_selector** out);
+/* Selector::for_lookup (sdpa.rs:210-276). */
+KH_API kh_status kh_selector_create_for_lookup(const kh_sdpa_config* config, uint32_t max_tokens,
+                                               const kh_page_table_layout* layout, kh_selector** out);
+/* Selector::for_partitions (sdpa.rs:170-207); max_kv_splits[i] belongs to variants[i]. */
+KH_API kh_status kh_selector_create_for_partitions(const kh_sdpa_config* config,
+                                                   const kh_execution_variant* variants, uint32_t num_variants,
+                                                   const uint32_t* max_kv_splits, uint32_t max_tokens,
+                                                   uint32_t max_requests, kh_selector** out);
+KH_API kh_status kh_selector_destroy(kh_selector* selector);
+KH_API kh_status kh_selector_limits_get(const kh_selector* selector, kh_selector_limits* out);
+KH_API kh_status kh_selector_variants(const kh_selector* selector, kh_execution_variant* out, uint32_t capacity,
+                                      uint32_t* count);
+/* Sets the routing policy and the SM count the KH_POLICY_B200 slice rule targets. */
+KH_API kh_status kh_selector_set_policy(kh_selector* selector, kh_selector_policy policy, uint32_t sm_count);
+
+/* Selector::select (sdpa.rs:278-380). The replay bucket policy is
+ * GQAReplayBucketPolicy::new(policy_max_tokens, policy_max_map_task_templates). */
+KH_API kh_status kh_selector_select(const kh_selector* selector, const kh_request_shape* requests,
+                                    uint32_t num_requests, uint32_t policy_max_tokens,
+                                    uint32_t policy_max_map_task_templates, uint32_t num_total_tokens,
+                                    kh_selection** out);
+/* Selector::select_partitioned (sdpa.rs:382-426). */
+KH_API kh_status kh_selector_select_partitioned(const kh_selector* selector, const kh_execution_variant* variant,
+                                                uint32_t kv_slice, int32_t direct_output,
+                                                const kh_request_shape* requests, uint32_t num_requests,
+                                                uint32_t policy_max_tokens, uint32_t policy_max_map_task_templates,
+                                                uint32_t num_total_tokens, kh_selection** out);
+KH_API kh_status kh_selection_destroy(kh_selection* selection);
+/* Selection accessors (sdpa.rs:99-125). Array getters write up to `capacity` records and set *count. */
+KH_API kh_status kh_selection_variant(const kh_selection* selection, kh_execution_variant* out);
+KH_API kh_status kh_selection_direct_output(const kh_selection* selection, int32_t* out);
+KH_API kh_status kh_selection_replay_shape(const kh_selection* selection, kh_replay_shape* out);
+KH_API kh_status kh_selection_metrics_get(const kh_selection* selection, kh_selection_metrics* out);
+KH_API kh_status kh_selection_q_token_ranges(const kh_selection* selection, kh_q_token_range* out, uint32_t capacity,
+                                             uint32_t* count);
+KH_API kh_status kh_selection_map_task_templates(const kh_selection* selection, kh_map_task_template* out,
+                                                 uint32_t capacity, uint32_t* count);
+KH_API kh_status kh_selection_cu_partial_outputs(const kh_selection* selection, uint32_t* out, uint32_t capacity,
+                                                 uint32_t* count);
+
+/* ---- batch metadata: EM/attn/gqa/batch_metadata.rs:100-253 ---------------------------------- */
+/* Host images of the six device arrays GQAMetadataBuffers::update uploads. The caller owns the
+ * arrays (capacities in elements); `update` fills them exactly as the reference fills its
+ * buffers, including the u32::MAX padding of map templates up to the padded capacity, and does
+ * not touch q_token_ranges for a SlicedKv selection. Elements past what `update` writes keep
+ * their previous contents. */
+typedef struct kh_metadata_arrays {
+    uint32_t* req_slots;               /* [max_tokens] */
+    uint32_t* flat_token_indices;      /* [max_tokens] */
+    uint32_t* visible_kv_token_ranges; /* [max_tokens][2] */
+    uint32_t* q_token_ranges;          /* [max_tokens][2] */
+    uint32_t* sdpa_map_task_templates; /* [max_map_task_templates][3] */
+    uint32_t* cu_sdpa_partial_outputs; /* [max_tokens + 1] */
+    uint32_t max_tokens;
+    uint32_t max_map_task_templates;
+} kh_metadata_arrays;
+
+KH_API kh_status kh_metadata_update(const kh_metadata_arrays* arrays, const uint32_t* req_slots,
+                                    const uint32_t* token_indices, const uint32_t* cu_tokens, uint32_t num_requests,
+                                    const kh_selection* selection, kh_replay_shape* out_shape);
+
+/* ---- SlicedKv compute: BM/components/gqa/sdpa/sliced_kv.rs ---------------------------------- */
+/* sliced_kv::Config (sliced_kv.rs:90-98) plus the KV-cache element type, which the reference
+ * fixes at one byte (sliced_kv.rs:113-125) and this library makes a parameter. tokens per page =
+ * page_bytes / (2 * num_kv_heads * head_dim * sizeof(kv_dtype)). */
+typedef struct kh_sliced_kv_config {
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    float scale;
+    uint32_t page_bytes;
+    kh_page_table_layout page_table_layout;
+    kh_dtype dtype;    /* Q / output element type */
+    kh_dtype kv_dtype; /* K/V page element type */
+} kh_sliced_kv_config;
+
+/* sliced_kv::Shape (sliced_kv.rs:215-219). */
+typedef struct kh_sliced_kv_shape {
+    uint32_t num_total_tokens;
+    uint32_t num_total_sdpa_map_task_templates;
+} kh_sliced_kv_shape;
+
+/* sliced_kv::MapBuffers (sliced_kv.rs:236-246), binding order 0..7 of MapInvocation::record
+ * (sliced_kv.rs:562-569). Partial statistics are f32 [Mt][Hq]; partial_output is f32 [Mt][Hq][D]
+ * (the reference stores it in the io dtype; this library keeps it in f32). */
+typedef struct kh_sliced_kv_map_buffers {
+    kh_buffer_ref q;
+    kh_buffer_ref kv_pages;
+    kh_buffer_ref req_slots;
+    kh_buffer_ref page_ids;
+    kh_buffer_ref sdpa_map_task_templates;
+    kh_buffer_ref partial_exp_sums;
+    kh_buffer_ref partial_max_logits;
+    kh_buffer_ref partial_output;
+} kh_sliced_kv_map_buffers;
+
+/* sliced_kv::ReduceBuffers (sliced_kv.rs:248-254). */
+typedef struct kh_sliced_kv_reduce_buffers {
+    kh_buffer_ref partial_exp_sums;
+    kh_buffer_ref partial_max_logits;
+    kh_buffer_ref partial_output;
+    kh_buffer_ref cu_sdpa_partial_outputs;
+    kh_buffer_ref output;
+} kh_sliced_kv_reduce_buffers;
+
+/* Byte sizes of Config (sliced_kv.rs:140-212). */
+typedef struct kh_sliced_kv_sizes {
+    uint64_t q_bytes;
+    uint64_t req_slots_bytes;
+    uint64_t page_ids_bytes;
+    uint64_t sdpa_map_task_templates_bytes;
+    uint64_t cu_sdpa_partial_outputs_bytes;
+    uint64_t partial_output_stats_bytes;
+    uint64_t partial_output_bytes;
+    uint32_t num_tokens_per_page;
+    uint32_t reserved;
+} kh_sliced_kv_sizes;
+
+typedef struct kh_sliced_kv kh_sliced_kv;
+
+/* Config::validate + Shape::validate + byte sizes. */
+KH_API kh_status kh_sliced_kv_sizes_get(const kh_sliced_kv_config* config, const kh_sliced_kv_shape* shape,
+                                        kh_sliced_kv_sizes* out);
+/* Compute::new(device, config, execution, shape) (sliced_kv.rs:322-355). */
+KH_API kh_status kh_sliced_kv_create(kh_device* device, const kh_sliced_kv_config* config,
+                                     const kh_execution_variant* execution, const kh_sliced_kv_shape* shape,
+                                     kh_sliced_kv** out);
+KH_API kh_status kh_sliced_kv_destroy(kh_sliced_kv* compute);
+/* Compute::invoke_map(...).record (sliced_kv.rs:357-375, 558-592). */
+KH_API kh_status kh_sliced_kv_map(kh_sliced_kv* compute, kh_stream* stream, const kh_sliced_kv_map_buffers* buffers,
+                                  uint32_t page_table_index, uint32_t num_active_tokens,
+                                  uint32_t num_active_kv_splits);
+/* Compute::invoke_reduce(...).record (sliced_kv.rs:377-388, 623-638). */
+KH_API kh_status kh_sliced_kv_reduce(kh_sliced_kv* compute, kh_stream* stream,
+                                     const kh_sliced_kv_reduce_buffers* buffers, uint32_t num_active_tokens);
+
+/* ---- SlicedQ compute: BM/components/gqa/sdpa/sliced_q.rs ------------------------------------ */
+/* sliced_q::Config (sliced_q.rs:145-153) plus kv_dtype. */
+typedef struct kh_sliced_q_config {
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    float scale;
+    uint32_t page_bytes;
+    kh_dtype dtype;
+    kh_page_table_layout page_table_layout;
+    kh_dtype kv_dtype;
+} kh_sliced_q_config;
+
+/* sliced_q::Shape (sliced_q.rs:248-253). */
+typedef struct kh_sliced_q_shape {
+    uint32_t num_total_tokens;
+    uint32_t num_total_q_token_tiles;
+    uint32_t num_total_sdpa_map_task_templates;
+} kh_sliced_q_shape;
+
+/* sliced_q::MapBuffers (sliced_q.rs:308-321). Partial ABI: statistics f32 [Mt][Hq][max_q_tokens],
+ * output f32 [Mt][Hq][max_q_tokens][D] (sliced_q.rs:78-101, io dtype there, f32 here). */
+typedef struct kh_sliced_q_map_buffers {
+    kh_buffer_ref q;
+    kh_buffer_ref kv_pages;
+    kh_buffer_ref req_slots;
+    kh_buffer_ref page_ids;
+    kh_buffer_ref visible_kv_token_ranges;
+    kh_buffer_ref q_token_ranges;
+    kh_buffer_ref sdpa_map_task_templates;
+    kh_buffer_ref partial_output;
+    kh_buffer_ref partial_exp_sums;
+    kh_buffer_ref partial_max_logits;
+} kh_sliced_q_map_buffers;
+
+/* sliced_q::DirectBuffers (sliced_q.rs:325-335). */
+typedef struct kh_sliced_q_direct_buffers {
+    kh_buffer_ref q;
+    kh_buffer_ref kv_pages;
+    kh_buffer_ref req_slots;
+    kh_buffer_ref page_ids;
+    kh_buffer_ref visible_kv_token_ranges;
+    kh_buffer_ref q_token_ranges;
+    kh_buffer_ref sdpa_map_task_templates;
+    kh_buffer_ref output;
+} kh_sliced_q_direct_buffers;
+
+/* sliced_q::ReduceBuffers (sliced_q.rs:337-345). */
+typedef struct kh_sliced_q_reduce_buffers {
+    kh_buffer_ref partial_output;
+    kh_buffer_ref partial_exp_sums;
+    kh_buffer_ref partial_max_logits;
+    kh_buffer_ref q_token_ranges;
+    kh_buffer_ref cu_sdpa_partial_outputs;
+    kh_buffer_ref output;
+} kh_sliced_q_reduce_buffers;
+
+typedef struct kh_sliced_q_sizes {
+    uint64_t q_bytes;
+    uint64_t partial_output_bytes;
+    uint64_t partial_output_stats_bytes;
+    uint32_t num_tokens_per_page;
+    uint32_t reserved;
+} kh_sliced_q_sizes;
+
+typedef struct kh_sliced_q kh_sliced_q;
+
+KH_API kh_status kh_sliced_q_sizes_get(const kh_sliced_q_config* config, const kh_execution_variant* execution,
+                                       const kh_sliced_q_shape* shape, kh_sliced_q_sizes* out);
+/* Compute::new / Compute::new_direct (sliced_q.rs:356-363). */
+KH_API kh_status kh_sliced_q_create(kh_device* device, const kh_sliced_q_config* config,
+                                    const kh_execution_variant* execution, const kh_sliced_q_shape* shape,
+                                    int32_t direct_output, kh_sliced_q** out);
+KH_API kh_status kh_sliced_q_destroy(kh_sliced_q* compute);
+/* Compute::invoke_map(...).record (sliced_q.rs:417-454, 547-592). */
+KH_API kh_status kh_sliced_q_map(kh_sliced_q* compute, kh_stream* stream, const kh_sliced_q_map_buffers* buffers,
+                                 uint32_t page_table_index, uint32_t num_active_tokens,
+                                 uint32_t num_active_q_token_tiles, uint32_t num_active_kv_splits);
+/* Compute::invoke_direct(...).record (sliced_q.rs:456-482). */
+KH_API kh_status kh_sliced_q_direct(kh_sliced_q* compute, kh_stream* stream,
+                                    const kh_sliced_q_direct_buffers* buffers, uint32_t page_table_index,
+                                    uint32_t num_active_tokens, uint32_t num_active_q_token_tiles);
+/* Compute::invoke_reduce(...).record (sliced_q.rs:484-503, 617-642). */
+KH_API kh_status kh_sliced_q_reduce(kh_sliced_q* compute, kh_stream* stream,
+                                    const kh_sliced_q_reduce_buffers* buffers, uint32_t num_active_q_token_tiles);
+
+/* ---- device status word: the analogue of SubmissionCheck (BM/metal/stream/check.rs:8-13) ---- */
+/* Reads (after synchronising the stream) and clears the sticky status the kernels of `device`
+ * write: 0 = clean; bit 0 = a bounded wait inside a kernel ran out; bit 1 = a page id addressed
+ * beyond the KV pool. Nonzero also returns KH_ABORTED. */
+KH_API kh_status kh_device_check(kh_device* device, kh_stream* stream, uint32_t* out_status_word);
+
+/* ---- cross-partition / cross-GPU LSE combine ------------------------------------------------ */
+/* Merges `num_partials` partial triples per (token, head) row with the partial-state merge of
+ * docs/gqa_sdpa_selection.md:443-460 (the formula of gqa_sdpa_sliced_kv_reduce.metal:30-55).
+ * Layout: exp_sums / max_logits f32 [num_partials][num_rows], partial_output f32
+ * [num_partials][num_rows][head_dim], rows = tokens * num_q_heads. Writes `output` in `out_dtype`
+ * ([num_rows][head_dim]); when out_exp_sums / out_max_logits are non-null also writes the merged
+ * statistics (f32 [num_rows]) so merges can be chained (per GPU, then across GPUs after an
+ * all-gather). The reference has no multi-device path; this is the merge its reducer applies,
+ * exposed for partials that arrive from other GPUs. */
+KH_API kh_status kh_combine_partials(kh_device* device, kh_stream* stream, uint32_t num_partials, uint32_t num_rows,
+                                     uint32_t head_dim, kh_buffer_ref exp_sums, kh_buffer_ref max_logits,
+                                     kh_buffer_ref partial_output, kh_dtype out_dtype, kh_buffer_ref output,
+                                     kh_buffer_ref out_exp_sums, kh_buffer_ref out_max_logits);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* KH_GQA_H_ */

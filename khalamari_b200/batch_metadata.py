@@ -1,0 +1,123 @@
+"""Batch metadata ABI: ``GQAMetadataBuffers``
+(crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs:100-320). Six capacity-sized u32 device
+arrays refreshed from one complete selection. Host images live in page-locked memory so that ``update``
+is a fill plus stream-ordered copies."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+from .device import Buffer, Device, PinnedArray, Stream
+from .replay import GQAReplayShape
+from .sdpa import ExecutionVariant, MapKernelKind
+from .selector import Selection
+
+_FIELDS = (("req_slots", 1), ("flat_token_indices", 1), ("visible_kv_token_ranges", 2), ("q_token_ranges", 2),
+           ("sdpa_map_task_templates", 3), ("cu_sdpa_partial_outputs", 1))
+
+
+class GQAMetadataBuffers:
+    def __init__(self, device: Device, max_tokens: int, max_map_task_templates: int):
+        if max_tokens <= 0:
+            raise abi.InvalidArgument(1, "GQA batch metadata requires tokens")
+        if max_map_task_templates <= 0:
+            raise abi.InvalidArgument(1, "GQA batch metadata requires Map task templates")
+        self._device = device
+        self._max_tokens = max_tokens
+        self._max_maps = max_map_task_templates
+        counts = {
+            "req_slots": max_tokens, "flat_token_indices": max_tokens, "visible_kv_token_ranges": max_tokens * 2,
+            "q_token_ranges": max_tokens * 2, "sdpa_map_task_templates": max_map_task_templates * 3,
+            "cu_sdpa_partial_outputs": max_tokens + 1,
+        }
+        self._host = {name: PinnedArray(count, np.uint32) for name, count in counts.items()}
+        for pinned in self._host.values():
+            pinned.array[:] = 0
+        self._dev = {name: Buffer.new_zeroed(device, count * 4) for name, count in counts.items()}
+        self._replay_shape = None
+        self._variant = None
+
+    def max_tokens(self) -> int:
+        return self._max_tokens
+
+    def max_map_task_templates(self) -> int:
+        return self._max_maps
+
+    def update(self, req_slots, token_indices, cu_tokens, selection: Selection,
+               stream: Stream | None = None) -> GQAReplayShape:
+        """``GQAMetadataBuffers::update`` (batch_metadata.rs:171-253): fills the host images through the C
+        ABI and uploads the written prefixes (on ``stream`` when given, else synchronously)."""
+        rs = np.ascontiguousarray(req_slots, dtype=np.uint32)
+        ti = np.ascontiguousarray(token_indices, dtype=np.uint32)
+        cu = np.ascontiguousarray(cu_tokens, dtype=np.uint32)
+        if rs.size != ti.size or cu.size != rs.size + 1:
+            raise abi.InvalidArgument(1, "GQA metadata update needs one slot and index per request and n+1 offsets")
+        u32p = C.POINTER(C.c_uint32)
+        arrays = abi.MetadataArraysC(
+            *[C.cast(self._host[name].ptr, u32p) for name, _ in _FIELDS], self._max_tokens, self._max_maps)
+        shape_c = abi.ReplayShapeC()
+        abi.call("kh_metadata_update", C.byref(arrays), rs.ctypes.data_as(u32p), ti.ctypes.data_as(u32p),
+                 cu.ctypes.data_as(u32p), rs.size, selection.handle, C.byref(shape_c))
+        shape = GQAReplayShape.from_c(shape_c)
+        variant = selection.variant()
+        written = {
+            "req_slots": shape.num_tokens, "flat_token_indices": shape.num_tokens,
+            "visible_kv_token_ranges": shape.num_tokens * 2,
+            "q_token_ranges": 0 if variant.kind == MapKernelKind.SlicedKv else shape.num_q_token_tiles * 2,
+            "sdpa_map_task_templates": shape.num_total_sdpa_map_task_templates * 3,
+            "cu_sdpa_partial_outputs": shape.num_q_token_tiles + 1,
+        }
+        for name, count in written.items():
+            if count == 0:
+                continue
+            if stream is None:
+                self._dev[name].write(0, self._host[name].array[:count])
+            else:
+                stream.write(self._dev[name], 0, self._host[name].ptr, count * 4)
+        self._replay_shape = shape
+        self._variant = variant
+        return shape
+
+    def upload_bytes(self) -> int:
+        """Bytes the last ``update`` copied to the device."""
+        shape, variant = self.replay_shape(), self.variant()
+        words = shape.num_tokens * 4 + shape.num_total_sdpa_map_task_templates * 3 + shape.num_q_token_tiles + 1
+        if variant.kind != MapKernelKind.SlicedKv:
+            words += shape.num_q_token_tiles * 2
+        return words * 4
+
+    def req_slots(self) -> Buffer:
+        return self._dev["req_slots"]
+
+    def flat_token_indices(self) -> Buffer:
+        return self._dev["flat_token_indices"]
+
+    def visible_kv_token_ranges(self) -> Buffer:
+        return self._dev["visible_kv_token_ranges"]
+
+    def q_token_ranges(self) -> Buffer:
+        return self._dev["q_token_ranges"]
+
+    def sdpa_map_task_templates(self) -> Buffer:
+        return self._dev["sdpa_map_task_templates"]
+
+    def cu_sdpa_partial_outputs(self) -> Buffer:
+        return self._dev["cu_sdpa_partial_outputs"]
+
+    def host_image(self, name: str) -> np.ndarray:
+        return self._host[name].array
+
+    def replay_shape(self) -> GQAReplayShape:
+        if self._replay_shape is None:
+            raise abi.InvalidArgument(1, "GQA batch metadata must be updated before recording")
+        return self._replay_shape
+
+    def variant(self) -> ExecutionVariant:
+        if self._variant is None:
+            raise abi.InvalidArgument(1, "GQA batch metadata must be updated before recording")
+        return self._variant
+
+    def direct_output(self) -> bool:
+        return self.variant().kind != MapKernelKind.SlicedKv and not self.replay_shape().reduce_sdpa_partial_outputs
