@@ -1,0 +1,390 @@
+#!/usr/bin/env python
+"""Benchmark of the paged GQA split-KV decode attention path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c2|c3|c1]
+
+One step = one attention call (map + LSE reduce) over one batch of synthetic paged decode requests.
+Default workload: batch 64, q_len 1, Hq 64 / Hkv 8 / head_dim 128, bf16, context lengths uniform in
+[1024, 8192] (seed 1), 16-token pages in a 40,000-page pool with random block tables, split-KV partitions
+of 512 tokens. Metric: KV-read GB/s = algorithmic KV bytes (every visible K and V row once) / time.
+With N > 1 every rank runs its own batch of independent requests (no collective on the data path; weak
+scaling) and the value is the sum of all ranks' KV bytes over the slowest rank's time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (batch, q_len, Hq, Hkv, D, dtype, context range, seed, partition)
+    "c2": dict(batch=64, q_len=1, hq=64, hkv=8, d=128, dtype="bf16", lo=1024, hi=8192, seed=1, partition=512,
+               pool_pages=40000, label="paged decode B64 Hq64/Hkv8/D128 bf16 ctx U[1024,8192] P16 part512"),
+    "c3": dict(batch=32, q_len=4, hq=24, hkv=4, d=256, dtype="bf16", lo=4096, hi=32768, seed=2, partition=0,
+               pool_pages=0, label="verify B32 q4 Hq24/Hkv4/D256 bf16 prefix U[4096,32768] P16"),
+    "c1": dict(batch=4, q_len=1, hq=16, hkv=2, d=256, dtype="f16", lo=0, hi=0, seed=0, partition=0, pool_pages=0,
+               contexts=[128, 517, 1024, 2048], label="decode B4 Hq16/Hkv2/D256 fp16 ctx {128,517,1024,2048} P16"),
+}
+PAGE = 16
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def contexts_for(spec, rank):
+    if "contexts" in spec:
+        return list(spec["contexts"])
+    rng = np.random.default_rng(spec["seed"] + 1000 * rank)
+    return rng.integers(spec["lo"], spec["hi"] + 1, size=spec["batch"]).tolist()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.stop = threading.Event()
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _sample(self):
+        try:
+            out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+            parts = [p.strip() for p in out.strip().split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self.stop.is_set():
+            self._sample()
+            self.stop.wait(0.2)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join(timeout=15)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(float(s[0])) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def build_device_case(device, spec, contexts, torch, seed):
+    """Synthetic inputs created on the device: N(0,1) Q/K/V in the storage dtype, a shared page pool and
+    per-request block tables that are random permutations of pool pages. Only pages a request owns are
+    filled; the rest of the pool keeps its allocation bytes."""
+    from khalamari_b200.device import Buffer
+    dt = torch.bfloat16 if spec["dtype"] == "bf16" else torch.float16
+    hq, hkv, d = spec["hq"], spec["hkv"], spec["d"]
+    page_elems = 2 * hkv * PAGE * d
+    pages_per_req = [-(-c // PAGE) for c in contexts]
+    pool_pages = spec["pool_pages"] or (sum(pages_per_req) + 16)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    pool = torch.empty(pool_pages * page_elems, dtype=dt, device="cuda")
+    chunk = 1 << 26
+    for begin in range(0, pool.numel(), chunk):
+        end = min(begin + chunk, pool.numel())
+        pool[begin:end] = torch.randn(end - begin, generator=gen, device="cuda", dtype=torch.float32).to(dt)
+    num_blocks = max(pages_per_req)
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(pool_pages).astype(np.uint32)
+    table = np.zeros((len(contexts), num_blocks), dtype=np.uint32)
+    cursor = 0
+    for r, n in enumerate(pages_per_req):
+        table[r, :n] = perm[cursor:cursor + n]
+        cursor += n
+    total_q = len(contexts) * spec["q_len"]
+    q = torch.randn(total_q * hq * d, generator=gen, device="cuda", dtype=torch.float32).to(dt)
+    out = torch.zeros_like(q)
+    wrap = lambda t: Buffer.wrap(device, t.data_ptr(), t.numel() * t.element_size())
+    return dict(pool=pool, q=q, out=out, table=table, d_pool=wrap(pool), d_q=wrap(q), d_out=wrap(out),
+                d_table=Buffer.from_slice(device, table.reshape(-1)), num_blocks=num_blocks)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from khalamari_b200.device import Device, Dtype, PinnedArray, Stream
+    from khalamari_b200.gqa import GQAAttention, GQACore
+    from khalamari_b200.request_page_table import GQAPageTableLayout
+    from khalamari_b200.selector import SelectorPolicy
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    spec = dict(WORKLOADS[args.workload])
+    if args.batch:
+        spec["batch"] = args.batch
+        spec["label"] += f" [batch {args.batch}]"
+    if args.pool_pages:
+        spec["pool_pages"] = args.pool_pages
+    if args.partition >= 0:
+        spec["partition"] = args.partition
+        spec["label"] += f" [partition {args.partition or 'selector'}]"
+    contexts = contexts_for(spec, rank)
+    q_len = spec["q_len"]
+    device = Device(local)
+    case = build_device_case(device, spec, contexts, torch, spec["seed"] + 1000 * rank)
+    torch_stream = torch.cuda.current_stream()
+    stream = Stream(device, torch_stream.cuda_stream)
+    io_dtype = Dtype.Bfloat16 if spec["dtype"] == "bf16" else Dtype.Float16
+    layout = GQAPageTableLayout(len(contexts), 1, case["num_blocks"], 1)
+    scale = 1.0 / float(np.sqrt(spec["d"]))
+    attention = GQAAttention(device, GQACore(spec["d"], spec["hq"], spec["hkv"], scale), io_dtype,
+                             2 * spec["hkv"] * PAGE * spec["d"] * 2, layout, len(contexts) * q_len,
+                             SelectorPolicy.B200)
+    req_slots = list(range(len(contexts)))
+    token_indices = [c - q_len for c in contexts]
+    cu_tokens = [i * q_len for i in range(len(contexts) + 1)]
+    selection = None
+    if spec["partition"]:
+        variant = next(v for v in attention.selector.variants() if v.kind == 0 and v.thread_block.max_q_tokens == 1)
+        selection = attention.select_partitioned(variant, spec["partition"], False, token_indices, cu_tokens)
+    attention.prepare(req_slots, token_indices, cu_tokens, selection=selection)
+    shape = attention.metadata.replay_shape()
+    kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * 2  # q_len new tokens are already in the cache
+
+    def step():
+        return attention.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    device.check(stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches = 0
+    with ClockSampler(local) as clocks:
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            events[i][0].record(torch_stream)
+            att = attention
+            meta = att.metadata
+            # the two halves of record_sdpa with an event between them, to time the map kernel by itself
+            if meta.variant().kind == 0:
+                from khalamari_b200 import sliced_kv
+                compute = att._sliced_kv(shape, meta.variant())
+                compute.invoke_map(stream, sliced_kv.MapBuffers(
+                    case["d_q"], case["d_pool"], meta.req_slots(), case["d_table"], meta.sdpa_map_task_templates(),
+                    att.partial_exp_sums, att.partial_max_logits, att.partial_output), 0, shape.num_tokens,
+                    shape.num_sdpa_map_task_templates)
+                events[i][1].record(torch_stream)
+                compute.invoke_reduce(stream, sliced_kv.ReduceBuffers(
+                    att.partial_exp_sums, att.partial_max_logits, att.partial_output, meta.cu_sdpa_partial_outputs(),
+                    case["d_out"]), shape.num_tokens)
+                launches += 2
+            else:
+                launches += step()
+                events[i][1].record(torch_stream)
+            events[i][2].record(torch_stream)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        barrier()
+        clock_summary = clocks.summary()
+    device.check(stream)
+    step_ms = [events[i][0].elapsed_time(events[i][2]) for i in range(args.steps)]
+    map_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
+    total_ms = events[0][0].elapsed_time(events[-1][2])
+    ms_per_step = total_ms / args.steps
+
+    # ---- end to end through the component seam with host buffers -------------------------------------
+    row_bytes = spec["hq"] * spec["d"] * 2
+    q_host = PinnedArray(len(contexts) * q_len * spec["hq"] * spec["d"], np.uint16)
+    out_host = PinnedArray(len(contexts) * q_len * spec["hq"] * spec["d"], np.uint16)
+    q_host.array[:] = case["q"].view(torch.int16).cpu().numpy().view(np.uint16)
+    e2e_steps = args.steps
+    h2d = d2h = 0
+    for _ in range(3):
+        attention.attend_host(stream, q_host, out_host, case["d_q"], case["d_out"], case["d_pool"], case["d_table"],
+                              req_slots, token_indices, cu_tokens, 0, selection)
+        stream.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        _, h2d, d2h = attention.attend_host(stream, q_host, out_host, case["d_q"], case["d_out"], case["d_pool"],
+                                            case["d_table"], req_slots, token_indices, cu_tokens, 0, selection)
+        stream.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    checksum = float(np.abs(out_host.array.view(np.int16).astype(np.float32)).sum())
+    device.check(stream)
+
+    # ---- max over ranks ----------------------------------------------------------------------------
+    stats = torch.tensor([ms_per_step, e2e_s * 1e3, float(np.mean(map_ms))], device="cuda", dtype=torch.float64)
+    totals = torch.tensor([float(kv_bytes), float(len(contexts) * q_len)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    ms_per_step, e2e_ms, map_ms_mean = stats.tolist()
+    total_kv_bytes, total_tokens = totals.tolist()
+
+    result = None
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        value = total_kv_bytes / (ms_per_step * 1e-3) / 1e9
+        achieved = kv_bytes / (map_ms_mean * 1e-3) / 1e9  # rank 0's map kernel against one GPU's peak
+        result = {
+            "metric": "GQA decode KV-read GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if spec["dtype"] == "bf16" else "f16",
+            "data": "synthetic",
+            "config": {"workload": spec["label"], "batch_per_gpu": len(contexts), "q_len": q_len,
+                       "kv_tokens_per_gpu": int(sum(contexts)), "map_tasks": shape.num_sdpa_map_task_templates * spec["hkv"],
+                       "l2": "inputs (KV pages read per step) larger than L2; no flush", "parallelism": f"dp{world} by request"},
+            "tokens_per_s": round(total_tokens / (ms_per_step * 1e-3), 1),
+            "hbm_frac": round(value / world / peak, 4),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel": "sdpa_map_kernel", "kernel_ms": round(map_ms_mean, 5)},
+            "e2e": {"value": round(total_kv_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 5),
+                    "tokens_per_s": round(total_tokens / (e2e_ms * 1e-3), 1)},
+            "gpu_launches": launches,
+            "clocks": clock_summary,
+            "step_ms_min_median_max": [round(min(step_ms), 5), round(sorted(step_ms)[len(step_ms) // 2], 5),
+                                       round(max(step_ms), 5)],
+            "output_checksum": checksum,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_baseline(spec, contexts, sample_requests=len(contexts))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+def cpu_inputs(spec, contexts, sample_requests, seed):
+    rng = np.random.default_rng(seed)
+    import oracle
+    rounder = oracle.round_bf16 if spec["dtype"] == "bf16" else oracle.round_f16
+    hq, hkv, d, q_len = spec["hq"], spec["hkv"], spec["d"], spec["q_len"]
+    ctxs = contexts[:sample_requests]
+    ks = [rounder(rng.standard_normal((c, hkv, d), dtype=np.float32))[1] for c in ctxs]
+    vs = [rounder(rng.standard_normal((c, hkv, d), dtype=np.float32))[1] for c in ctxs]
+    q = rounder(rng.standard_normal((len(ctxs) * q_len, hq, d), dtype=np.float32))[1]
+    cu = [i * q_len for i in range(len(ctxs) + 1)]
+    ti = [c - q_len for c in ctxs]
+    return cu, ti, q, ks, vs
+
+
+def cpu_pass(spec, inputs, threads):
+    import oracle
+    cu, ti, q, ks, vs = inputs
+    scale = 1.0 / float(np.sqrt(spec["d"]))
+    t0 = time.perf_counter()
+    oracle.projected_gqa(cu, ti, q, ks, vs, spec["d"], spec["hq"], spec["hkv"], scale, threads)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(spec, contexts, sample_requests):
+    """The CPU restatement of the reference's GQA SDPA (oracle/, kind "port") on the host cores, contiguous
+    per-request K/V as the reference's CPU path takes them, one pass over a bounded sample."""
+    import oracle
+    threads = oracle.max_threads()
+    # keep the sample near 10-30 s of CPU work: about 0.4 core-seconds per 4.6k-token Hq64/D128 request
+    work = sum(contexts[:sample_requests]) * spec["hq"] * spec["d"] * spec["q_len"]
+    budget = 2.0e11 * threads / 8
+    while sample_requests > 1 and work > budget:
+        sample_requests //= 2
+        work = sum(contexts[:sample_requests]) * spec["hq"] * spec["d"] * spec["q_len"]
+    inputs = cpu_inputs(spec, contexts, sample_requests, spec["seed"])
+    seconds = cpu_pass(spec, inputs, threads)
+    sample_bytes = sum(contexts[:sample_requests]) * 2 * spec["hkv"] * spec["d"] * 2
+    return {"value": round(sample_bytes / seconds / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"first {sample_requests} of {len(contexts)} requests, one pass, {seconds:.2f} s",
+            "tokens_per_s": round(sample_requests * spec["q_len"] / seconds, 2)}
+
+
+def run_reference(args):
+    """The reference arm: the reference's own CPU implementation of the path. The reference is Rust and
+    cannot be built in this image, so this times its C restatement (oracle/) on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    import oracle
+    spec = WORKLOADS[args.workload]
+    contexts = contexts_for(spec, 0)
+    threads = oracle.max_threads()
+    sample = max(1, min(len(contexts), 8))
+    inputs = cpu_inputs(spec, contexts, sample, spec["seed"])
+    for _ in range(min(args.warmup, 1)):
+        cpu_pass(spec, inputs, threads)
+    times = [cpu_pass(spec, inputs, threads) for _ in range(args.steps)]
+    seconds = float(np.mean(times))
+    sample_bytes = sum(contexts[:sample]) * 2 * spec["hkv"] * spec["d"] * 2
+    value = round(sample_bytes / seconds / 1e9, 4)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return {
+        "impl": "reference", "metric": "GQA decode KV-read GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": round(seconds * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": spec["label"], "sample": f"first {sample} of {len(contexts)} requests per step"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"first {sample} of {len(contexts)} requests per step, {args.steps} steps"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "tokens_per_s": round(sample * spec["q_len"] / seconds, 2),
+    }
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")
+    parser.add_argument("--pool-pages", type=int, default=0, help="override the page pool size (profiling captures)")
+    parser.add_argument("--partition", type=int, default=-1, help="override the split-KV partition (0: selector)")
+    args = parser.parse_args()
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if result is not None:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

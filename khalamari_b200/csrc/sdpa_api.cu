@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(128) sdpa_reduce_kernel(const ReduceParams p) 
 // ---------------------------------------------------------------------------------------------
 // Kernel instance table
 // ---------------------------------------------------------------------------------------------
-using MapKernel = void (*)(const CUtensorMap, const MapParams);
+using MapKernel = void (*)(const CUtensorMap, const CUtensorMap, const MapParams);
 
 struct MapInstance {
     MapKernel kernel;
@@ -153,46 +154,40 @@ struct MapInstance {
     int stages;
 };
 
-template <typename T, int D, int P, int MT, int KVW>
+template <typename T, int D, int P, int MT, int KVW, bool HALF>
 static MapInstance make_instance() {
-    using G = MapGeometry<D, P, MT, KVW>;
-    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
-                       G::kStages};
+    using G = MapGeometry<D, P, MT, KVW, HALF>;
+    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, HALF>, G::kThreads, G::kSmemBytes, G::kStageTokens,
+                       G::kBoxRows, G::kStages};
 }
 
-// Consumer-warp shapes. head_dim 128 runs 8 consumer warps plus the producer (9 warps, 168 registers per
-// thread, no spills). head_dim 256 keeps a 16 x 256 f32 accumulator per thread (128 registers), so it runs
-// 4 consumer warps plus the producer (5 warps, up to 255 registers per thread).
+// Consumer-warp shapes: 4 consumer warps plus the producer (5 warps, up to 255 registers per thread, one
+// consumer warp per SM sub-partition). `rows` = Q rows per task (max_q_tokens x max_q_heads); tasks of at
+// most 8 rows (decode with a group of up to 8 heads) use the half-tile instance, which skips the softmax
+// work of fragment rows 8-15 and uses them to carry the rounding remainder of the probabilities.
 template <typename T, int D, int P>
-static MapInstance pick_rows(uint32_t row_tiles) {
-    constexpr int kConsumers = (D == 128) ? 8 : 4;
-    switch (row_tiles) {
-        case 1:
-            return make_instance<T, D, P, 1, kConsumers>();
-        case 2:
-            return make_instance<T, D, P, 2, kConsumers / 2>();
-        case 4:
-            return make_instance<T, D, P, 4, kConsumers / 4>();
-        default:
-            return make_instance<T, D, P, 8, 1>();
-    }
+static MapInstance pick_rows(uint32_t rows) {
+    constexpr int kConsumers = 4;
+    if (rows <= 8) return make_instance<T, D, P, 1, kConsumers, true>();
+    if (rows <= 16) return make_instance<T, D, P, 1, kConsumers, false>();
+    if (rows <= 32) return make_instance<T, D, P, 2, kConsumers / 2, false>();
+    if (rows <= 64) return make_instance<T, D, P, 4, kConsumers / 4, false>();
+    return make_instance<T, D, P, 8, 1, false>();
 }
 
 template <typename T>
-static MapInstance pick_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t row_tiles) {
+static MapInstance pick_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
     KH_REQUIRE(tokens_per_page == 16, "this build instantiates 16-token pages only (got %u)", tokens_per_page);
-    if (head_dim == 128) return pick_rows<T, 128, 16>(row_tiles);
+    if (head_dim == 128) return pick_rows<T, 128, 16>(rows);
     KH_REQUIRE(head_dim == 256, "this build instantiates head_dim 128 and 256 only (got %u)", head_dim);
-    return pick_rows<T, 256, 16>(row_tiles);
+    return pick_rows<T, 256, 16>(rows);
 }
 
 static MapInstance pick_instance(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
     KH_REQUIRE(rows >= 1 && rows <= 128, "a Map task holds at most 128 (Q token, Q head) rows (got %u)", rows);
-    uint32_t row_tiles = 1;
-    while (row_tiles * 16 < rows) row_tiles *= 2;
-    if (dtype == KH_DTYPE_BFLOAT16) return pick_geometry<__nv_bfloat16>(head_dim, tokens_per_page, row_tiles);
+    if (dtype == KH_DTYPE_BFLOAT16) return pick_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows);
     KH_REQUIRE(dtype == KH_DTYPE_FLOAT16, "Q/output dtype must be Bfloat16 or Float16 on this backend");
-    return pick_geometry<__half>(head_dim, tokens_per_page, row_tiles);
+    return pick_geometry<__half>(head_dim, tokens_per_page, rows);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -231,6 +226,33 @@ struct ComputeCommon {
     kh_execution_variant variant;
     MapInstance instance;
     std::vector<PoolMap> pool_maps;
+    std::vector<PoolMap> q_maps;
+
+    // Tensor map over Q [tokens * Hq rows][head_dim], one box = the Q heads of one task for one token.
+    const CUtensorMap& q_map(kh_buffer_ref q) {
+        for (const auto& entry : q_maps) {
+            if (entry.ptr == q.ptr && entry.bytes == q.bytes) return entry.map;
+        }
+        KH_REQUIRE((reinterpret_cast<uintptr_t>(q.ptr) & 127) == 0, "q must be 128-byte aligned");
+        const uint64_t rows = q.bytes / (uint64_t(head_dim) * 2);
+        KH_REQUIRE(rows > 0 && rows <= 0x7fffffffull, "q holds an unsupported number of rows");
+        PoolMap entry{};
+        entry.ptr = q.ptr;
+        entry.bytes = q.bytes;
+        const cuuint64_t dims[2] = {head_dim, rows};
+        const cuuint64_t strides[1] = {uint64_t(head_dim) * 2};
+        const cuuint32_t box[2] = {64, variant.max_q_heads};
+        const cuuint32_t elem_strides[2] = {1, 1};
+        const CUtensorMapDataType type =
+            dtype == KH_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const CUresult rc = encode_tiled_fn()(&entry.map, type, 2, q.ptr, dims, strides, box, elem_strides,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) raise(KH_INTERNAL, "cuTensorMapEncodeTiled (q) failed with code %d", int(rc));
+        if (q_maps.size() >= 8) q_maps.erase(q_maps.begin());
+        q_maps.push_back(entry);
+        return q_maps.back().map;
+    }
 
     const CUtensorMap& pool_map(kh_buffer_ref pages) {
         for (const auto& entry : pool_maps) {
@@ -286,11 +308,12 @@ static void need(kh_buffer_ref buffer, uint64_t bytes, const char* name) {
                (unsigned long long)buffer.bytes, (unsigned long long)bytes);
 }
 
-static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buffer_ref kv_pages,
+static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buffer_ref q, kh_buffer_ref kv_pages,
                        uint32_t num_templates) {
     KH_REQUIRE(stream != nullptr && stream->device == c.device, "stream does not belong to the compute's device");
     use_device(c.device);
     const CUtensorMap& map = c.pool_map(kv_pages);
+    const CUtensorMap& qmap = c.q_map(q);
     p.status = c.device->status;
     p.num_templates = num_templates;
     p.num_q_heads = c.num_q_heads;
@@ -303,11 +326,18 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     p.pages_per_request_layer = c.layout.num_blocks * c.layout.num_page_ids_per_block;
     p.pool_pages = static_cast<uint32_t>(std::min<uint64_t>(kv_pages.bytes / c.page_bytes, 0xffffffffull));
     p.scale_log2e = c.scale * 1.4426950408889634f;
+    // Measurement aid: KH_GQA_STREAM_ONLY=1 makes the consumer warps release every K/V stage without
+    // computing, which times the paged TMA gather by itself (outputs are then meaningless).
+    static const bool stream_only = [] {
+        const char* value = std::getenv("KH_GQA_STREAM_ONLY");
+        return value != nullptr && value[0] == '1';
+    }();
+    p.stream_only = stream_only ? 1u : 0u;
     if (num_templates == 0) return;
     const uint64_t tasks = uint64_t(num_templates) * c.num_kv_heads * p.head_ranges;
     KH_REQUIRE(tasks <= 0xffffffffull, "GQA SDPA map task count must fit u32");
     const uint32_t grid = static_cast<uint32_t>(std::min<uint64_t>(tasks, uint64_t(c.device->sm_count)));
-    c.instance.kernel<<<grid, c.instance.threads, c.instance.smem_bytes, stream->stream>>>(map, p);
+    c.instance.kernel<<<grid, c.instance.threads, c.instance.smem_bytes, stream->stream>>>(map, qmap, p);
     KH_CUDA(cudaGetLastError());
 }
 
@@ -784,7 +814,6 @@ kh_status kh_sliced_kv_map(kh_sliced_kv* compute, kh_stream* stream, const kh_sl
         need(buffers->partial_max_logits, z.partial_output_stats_bytes, "partial_max_logits");
         need(buffers->partial_output, z.partial_output_bytes, "partial_output");
         MapParams p{};
-        p.q = buffers->q.ptr;
         p.req_slots = static_cast<const uint32_t*>(buffers->req_slots.ptr);
         p.page_ids = static_cast<const uint32_t*>(buffers->page_ids.ptr);
         p.visible = nullptr;
@@ -798,7 +827,7 @@ kh_status kh_sliced_kv_map(kh_sliced_kv* compute, kh_stream* stream, const kh_sl
         p.num_active_q_tiles = num_active_tokens;
         p.layer_index = page_table_index;
         p.direct = 0;
-        launch_map(compute->common, stream, p, buffers->kv_pages, num_active_kv_splits);
+        launch_map(compute->common, stream, p, buffers->q, buffers->kv_pages, num_active_kv_splits);
         return KH_OK;
     });
 }
@@ -905,7 +934,6 @@ static void sliced_q_launch(kh_sliced_q* compute, kh_stream* stream, const kh_sl
         need(partial_max, z.partial_output_stats_bytes, "partial_max_logits");
     }
     MapParams p{};
-    p.q = in.q.ptr;
     p.req_slots = static_cast<const uint32_t*>(in.req_slots.ptr);
     p.page_ids = static_cast<const uint32_t*>(in.page_ids.ptr);
     p.visible = static_cast<const uint32_t*>(in.visible_kv_token_ranges.ptr);
@@ -922,7 +950,7 @@ static void sliced_q_launch(kh_sliced_q* compute, kh_stream* stream, const kh_sl
     p.num_active_q_tiles = num_active_q_token_tiles;
     p.layer_index = page_table_index;
     p.direct = direct ? 1u : 0u;
-    launch_map(compute->common, stream, p, in.kv_pages, num_active_kv_splits);
+    launch_map(compute->common, stream, p, in.q, in.kv_pages, num_active_kv_splits);
 }
 
 kh_status kh_sliced_q_map(kh_sliced_q* compute, kh_stream* stream, const kh_sliced_q_map_buffers* buffers,

@@ -6,17 +6,23 @@
 // (crates/inference-backend-metal/src/components/metal/gqa_sdpa_sliced_kv_map.metal:36,
 //  crates/inference-backend-metal/src/components/metal/gqa_sdpa_sliced_q_map.metal:29).
 //
-// Data movement: one producer warp streams the task's K and V page chunks from the paged pool
-// into a ring of shared-memory stages with TMA tile copies (128-byte swizzle, one mbarrier per
-// stage, no multicast). A page chunk [tokens_per_page][head_dim] of one KV head is contiguous in
-// the page layout [K/V][Hkv][P][D], so it is one TMA box per 64-element column half.
-// Math: consumer warps hold all Q rows of the task -- (Q tokens of the range) x (Q heads of the KV
-// group) -- as the M dimension of warp-level tensor-core tiles, so every K/V byte is read from HBM
-// once and feeds all of them. S = Q K^T and O += P V run as m16n8k16 MMAs with f32 accumulators;
-// the online softmax keeps a running row maximum with quad shuffles. KV stages are dealt round
-// robin to KVW "KV warps" per row tile; their (m, l, O) states are merged through shared memory at
-// the end of the task and either published as an f32 partial (max, exp-sum, normalised output) or
-// written directly as the final output.
+// Data movement (producer warp). All global reads of the kernel are issued by one producer warp:
+//  - it decodes 32 upcoming tasks at a time, one per lane (template -> Q range -> request slot is a
+//    chain of dependent loads, paid once per 32 tasks),
+//  - stages each task's page ids into shared memory one task ahead (cp.async),
+//  - publishes the task descriptor and the task's Q rows (TMA tile copy, 128-byte swizzle) into a
+//    small task ring, and
+//  - streams the task's K and V page chunks from the paged pool into a ring of shared-memory stages
+//    with TMA tile copies (128-byte swizzle, one mbarrier per stage, no multicast). A page chunk
+//    [tokens_per_page][head_dim] of one KV head is contiguous in the page layout [K/V][Hkv][P][D];
+//    it is one TMA box per 64-element column half.
+// Math (consumer warps). The Q rows of a task -- (Q tokens of the range) x (Q heads of the KV group)
+// -- are the M dimension of warp-level tensor-core tiles, so every K/V byte is read from HBM once
+// and feeds all of them. S = Q K^T and O += P V run as m16n8k16 MMAs with f32 accumulators; the
+// online softmax keeps a running row maximum with quad shuffles. KV stages are dealt round robin to
+// KVW "KV warps" per 16-row tile; at the end of the task every warp writes its (m, l, O) state to
+// shared memory and all consumer threads merge and publish a slice each: either an f32 partial
+// (max, exp-sum, normalised output) or the final output.
 #pragma once
 
 #include <cuda.h>
@@ -29,7 +35,6 @@
 namespace kh {
 
 struct MapParams {
-    const void* q;                    // [T][Hq][D] io dtype
     const uint32_t* req_slots;        // [T]
     const uint32_t* page_ids;         // [slots][L][B][n]
     const uint32_t* visible;          // [T][2] request-local [begin, end) per flat Q token; null: template range
@@ -55,12 +60,14 @@ struct MapParams {
     uint32_t pool_pages;
     float scale_log2e;                // scale * log2(e)
     uint32_t direct;                  // 1: write final output, 0: write partials
+    uint32_t stream_only;             // measurement aid: consumers release every stage without computing
 };
 
 constexpr uint32_t kStatusWaitExpired = 1u;
 constexpr uint32_t kStatusPageOutOfPool = 2u;
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr int kMaxPidsPerSegment = 160;  // page ids staged per task segment (2048 tokens of 16 + slack)
+constexpr int kMaxTaskTokens = 32;       // Q tokens per task (the reference caps the tile at 32, sdpa.rs:117)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -78,6 +85,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// The barrier counts one arrival once all cp.async copies this thread issued so far have landed.
+__device__ __forceinline__ void mbar_arrive_after_cp_async(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -93,7 +105,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait. Once any wait of the CTA has run out, `abort_flag` (shared) is set, every later
-// wait returns at once and the kernel runs to its end without touching the ring again; the host
+// wait returns at once and the kernel runs to its end without touching the rings again; the host
 // reads the sticky status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status) {
@@ -162,20 +174,51 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t packed);
+
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t packed) {
+    return make_float2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xffff0000u));
+}
+
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t packed) {
+    return __half22float2(*reinterpret_cast<__half2*>(&packed));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
+template <int ID>
 __device__ __forceinline__ void consumer_barrier(int threads) {
-    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(threads) : "memory");
 }
+
+// Task descriptor as the producer publishes it to the consumers (shared memory).
+struct TaskSlot {
+    uint32_t tmpl;
+    uint32_t head_begin;   // first Q head of the task (absolute)
+    uint32_t num_heads;    // active Q heads in the task
+    uint32_t tok_begin;    // first flat Q token
+    uint32_t num_toks;     // Q tokens in the range
+    uint32_t kv_begin;
+    uint32_t kv_end;
+    uint32_t tile_begin;   // kv_begin rounded down to a stage boundary
+    uint32_t num_tiles;
+    uint32_t done;         // 1: no more tasks for this CTA
+    uint32_t pad[2];
+    uint32_t visible[2 * kMaxTaskTokens];  // per Q token [begin, end), only when MapParams::visible is set
+};
 
 // Compile-time geometry of one kernel instance.
 //   D: head dimension (128 or 256). P: tokens per page. MT: 16-row tiles of Q rows per task.
-//   KVW: KV warps per row tile. Consumer warps = MT * KVW; one extra warp produces.
-template <int D, int P, int MT, int KVW>
+//   KVW: KV warps per row tile. HALF: only rows 0-7 of the (single) row tile are ever valid.
+//   Consumer warps = MT * KVW; one extra warp produces.
+template <int D, int P, int MT, int KVW, bool HALF>
 struct MapGeometry {
     static constexpr int kStageTokens = (D == 128) ? 32 : 16;
     static constexpr int kBoxRows = (P < kStageTokens) ? P : kStageTokens;
@@ -187,51 +230,51 @@ struct MapGeometry {
     static constexpr int kBoxesPerStage = 2 * kBoxesPerPlane * kColumnHalves;
     static constexpr int kConsumerWarps = MT * KVW;
     static constexpr int kThreads = (kConsumerWarps + 1) * 32;
-    static constexpr int kQBytes = MT * 16 * D * 2;
-    static constexpr int kMergeSlotFloats = (D / 2 + 4) * 32;  // O fragment + (m, l) x 2 rows, per lane
-    static constexpr int kMergeSlots = MT * (KVW / 2);
-    static constexpr int kMergeBytes = kMergeSlots * kMergeSlotFloats * 4;
+    static constexpr int kQRows = MT * 16;
+    static constexpr int kQBytes = kQRows * D * 2;
+    static constexpr int kTaskSlots = 2;  // the producer publishes at most one task ahead of the consumers
+    static constexpr int kFragRegs = HALF ? D / 4 : D / 2;        // O accumulator registers a warp parks
+    static constexpr int kMergeSlotFloats = (kFragRegs + 4) * 32;  // O fragment + (m, l) x 2 rows, per lane
+    static constexpr int kMergeBytes = (KVW == 1) ? 0 : kConsumerWarps * kMergeSlotFloats * 4;  // one KV warp: no merge
     static constexpr int kPidBytes = 2 * kMaxPidsPerSegment * 4;
-    static constexpr int kFixedBytes = kQBytes + kMergeBytes + kPidBytes + 512 /* barriers, flags */;
+    static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
+    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 512;
     static constexpr int kSmemLimit = 227 * 1024 - 1024 /* alignment slack */;
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
-    static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
+    // A KV warp consumes the stages whose running number is congruent to its index modulo KVW. With the
+    // ring depth a multiple of KVW every ring slot is always consumed by the same warp, so a warp can
+    // never wait on a slot more than one phase ahead of the slot's barrier (phase parity cannot alias).
+    static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
+    static constexpr int kStages = kStagesCapped / KVW * KVW;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
-    static_assert(kStages >= 3, "shared memory ring too small");
+    static_assert(kStages >= 2 && kStages >= KVW, "shared memory ring too small");
     static_assert(D % 64 == 0 && (P == 8 || P == 16 || P == 32), "unsupported page geometry");
     static_assert((KVW & (KVW - 1)) == 0, "KV warps must be a power of two");
+    static_assert(!HALF || MT == 1, "half-tile mode needs a single row tile");
+    static_assert((D / 8) % KVW == 0, "output n-tiles must split evenly across KV warps");
+    static_assert(sizeof(TaskSlot) % 8 == 0, "task slots must keep the barriers 8-byte aligned");
 };
 
+// Per-lane decoded task (producer registers).
 struct TaskInfo {
-    uint32_t tmpl;
-    uint32_t kv_head;
-    uint32_t head_begin;   // first Q head of the task (absolute)
-    uint32_t num_heads;    // active Q heads in the task
-    uint32_t tok_begin;    // first flat Q token
-    uint32_t num_toks;     // Q tokens in the range
-    uint32_t kv_begin;
-    uint32_t kv_end;
-    uint32_t req_slot;
-    uint32_t tile_begin;   // kv_begin rounded down to a stage boundary
-    uint32_t num_tiles;
-    bool active;
+    uint32_t tmpl, head_begin, num_heads, tok_begin, num_toks, kv_begin, kv_end, req_slot, kv_head, active;
 };
 
 // Decodes flat task index -> template, KV head, head range, and applies the reference kernels'
 // early-return rules for padded and inactive templates (gqa_sdpa_sliced_kv_map.metal:56-58,
 // gqa_sdpa_sliced_q_map.metal:56-67).
-template <int STAGE_TOKENS>
-__device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint32_t task) {
+__device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint64_t task, uint32_t total_tasks) {
     TaskInfo t;
+    t.tmpl = t.head_begin = t.num_heads = t.tok_begin = t.num_toks = t.kv_begin = t.kv_end = t.req_slot = t.kv_head = 0;
+    t.active = 0;
+    if (task >= total_tasks) return t;
     const uint32_t cells = p.num_kv_heads * p.head_ranges;
-    t.tmpl = task / cells;
-    const uint32_t cell = task % cells;
+    t.tmpl = uint32_t(task) / cells;
+    const uint32_t cell = uint32_t(task) % cells;
     t.kv_head = cell / p.head_ranges;
     const uint32_t range = cell % p.head_ranges;
     t.head_begin = t.kv_head * p.group + range * p.heads_per_task;
     t.num_heads = min(p.heads_per_task, p.group - range * p.heads_per_task);
-    t.active = false;
-    t.tok_begin = t.num_toks = t.kv_begin = t.kv_end = t.req_slot = t.tile_begin = t.num_tiles = 0;
     const uint32_t q_range = p.templates[t.tmpl * 3];
     if (p.q_ranges == nullptr) {
         if (q_range >= p.num_active_tokens) return t;
@@ -243,68 +286,91 @@ __device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint32_t tas
         const uint32_t end = p.q_ranges[q_range * 2 + 1];
         if (begin >= p.num_active_tokens || end > p.num_active_tokens || end <= begin) return t;
         t.tok_begin = begin;
-        t.num_toks = min(end - begin, p.max_q_tokens);
+        t.num_toks = min(min(end - begin, p.max_q_tokens), uint32_t(kMaxTaskTokens));
     }
     t.kv_begin = p.templates[t.tmpl * 3 + 1];
     t.kv_end = p.templates[t.tmpl * 3 + 2];
     t.req_slot = p.req_slots[t.tok_begin];
-    t.active = true;
-    if (t.kv_end > t.kv_begin) {
-        t.tile_begin = t.kv_begin / STAGE_TOKENS * STAGE_TOKENS;
-        t.num_tiles = (t.kv_end - t.tile_begin + STAGE_TOKENS - 1) / STAGE_TOKENS;
-    }
+    t.active = 1;
     return t;
 }
 
-template <typename T, int D, int P, int MT, int KVW>
-__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW>::kThreads, 1)
-sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
-    using G = MapGeometry<D, P, MT, KVW>;
+__device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
+    TaskInfo r;
+    r.tmpl = __shfl_sync(0xffffffffu, t.tmpl, lane);
+    r.head_begin = __shfl_sync(0xffffffffu, t.head_begin, lane);
+    r.num_heads = __shfl_sync(0xffffffffu, t.num_heads, lane);
+    r.tok_begin = __shfl_sync(0xffffffffu, t.tok_begin, lane);
+    r.num_toks = __shfl_sync(0xffffffffu, t.num_toks, lane);
+    r.kv_begin = __shfl_sync(0xffffffffu, t.kv_begin, lane);
+    r.kv_end = __shfl_sync(0xffffffffu, t.kv_end, lane);
+    r.req_slot = __shfl_sync(0xffffffffu, t.req_slot, lane);
+    r.kv_head = __shfl_sync(0xffffffffu, t.kv_head, lane);
+    r.active = __shfl_sync(0xffffffffu, t.active, lane);
+    return r;
+}
+
+template <typename T, int D, int P, int MT, int KVW, bool HALF>
+__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, HALF>::kThreads, 1)
+sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
+                const MapParams p) {
+    using G = MapGeometry<D, P, MT, KVW, HALF>;
     constexpr int ST = G::kStageTokens;
     constexpr int NS = G::kStages;
+    constexpr int TQ = G::kTaskSlots;
     constexpr int NCW = G::kConsumerWarps;
     constexpr int NT = ST / 8;       // S n-tiles (8 KV tokens each) per stage
     constexpr int KT = ST / 16;      // PV k-tiles (16 KV tokens each) per stage
     constexpr int DK = D / 16;       // QK k-steps
     constexpr int DN = D / 8;        // O n-tiles
+    constexpr int NROW = HALF ? 1 : 2;  // fragment rows (g, g + 8) that can be valid
+    constexpr int NH = G::kColumnHalves;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
-    uint8_t* q_smem = ring + NS * G::kStageBytes;
-    float* merge = reinterpret_cast<float*>(q_smem + G::kQBytes);
+    uint8_t* q_ring = ring + NS * G::kStageBytes;
+    float* merge = reinterpret_cast<float*>(q_ring + TQ * G::kQBytes);
     uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS);
+    TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 2 * TQ);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t full_bar = smem_addr(bars);
     const uint32_t empty_bar = smem_addr(bars + NS);
+    const uint32_t task_full_bar = smem_addr(bars + 2 * NS);
+    const uint32_t task_empty_bar = smem_addr(bars + 2 * NS + TQ);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, MT);
         }
+        for (int s = 0; s < TQ; ++s) {
+            mbar_init(task_full_bar + 8 * s, 33);  // 32 lanes' cp.async arrivals + the expect_tx arrival
+            mbar_init(task_empty_bar + 8 * s, NCW);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // Q rows no copy ever writes (row padding of the tile) must not hold NaN bit patterns.
+    for (int i = threadIdx.x; i < TQ * G::kQBytes / 16; i += G::kThreads) {
+        reinterpret_cast<uint4*>(q_ring)[i] = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
     const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
-    const uint32_t rows_per_page_plane = P;  // rows of one (page, plane, head) chunk
 
     if (warp == NCW) {
         // ------------------------------ producer warp -----------------------------------------
         uint32_t stage_counter = 0;
-        uint32_t task = blockIdx.x;
+        uint32_t pushed = 0;  // task-ring pushes so far
         int buf = 0;
-        TaskInfo cur = task < total_tasks ? decode_task<ST>(p, task) : TaskInfo{};
-        if (task >= total_tasks) cur.active = false;
 
-        // Stages the page ids of pages [first_page, first_page + count) of a task into pid_smem[buf].
+        // Stages the page ids of pages [first_page, first_page + count) of a task into pid_smem[which].
         auto stage_pids = [&](const TaskInfo& t, uint32_t first_page, uint32_t count, int which) {
             const uint64_t base = (uint64_t(t.req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
             for (uint32_t i = lane; i < count; i += 32) {
@@ -314,40 +380,97 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        auto task_pages = [&](const TaskInfo& t, uint32_t& first_page, uint32_t& num_pages) {
-            first_page = t.tile_begin / P;
-            num_pages = t.num_tiles == 0 ? 0 : (t.kv_end + P - 1) / P - first_page;
+        auto task_tiles = [&](const TaskInfo& t, uint32_t& tile_begin, uint32_t& num_tiles) {
+            tile_begin = num_tiles = 0;
+            if (t.active && t.kv_end > t.kv_begin) {
+                tile_begin = t.kv_begin / ST * ST;
+                num_tiles = (t.kv_end - tile_begin + ST - 1) / ST;
+            }
+        };
+        auto prefetch_pids = [&](const TaskInfo& t, int which) {
+            uint32_t tile_begin, num_tiles;
+            task_tiles(t, tile_begin, num_tiles);
+            if (num_tiles == 0) return;
+            const uint32_t first_page = tile_begin / P;
+            const uint32_t num_pages = (t.kv_end + P - 1) / P - first_page;
+            stage_pids(t, first_page, min(num_pages, uint32_t(kMaxPidsPerSegment)), which);
+        };
+        // Lane l decodes this CTA's task number first_index + l.
+        auto decode_batch = [&](uint32_t first_index) {
+            return decode_task(p, blockIdx.x + (uint64_t(first_index) + lane) * gridDim.x, total_tasks);
         };
 
-        if (cur.active && cur.num_tiles > 0) {
-            uint32_t fp, np;
-            task_pages(cur, fp, np);
-            stage_pids(cur, fp, min(np, uint32_t(kMaxPidsPerSegment)), buf);
-        }
-        while (task < total_tasks) {
-            const uint32_t next_task = task + gridDim.x;
-            TaskInfo nxt{};
-            nxt.active = false;
-            if (next_task < total_tasks) nxt = decode_task<ST>(p, next_task);
-            // current task's first segment is in flight or landed; wait for it, then prefetch the next task's.
+        // Two batches of 32 decoded tasks live in registers.
+        TaskInfo batch_cur = decode_batch(0);
+        TaskInfo batch_next = decode_batch(32);
+        TaskInfo cur = shfl_task(batch_cur, 0);
+        prefetch_pids(cur, buf);
+        bool aborted = false;
+        for (uint32_t index = 0;; ++index) {
+            const uint64_t task = blockIdx.x + uint64_t(index) * gridDim.x;
+            if (task >= total_tasks) break;
+            // next task's descriptor: from the current batch, or lane 0 of the next one
+            const uint32_t next_lane = (index + 1) & 31;
+            const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
-            if (nxt.active && nxt.num_tiles > 0) {
-                uint32_t fp, np;
-                task_pages(nxt, fp, np);
-                stage_pids(nxt, fp, min(np, uint32_t(kMaxPidsPerSegment)), buf ^ 1);
+            prefetch_pids(nxt, buf ^ 1);
+
+            uint32_t tile_begin, num_tiles;
+            task_tiles(cur, tile_begin, num_tiles);
+            if (cur.active && !aborted) {
+                // ---- publish the task: descriptor, visibility rows, Q rows
+                const uint32_t slot = pushed % TQ;
+                const uint32_t phase = (pushed / TQ) & 1;
+                if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) aborted = true;
+                if (!aborted) {
+                    TaskSlot* ts = task_ring + slot;
+                    if (lane == 0) {
+                        ts->tmpl = cur.tmpl;
+                        ts->head_begin = cur.head_begin;
+                        ts->num_heads = cur.num_heads;
+                        ts->tok_begin = cur.tok_begin;
+                        ts->num_toks = cur.num_toks;
+                        ts->kv_begin = cur.kv_begin;
+                        ts->kv_end = cur.kv_end;
+                        ts->tile_begin = tile_begin;
+                        ts->num_tiles = num_tiles;
+                        ts->done = 0;
+                    }
+                    if (p.visible != nullptr) {
+                        for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
+                            const uint32_t dst = smem_addr(&ts->visible[i]);
+                            const uint32_t* src = p.visible + uint64_t(cur.tok_begin) * 2 + i;
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                        }
+                    }
+                    mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+                    const uint32_t q_boxes = cur.num_toks * NH;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
+                    }
+                    __syncwarp();
+                    for (uint32_t b = lane; b < q_boxes; b += 32) {
+                        const uint32_t tok = b / NH;
+                        const uint32_t half = b % NH;
+                        const uint32_t dst = smem_addr(q_ring + slot * G::kQBytes + half * (G::kQRows * 128) +
+                                                       tok * p.heads_per_task * 128);
+                        const uint32_t row = (cur.tok_begin + tok) * p.num_q_heads + cur.head_begin;
+                        tma_load_2d(dst, &q_map, half * 64, static_cast<int32_t>(row), task_full_bar + 8 * slot);
+                    }
+                    ++pushed;
+                }
             }
-            if (cur.active && cur.num_tiles > 0) {
-                uint32_t first_page, num_pages;
-                task_pages(cur, first_page, num_pages);
+            if (cur.active && num_tiles > 0 && !aborted) {
+                const uint32_t first_page = tile_begin / P;
+                const uint32_t num_pages = (cur.kv_end + P - 1) / P - first_page;
                 uint32_t seg_first = first_page;  // first page whose id is staged in pid_smem[buf]
                 uint32_t seg_count = min(num_pages, uint32_t(kMaxPidsPerSegment));
-                for (uint32_t tile = 0; tile < cur.num_tiles; ++tile, ++stage_counter) {
-                    const uint32_t tile_tok = cur.tile_begin + tile * ST;
+                for (uint32_t tile = 0; tile < num_tiles; ++tile, ++stage_counter) {
+                    const uint32_t tile_tok = tile_begin + tile * ST;
                     // Page span of this stage; restage ids synchronously for very long tasks.
                     const uint32_t last_page_needed = (min(tile_tok + ST, cur.kv_end) - 1) / P;
                     if (last_page_needed >= seg_first + seg_count) {
-                        // The prefetched segment of the next task shares the copy queue: drain it first.
                         asm volatile("cp.async.wait_group 0;" ::: "memory");
                         __syncwarp();
                         seg_first = tile_tok / P;
@@ -358,8 +481,10 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                     }
                     const uint32_t slot = stage_counter % NS;
                     const uint32_t phase = (stage_counter / NS) & 1;
-                    const bool ok = mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status);
-                    if (!ok) continue;
+                    if (!mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
+                        aborted = true;
+                        break;
+                    }
                     // Which boxes hold at least one token below kv_end.
                     uint32_t boxes_needed = 0;
 #pragma unroll
@@ -367,34 +492,49 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                         if (tile_tok + b * G::kBoxRows < cur.kv_end) ++boxes_needed;
                     }
                     if (lane == 0) {
-                        mbar_arrive_expect_tx(full_bar + 8 * slot, boxes_needed * 2 * G::kColumnHalves * G::kBoxBytes);
+                        mbar_arrive_expect_tx(full_bar + 8 * slot, boxes_needed * 2 * NH * G::kBoxBytes);
                     }
                     __syncwarp();
                     if (lane < G::kBoxesPerStage) {
                         // lane -> (plane, token box, column half)
-                        const int half = lane % G::kColumnHalves;
-                        const int box = (lane / G::kColumnHalves) % G::kBoxesPerPlane;
-                        const int plane = lane / (G::kColumnHalves * G::kBoxesPerPlane);
+                        const int half = lane % NH;
+                        const int box = (lane / NH) % G::kBoxesPerPlane;
+                        const int plane = lane / (NH * G::kBoxesPerPlane);
                         const uint32_t tok = tile_tok + box * G::kBoxRows;
                         if (tok < cur.kv_end) {
                             const uint32_t page_index = tok / P;
                             const uint32_t pid = pid_smem[buf * kMaxPidsPerSegment + (page_index - seg_first)];
                             if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
-                            const uint64_t row = ((uint64_t(pid) * 2 + plane) * p.num_kv_heads + cur.kv_head) *
-                                                     rows_per_page_plane + tok % P;
+                            const uint64_t row = ((uint64_t(pid) * 2 + plane) * p.num_kv_heads + cur.kv_head) * P + tok % P;
                             const uint32_t dst = smem_addr(ring + slot * G::kStageBytes + plane * G::kPlaneBytes +
-                                                           (box * G::kColumnHalves + half) * G::kBoxBytes);
+                                                           (box * NH + half) * G::kBoxBytes);
                             tma_load_2d(dst, &kv_map, half * 64, static_cast<int32_t>(row), full_bar + 8 * slot);
                         }
                     }
                 }
             }
+            // advance
             cur = nxt;
-            task = next_task;
             buf ^= 1;
+            if (next_lane == 0) {
+                batch_cur = batch_next;
+                batch_next = decode_batch(index + 1 + 32);
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        // Abort path only: copies already issued may still be landing; wait (bounded) for each stage's
+        // ---- tell the consumers there is nothing more
+        if (!aborted) {
+            const uint32_t slot = pushed % TQ;
+            const uint32_t phase = (pushed / TQ) & 1;
+            if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
+                if (lane == 0) {
+                    task_ring[slot].done = 1;
+                    mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
+                }
+                mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+            }
+        }
+        // Abort path only: copies already issued may still be landing; wait (bounded) for each ring slot's
         // last issued phase before the CTA may retire.
         if (*abort_flag) {
             for (uint32_t back = 0; back < uint32_t(NS) && back < stage_counter; ++back) {
@@ -403,58 +543,49 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                     if (mbar_try_wait(full_bar + 8 * (c % NS), (c / NS) & 1)) break;
                 }
             }
+            for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
+                const uint32_t c = pushed - 1 - back;
+                for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                    if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
+                }
+            }
         }
     } else {
         // ------------------------------ consumer warps ----------------------------------------
         const int mt = warp % MT;   // row tile
         const int kw = warp / MT;   // KV warp index within the row tile
-        const int ctid = threadIdx.x;
         const int g = lane >> 2;    // fragment row group
         const int tq = lane & 3;    // thread in quad
         uint32_t stage_counter = 0;
-        const T* q_global = reinterpret_cast<const T*>(p.q);
+        const int lm_mat = lane >> 3;  // which of the four 8x8 matrices this lane addresses in ldmatrix
+        const int lm_row = lane & 7;
 
-        for (uint32_t task = blockIdx.x; task < total_tasks; task += gridDim.x) {
-            const TaskInfo t = decode_task<ST>(p, task);
-            if (!t.active) continue;
-
-            // ---- stage Q rows: row = tok_local * heads_per_task + head_local, 16-byte chunks, XOR swizzle
-            for (int idx = ctid; idx < MT * 16 * (D / 8); idx += NCW * 32) {
-                const int row = idx / (D / 8);
-                const int chunk = idx % (D / 8);
-                const uint32_t tok_local = row / p.heads_per_task;
-                const uint32_t head_local = row % p.heads_per_task;
-                uint4 value = make_uint4(0, 0, 0, 0);
-                if (tok_local < t.num_toks && head_local < t.num_heads) {
-                    const T* src = q_global +
-                                   (uint64_t(t.tok_begin + tok_local) * p.num_q_heads + t.head_begin + head_local) * D +
-                                   chunk * 8;
-                    value = *reinterpret_cast<const uint4*>(src);
-                }
-                const int phys = (chunk & ~7) | ((chunk ^ row) & 7);
-                *reinterpret_cast<uint4*>(q_smem + row * (D * 2) + phys * 16) = value;
-            }
-            consumer_barrier(NCW * 32);
+        for (uint32_t popped = 0;; ++popped) {
+            const uint32_t tslot = popped % TQ;
+            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p.status)) break;
+            const TaskSlot* ts = task_ring + tslot;
+            if (ts->done) break;
+            const uint32_t t_tmpl = ts->tmpl, t_head_begin = ts->head_begin, t_num_heads = ts->num_heads;
+            const uint32_t t_tok_begin = ts->tok_begin, t_num_toks = ts->num_toks;
+            const uint32_t t_kv_begin = ts->kv_begin, t_kv_end = ts->kv_end;
+            const uint32_t t_tile_begin = ts->tile_begin, t_num_tiles = ts->num_tiles;
 
             // ---- per-thread row bounds: rows g and g + 8 of row tile mt
-            uint32_t lo[2], hi[2];
-            bool row_valid[2];
-            uint32_t row_tok[2], row_head[2];
+            uint32_t lo[NROW], hi[NROW];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NROW; ++i) {
                 const uint32_t row = mt * 16 + g + 8 * i;
-                row_tok[i] = row / p.heads_per_task;
-                row_head[i] = row % p.heads_per_task;
-                row_valid[i] = row_tok[i] < t.num_toks && row_head[i] < t.num_heads;
+                const uint32_t row_tok = row / p.heads_per_task;
+                const uint32_t row_head = row % p.heads_per_task;
                 lo[i] = hi[i] = 0;
-                if (row_valid[i]) {
+                if (row_tok < t_num_toks && row_head < t_num_heads) {
                     uint32_t vb = 0, ve = 0xffffffffu;
                     if (p.visible != nullptr) {
-                        vb = p.visible[(t.tok_begin + row_tok[i]) * 2];
-                        ve = p.visible[(t.tok_begin + row_tok[i]) * 2 + 1];
+                        vb = ts->visible[row_tok * 2];
+                        ve = ts->visible[row_tok * 2 + 1];
                     }
-                    lo[i] = max(vb, t.kv_begin);
-                    hi[i] = min(ve, t.kv_end);
+                    lo[i] = max(vb, t_kv_begin);
+                    hi[i] = min(ve, t_kv_end);
                     if (hi[i] < lo[i]) hi[i] = lo[i];
                 }
             }
@@ -464,32 +595,33 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
             for (int n = 0; n < DN; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
             float m_run[2] = {-INFINITY, -INFINITY};
             float l_run[2] = {0.0f, 0.0f};
+            const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * 16 * 128;
 
-            // ldmatrix lane roles
-            const int lm_mat = lane >> 3;  // which of the four 8x8 matrices this lane addresses
-            const int lm_row = lane & 7;
-            const uint32_t q_tile = smem_addr(q_smem) + mt * 16 * (D * 2);
-
-            for (uint32_t tile = kw; tile < t.num_tiles; tile += KVW) {
+            // this warp's first tile: the first whose running stage number is congruent to kw modulo KVW
+            for (uint32_t tile = (uint32_t(kw) + KVW - stage_counter % KVW) % KVW; tile < t_num_tiles; tile += KVW) {
                 const uint32_t counter = stage_counter + tile;
                 const uint32_t slot = counter % NS;
                 const uint32_t phase = (counter / NS) & 1;
-                const bool ok = mbar_wait(full_bar + 8 * slot, phase, abort_flag, p.status);
-                if (!ok) continue;
-                const uint32_t tile_tok = t.tile_begin + tile * ST;
+                if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p.status)) continue;
+                if (p.stream_only) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
+                    continue;
+                }
+                const uint32_t tile_tok = t_tile_begin + tile * ST;
                 const uint32_t k_base = smem_addr(ring + slot * G::kStageBytes);
                 const uint32_t v_base = k_base + G::kPlaneBytes;
 
                 // Rows of tokens at or past kv_end may never have been written (or loaded): clear them in V
                 // so that a zero probability times stale bits cannot produce NaN.
-                if (tile_tok + ST > t.kv_end) {
-                    const uint32_t first_bad = t.kv_end - tile_tok;
+                if (tile_tok + ST > t_kv_end) {
+                    const uint32_t first_bad = t_kv_end - tile_tok;
                     for (uint32_t idx = first_bad * (D / 8) + lane; idx < uint32_t(ST) * (D / 8); idx += 32) {
                         const uint32_t r = idx / (D / 8);
                         const uint32_t c = idx % (D / 8);
                         const uint32_t box = r / G::kBoxRows;
-                        const uint32_t addr = v_base + (box * G::kColumnHalves + c / 8) * G::kBoxBytes +
-                                              (r % G::kBoxRows) * 128 + (c % 8) * 16;
+                        const uint32_t addr = v_base + (box * NH + c / 8) * G::kBoxBytes + (r % G::kBoxRows) * 128 +
+                                              (c % 8) * 16;
                         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
@@ -505,8 +637,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                     {
                         const int row = (lm_mat & 1) * 8 + lm_row;
                         const int chunk = 2 * kk + (lm_mat >> 1);
-                        const int phys = (chunk & ~7) | ((chunk ^ row) & 7);
-                        ldmatrix_x4(a, q_tile + row * (D * 2) + phys * 16);
+                        ldmatrix_x4(a, q_tile + (chunk / 8) * (G::kQRows * 128) + row * 128 +
+                                           (((chunk & 7) ^ (row & 7)) << 4));
                     }
 #pragma unroll
                     for (int jp = 0; jp < NT / 2; ++jp) {
@@ -515,7 +647,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                         const int chunk = 2 * kk + (lm_mat & 1);                // 16-byte chunk along D
                         const int box = tok / G::kBoxRows;
                         const int r = tok % G::kBoxRows;
-                        const uint32_t addr = k_base + (box * G::kColumnHalves + chunk / 8) * G::kBoxBytes + r * 128 +
+                        const uint32_t addr = k_base + (box * NH + chunk / 8) * G::kBoxBytes + r * 128 +
                                               (((chunk & 7) ^ (r & 7)) << 4);
                         ldmatrix_x4(b, addr);
                         mma_16816<T>(s[2 * jp], a, b[0], b[1]);
@@ -524,11 +656,13 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                 }
 
                 // ---- mask, scale, running maximum
-                float tile_max[2] = {-INFINITY, -INFINITY};
+                float tile_max[NROW];
+#pragma unroll
+                for (int i = 0; i < NROW; ++i) tile_max[i] = -INFINITY;
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                    for (int e = 0; e < 2 * NROW; ++e) {
                         const int i = e >> 1;
                         const uint32_t tok = tile_tok + j * 8 + tq * 2 + (e & 1);
                         const bool visible = tok >= lo[i] && tok < hi[i];
@@ -537,9 +671,10 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                         tile_max[i] = fmaxf(tile_max[i], value);
                     }
                 }
-                float alpha[2], base[2];
+                float alpha[NROW], base[NROW];
+                bool rescale = false;
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
+                for (int i = 0; i < NROW; ++i) {
                     tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
                     tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
                     const float m_new = fmaxf(m_run[i], tile_max[i]);
@@ -547,38 +682,44 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                     // nothing has been accumulated while the running maximum is -inf: no rescale needed
                     alpha[i] = m_run[i] == -INFINITY ? 1.0f : fast_exp2(m_run[i] - base[i]);
                     m_run[i] = m_new;
+                    rescale = rescale || alpha[i] != 1.0f;
                 }
-                const bool rescale = (alpha[0] != 1.0f) || (alpha[1] != 1.0f);
                 if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
                     for (int n = 0; n < DN; ++n) {
-                        o[n][0] *= alpha[0];
-                        o[n][1] *= alpha[0];
-                        o[n][2] *= alpha[1];
-                        o[n][3] *= alpha[1];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) o[n][e] *= alpha[HALF ? 0 : (e >> 1)];
                     }
-                    l_run[0] *= alpha[0];
-                    l_run[1] *= alpha[1];
+#pragma unroll
+                    for (int i = 0; i < NROW; ++i) l_run[i] *= alpha[i];
                 }
 
-                // ---- P = exp2(S - max), packed as the A operand of P V
-                uint32_t pa[KT][4];
+                // ---- P = exp2(S - max) as the A operand of P V. A probability rounded to 8 mantissa bits
+                // would cost up to 2^-9 of |p v| per term, which short contexts turn into errors of several
+                // 1e-3; P is therefore split into a rounded part and the rounding remainder (two MMAs per V
+                // fragment), which keeps 16 bits of every probability.
+                uint32_t pa[KT][4], pb[KT][4];
 #pragma unroll
                 for (int kt = 0; kt < KT; ++kt) {
-                    float pv[2][4];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
+                        float pv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            pv[h][e] = fast_exp2(s[2 * kt + h][e] - base[e >> 1]);
+                        for (int e = 0; e < 2 * NROW; ++e) pv[e] = fast_exp2(s[2 * kt + h][e] - base[e >> 1]);
+                        l_run[0] += pv[0] + pv[1];
+                        if (!HALF) l_run[1] += pv[2] + pv[3];
+                        pa[kt][2 * h] = pack2<T>(pv[0], pv[1]);
+                        const float2 r01 = unpack2<T>(pa[kt][2 * h]);
+                        pb[kt][2 * h] = pack2<T>(pv[0] - r01.x, pv[1] - r01.y);
+                        if (HALF) {
+                            // rows 8-15 of the tile are free: they carry the remainder, so one MMA does both
+                            pa[kt][2 * h + 1] = pb[kt][2 * h];
+                        } else {
+                            pa[kt][2 * h + 1] = pack2<T>(pv[2], pv[3]);
+                            const float2 r23 = unpack2<T>(pa[kt][2 * h + 1]);
+                            pb[kt][2 * h + 1] = pack2<T>(pv[2] - r23.x, pv[3] - r23.y);
                         }
-                        l_run[0] += pv[h][0] + pv[h][1];
-                        l_run[1] += pv[h][2] + pv[h][3];
                     }
-                    pa[kt][0] = pack2<T>(pv[0][0], pv[0][1]);
-                    pa[kt][1] = pack2<T>(pv[0][2], pv[0][3]);
-                    pa[kt][2] = pack2<T>(pv[1][0], pv[1][1]);
-                    pa[kt][3] = pack2<T>(pv[1][2], pv[1][3]);
                 }
 
                 // ---- O += P V
@@ -591,99 +732,132 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const MapParams p) {
                         const int chunk = 2 * np + (lm_mat >> 1);
                         const int box = tok / G::kBoxRows;
                         const int r = tok % G::kBoxRows;
-                        const uint32_t addr = v_base + (box * G::kColumnHalves + chunk / 8) * G::kBoxBytes + r * 128 +
+                        const uint32_t addr = v_base + (box * NH + chunk / 8) * G::kBoxBytes + r * 128 +
                                               (((chunk & 7) ^ (r & 7)) << 4);
                         ldmatrix_x4_trans(b, addr);
                         mma_16816<T>(o[2 * np], pa[kt], b[0], b[1]);
                         mma_16816<T>(o[2 * np + 1], pa[kt], b[2], b[3]);
+                        if (!HALF) {
+                            mma_16816<T>(o[2 * np], pb[kt], b[0], b[1]);
+                            mma_16816<T>(o[2 * np + 1], pb[kt], b[2], b[3]);
+                        }
                     }
                 }
 
                 // ---- release the stage
-                if (tile_tok + ST > t.kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (tile_tok + ST > t_kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
             }
-            stage_counter += t.num_tiles;
+            stage_counter += t_num_tiles;
 
+            if (HALF) {
+#pragma unroll
+                for (int n = 0; n < DN; ++n) {
+                    o[n][0] += o[n][2];
+                    o[n][1] += o[n][3];
+                }
+            }
             // ---- quad-reduce the exp-sums
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NROW; ++i) {
                 l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
                 l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
             }
 
-            // ---- tree-merge the KV warps of this row tile through shared memory (fragment order)
+            // ---- every warp parks its state in shared memory (fragment order: conflict free) ...
+            constexpr int FR = G::kFragRegs;
+            float weight[KVW][NROW];
+            float inv_l[NROW], m_all[NROW], l_all[NROW];
+            if constexpr (KVW > 1) {
+                float* my_slot = merge + warp * G::kMergeSlotFloats;
+                consumer_barrier<1>(NCW * 32);  // the previous task's merge reads are finished
 #pragma unroll
-            for (int step = KVW / 2; step >= 1; step /= 2) {
-                float* slot_mem = merge + (mt * (KVW / 2) + (kw % step)) * G::kMergeSlotFloats;
-                if (kw >= step && kw < 2 * step) {
+                for (int n = 0; n < DN; ++n) {
 #pragma unroll
-                    for (int n = 0; n < DN; ++n) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) slot_mem[(n * 4 + e) * 32 + lane] = o[n][e];
-                    }
-                    slot_mem[(DN * 4 + 0) * 32 + lane] = m_run[0];
-                    slot_mem[(DN * 4 + 1) * 32 + lane] = m_run[1];
-                    slot_mem[(DN * 4 + 2) * 32 + lane] = l_run[0];
-                    slot_mem[(DN * 4 + 3) * 32 + lane] = l_run[1];
+                    for (int e = 0; e < 2 * NROW; ++e) my_slot[(n * 2 * NROW + e) * 32 + lane] = o[n][e];
                 }
-                consumer_barrier(NCW * 32);
-                if (kw < step) {
-                    float fa[2], fb[2];
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const float m_other = slot_mem[(DN * 4 + i) * 32 + lane];
-                        const float l_other = slot_mem[(DN * 4 + 2 + i) * 32 + lane];
-                        const float m_new = fmaxf(m_run[i], m_other);
-                        const float b = m_new == -INFINITY ? 0.0f : m_new;
-                        fa[i] = fast_exp2(m_run[i] - b);
-                        fb[i] = fast_exp2(m_other - b);
-                        l_run[i] = l_run[i] * fa[i] + l_other * fb[i];
-                        m_run[i] = m_new;
-                    }
-#pragma unroll
-                    for (int n = 0; n < DN; ++n) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            o[n][e] = o[n][e] * fa[e >> 1] + slot_mem[(n * 4 + e) * 32 + lane] * fb[e >> 1];
-                        }
-                    }
+                for (int i = 0; i < NROW; ++i) {
+                    my_slot[(FR + i) * 32 + lane] = m_run[i];
+                    my_slot[(FR + 2 + i) * 32 + lane] = l_run[i];
                 }
-                consumer_barrier(NCW * 32);
-            }
-            if (KVW == 1) consumer_barrier(NCW * 32);  // Q tile reuse fence when there is no merge
+                consumer_barrier<2>(NCW * 32);
 
-            // ---- publish
-            if (kw == 0) {
+                // ---- ... and each thread merges and publishes a slice: n-tiles [kw * DN / KVW, (kw + 1) * DN / KVW)
+                // of its row tile's fragment, at its own lane position.
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    if (!row_valid[i]) continue;
-                    const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
-                    const uint32_t head = t.head_begin + row_head[i];
-                    if (p.direct) {
-                        T* dst = reinterpret_cast<T*>(p.out) +
-                                 (uint64_t(t.tok_begin + row_tok[i]) * p.num_q_heads + head) * D + tq * 2;
+                for (int i = 0; i < NROW; ++i) {
+                    float m_max = -INFINITY;
 #pragma unroll
-                        for (int n = 0; n < DN; ++n) {
-                            const uint32_t packed = pack2<T>(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
-                            *reinterpret_cast<uint32_t*>(dst + n * 8) = packed;
+                    for (int k = 0; k < KVW; ++k) {
+                        m_max = fmaxf(m_max, merge[(k * MT + mt) * G::kMergeSlotFloats + (FR + i) * 32 + lane]);
+                    }
+                    const float b = m_max == -INFINITY ? 0.0f : m_max;
+                    float l_sum = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < KVW; ++k) {
+                        const float* slot_mem = merge + (k * MT + mt) * G::kMergeSlotFloats;
+                        weight[k][i] = fast_exp2(slot_mem[(FR + i) * 32 + lane] - b);
+                        l_sum += slot_mem[(FR + 2 + i) * 32 + lane] * weight[k][i];
+                    }
+                    m_all[i] = m_max;
+                    l_all[i] = l_sum;
+                    inv_l[i] = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+                }
+            } else {
+                // a single KV warp per row tile publishes straight from its registers
+#pragma unroll
+                for (int i = 0; i < NROW; ++i) {
+                    weight[0][i] = 1.0f;
+                    m_all[i] = m_run[i];
+                    l_all[i] = l_run[i];
+                    inv_l[i] = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+                }
+            }
+            constexpr int NTILES_PER_THREAD = DN / KVW;
+#pragma unroll
+            for (int i = 0; i < NROW; ++i) {
+                const uint32_t row = mt * 16 + g + 8 * i;
+                const uint32_t row_tok = row / p.heads_per_task;
+                const uint32_t row_head = row % p.heads_per_task;
+                if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
+                const uint32_t head = t_head_begin + row_head;
+                const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
+#pragma unroll
+                for (int nn = 0; nn < NTILES_PER_THREAD; ++nn) {
+                    const int n = (KVW == 1) ? nn : kw * NTILES_PER_THREAD + nn;  // compile-time index when unsplit
+                    float v0 = 0.0f, v1 = 0.0f;
+                    if constexpr (KVW > 1) {
+#pragma unroll
+                        for (int k = 0; k < KVW; ++k) {
+                            const float* slot_mem = merge + (k * MT + mt) * G::kMergeSlotFloats;
+                            v0 += weight[k][i] * slot_mem[(n * 2 * NROW + 2 * i) * 32 + lane];
+                            v1 += weight[k][i] * slot_mem[(n * 2 * NROW + 2 * i + 1) * 32 + lane];
                         }
                     } else {
-                        const uint64_t index = (uint64_t(t.tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok[i];
-                        float* dst = p.partial_out + index * D + tq * 2;
-#pragma unroll
-                        for (int n = 0; n < DN; ++n) {
-                            *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
-                        }
-                        if (tq == 0) {
-                            p.partial_sum[index] = l_run[i];
-                            // the running maximum lives in the log2 domain of scale * log2(e); publish natural log
-                            p.partial_max[index] = l_run[i] > 0.0f ? m_run[i] * 0.6931471805599453f : -INFINITY;
-                        }
+                        v0 = o[n][2 * i];
+                        v1 = o[n][2 * i + 1];
+                    }
+                    v0 *= inv_l[i];
+                    v1 *= inv_l[i];
+                    if (p.direct) {
+                        T* dst = reinterpret_cast<T*>(p.out) +
+                                 (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + n * 8 + tq * 2;
+                        *reinterpret_cast<uint32_t*>(dst) = pack2<T>(v0, v1);
+                    } else {
+                        *reinterpret_cast<float2*>(p.partial_out + index * D + n * 8 + tq * 2) = make_float2(v0, v1);
                     }
                 }
+                if (!p.direct && kw == 0 && tq == 0) {
+                    p.partial_sum[index] = l_all[i];
+                    // the running maximum lives in the log2 domain of scale * log2(e); publish natural log
+                    p.partial_max[index] = l_all[i] > 0.0f ? m_all[i] * 0.6931471805599453f : -INFINITY;
+                }
             }
+            // ---- hand the task slot (descriptor + Q rows) back to the producer
+            __syncwarp();
+            if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
         }
     }
     __syncthreads();

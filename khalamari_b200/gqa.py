@@ -1,0 +1,168 @@
+"""The GQA component seam: ``GQA.prepare`` and ``GQA.record_sdpa``
+(crates/inference-executor-metal/src/attn/gqa/backend.rs:255-286 and 438-542), limited to attention.
+
+``GQAAttention`` owns what the reference's gated / ungated GQA layer owners own for this path: the SDPA
+selector, the batch metadata buffers and the partial-state scratch
+(crates/inference-executor-metal/src/attn/gqa/scratch.rs:49-83). The caller owns Q, the KV page pool, the
+request page table and the output, as the executor does in the reference."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import abi, sdpa, sliced_kv, sliced_q
+from .batch_metadata import GQAMetadataBuffers
+from .device import Buffer, Device, Dtype, PinnedArray, Stream
+from .replay import GQAReplayBucketPolicy, GQAReplayShape
+from .request_page_table import GQAPageTableLayout
+from .selector import RequestShape, Selection, Selector, SelectorPolicy
+
+
+@dataclass(frozen=True)
+class GQACore:
+    """The fields of ``GQACore`` this path reads (crates/inference-executor-core/src/attn/gqa/core.rs:4-41)."""
+
+    head_dim: int
+    num_q_heads: int
+    num_kv_heads: int
+    scale: float
+
+    def validate(self) -> None:
+        if self.head_dim <= 0 or self.num_q_heads <= 0 or self.num_kv_heads <= 0:
+            raise abi.InvalidArgument(1, "GQA core dimensions must be positive")
+        if self.num_q_heads % self.num_kv_heads != 0:
+            raise abi.InvalidArgument(1, "GQA Q heads must be a multiple of KV heads")
+        if not self.scale > 0.0:
+            raise abi.InvalidArgument(1, "GQA scale must be positive")
+
+
+class GQAAttention:
+    def __init__(self, device: Device, core: GQACore, io_dtype: Dtype, page_bytes: int,
+                 page_table_layout: GQAPageTableLayout, max_tokens: int,
+                 policy: SelectorPolicy = SelectorPolicy.B200, selector: Selector | None = None):
+        core.validate()
+        self.device = device
+        self.core = core
+        self.io_dtype = io_dtype
+        self.page_bytes = page_bytes
+        self.layout = page_table_layout
+        elem = io_dtype.item_size()
+        self.tokens_per_page = page_bytes // (2 * core.num_kv_heads * core.head_dim * elem)
+        self.sdpa_config = sdpa.Config(io_dtype, core.num_q_heads, core.num_kv_heads, core.head_dim,
+                                       self.tokens_per_page)
+        if selector is None:
+            selector = Selector.for_lookup(self.sdpa_config, max_tokens, page_table_layout)
+            selector.set_policy(policy, device.sm_count())
+        self.selector = selector
+        limits = selector.limits()
+        self.limits = limits
+        self.metadata = GQAMetadataBuffers(device, limits.max_tokens, limits.max_map_task_templates)
+        self.policy = GQAReplayBucketPolicy(limits.max_tokens, limits.max_map_task_templates)
+        states = limits.partial_state_group_capacity * core.num_q_heads
+        self.partial_exp_sums = Buffer.new_zeroed(device, states * 4)
+        self.partial_max_logits = Buffer.new_zeroed(device, states * 4)
+        self.partial_output = Buffer.new_zeroed(device, states * core.head_dim * 4)
+        self._computes = {}
+        self.selection: Selection | None = None
+
+    # -- GQA::prepare (backend.rs:255-286) ---------------------------------------------------------
+    def prepare(self, req_slots, token_indices, cu_tokens, num_total_tokens: int | None = None,
+                stream: Stream | None = None, selection: Selection | None = None) -> GQAReplayShape:
+        num_tokens = int(cu_tokens[-1]) if len(cu_tokens) else 0
+        if num_tokens <= 0:
+            raise abi.InvalidArgument(1, "GQA replay requires active tokens")
+        if num_total_tokens is None:
+            num_total_tokens = num_tokens
+        if selection is None:
+            shapes = RequestShape.from_batch(list(token_indices), list(cu_tokens))
+            selection = self.selector.select(shapes, self.policy, num_total_tokens)
+        self.selection = selection
+        return self.metadata.update(req_slots, token_indices, cu_tokens, selection, stream)
+
+    def select_partitioned(self, variant, kv_slice, direct_output, token_indices, cu_tokens,
+                           num_total_tokens=None) -> Selection:
+        shapes = RequestShape.from_batch(list(token_indices), list(cu_tokens))
+        total = int(cu_tokens[-1]) if num_total_tokens is None else num_total_tokens
+        return self.selector.select_partitioned(variant, kv_slice, direct_output, shapes, self.policy, total)
+
+    def _sliced_kv(self, shape: GQAReplayShape, execution):
+        key = ("kv", execution, shape.num_total_tokens, shape.num_total_sdpa_map_task_templates)
+        if key not in self._computes:
+            config = sliced_kv.Config(self.core.num_q_heads, self.core.num_kv_heads, self.core.head_dim,
+                                      self.core.scale, self.page_bytes, self.layout, self.io_dtype)
+            self._computes[key] = sliced_kv.Compute(
+                self.device, config, execution,
+                sliced_kv.Shape(shape.num_total_tokens, shape.num_total_sdpa_map_task_templates))
+        return self._computes[key]
+
+    def _sliced_q(self, shape: GQAReplayShape, execution, direct: bool):
+        key = ("q", execution, direct, shape.num_total_tokens, shape.num_total_q_token_tiles,
+               shape.num_total_sdpa_map_task_templates)
+        if key not in self._computes:
+            config = sliced_q.Config(self.core.num_q_heads, self.core.num_kv_heads, self.core.head_dim,
+                                     self.core.scale, self.page_bytes, self.io_dtype, self.layout)
+            self._computes[key] = sliced_q.Compute(
+                self.device, config, execution,
+                sliced_q.Shape(shape.num_total_tokens, shape.num_total_q_token_tiles,
+                               shape.num_total_sdpa_map_task_templates), direct)
+        return self._computes[key]
+
+    # -- GQA::record_sdpa (backend.rs:438-542) -----------------------------------------------------
+    def record_sdpa(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer, output: Buffer,
+                    gqa_layer_index: int = 0) -> int:
+        """Enqueues the selected branch on ``stream`` and returns how many kernels it launched."""
+        meta = self.metadata
+        shape = meta.replay_shape()
+        execution = meta.variant()
+        if execution.kind == sdpa.MapKernelKind.SlicedKv:
+            compute = self._sliced_kv(shape, execution)
+            compute.invoke_map(stream, sliced_kv.MapBuffers(
+                q, kv_pages, meta.req_slots(), page_ids, meta.sdpa_map_task_templates(), self.partial_exp_sums,
+                self.partial_max_logits, self.partial_output), gqa_layer_index, shape.num_tokens,
+                shape.num_sdpa_map_task_templates)
+            compute.invoke_reduce(stream, sliced_kv.ReduceBuffers(
+                self.partial_exp_sums, self.partial_max_logits, self.partial_output, meta.cu_sdpa_partial_outputs(),
+                output), shape.num_tokens)
+            return 2
+        if meta.direct_output():
+            compute = self._sliced_q(shape, execution, True)
+            compute.invoke_direct(stream, sliced_q.DirectBuffers(
+                q, kv_pages, meta.req_slots(), page_ids, meta.visible_kv_token_ranges(), meta.q_token_ranges(),
+                meta.sdpa_map_task_templates(), output), gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles)
+            return 1
+        compute = self._sliced_q(shape, execution, False)
+        compute.invoke_map(stream, sliced_q.MapBuffers(
+            q, kv_pages, meta.req_slots(), page_ids, meta.visible_kv_token_ranges(), meta.q_token_ranges(),
+            meta.sdpa_map_task_templates(), self.partial_output, self.partial_exp_sums, self.partial_max_logits),
+            gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates)
+        compute.invoke_reduce(stream, sliced_q.ReduceBuffers(
+            self.partial_output, self.partial_exp_sums, self.partial_max_logits, meta.q_token_ranges(),
+            meta.cu_sdpa_partial_outputs(), output), shape.num_q_token_tiles)
+        return 2
+
+    # -- end-to-end call with host buffers -----------------------------------------------------------
+    def attend_host(self, stream: Stream, q_host: PinnedArray, out_host: PinnedArray, q_dev: Buffer, out_dev: Buffer,
+                    kv_pages: Buffer, page_ids: Buffer, req_slots, token_indices, cu_tokens,
+                    gqa_layer_index: int = 0, selection: Selection | None = None) -> tuple[int, int, int]:
+        """One attention call the way a host-side caller issues it: plan the batch, copy this step's Q and
+        metadata to the device, run attention over the resident KV pages, and copy the output back. Returns
+        (kernel launches, host->device bytes, device->host bytes). The caller synchronises ``stream``."""
+        num_tokens = int(cu_tokens[-1])
+        row = self.core.num_q_heads * self.core.head_dim * self.io_dtype.item_size()
+        self.prepare(req_slots, token_indices, cu_tokens, num_tokens, stream, selection)
+        stream.write(q_dev, 0, q_host.ptr, num_tokens * row)
+        launches = self.record_sdpa(stream, q_dev, kv_pages, page_ids, out_dev, gqa_layer_index)
+        stream.read(out_dev, 0, out_host.ptr, num_tokens * row)
+        return launches, num_tokens * row + self.metadata.upload_bytes(), num_tokens * row
+
+
+def combine_partials(device: Device, stream: Stream, num_partials: int, num_rows: int, head_dim: int,
+                     exp_sums: Buffer, max_logits: Buffer, partial_output: Buffer, out_dtype: Dtype, output: Buffer,
+                     out_exp_sums: Buffer | None = None, out_max_logits: Buffer | None = None) -> None:
+    """LSE merge of ``num_partials`` triples per row (``kh_combine_partials``): the reducer's formula
+    (docs/gqa_sdpa_selection.md:443-460) applied to partials that may come from other GPUs."""
+    null = abi.BufferRef()
+    abi.call("kh_combine_partials", device.handle, stream.handle, num_partials, num_rows, head_dim, exp_sums.ref,
+             max_logits.ref, partial_output.ref, int(out_dtype), output.ref,
+             out_exp_sums.ref if out_exp_sums else null, out_max_logits.ref if out_max_logits else null)

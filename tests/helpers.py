@@ -1,0 +1,190 @@
+"""Shared builders for the parity tests: seeded paged KV pools, block tables and the oracle's answer.
+
+RNG: ``numpy.random.default_rng(seed)`` (PCG64) standard normals, rounded to the storage dtype and upcast
+to f32 for the oracle, as the reference's tests do (sliced_kv_test.rs:171-182)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+import oracle
+
+ABS_TOL = 2.0e-3   # max-abs bound of the build contract
+REL_TOL = 1.0e-2   # max-rel bound of the build contract
+
+
+def round_to(dtype_name: str, values: np.ndarray):
+    """Returns (uint16 storage bits, f32 value of those bits)."""
+    if dtype_name == "bf16":
+        return oracle.round_bf16(values)
+    if dtype_name == "f16":
+        return oracle.round_f16(values)
+    raise ValueError(dtype_name)
+
+
+def bits_to_f32(dtype_name: str, bits: np.ndarray) -> np.ndarray:
+    if dtype_name == "bf16":
+        return oracle.bf16_bits_to_f32(bits)
+    return np.ascontiguousarray(bits, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def nan_bits(dtype_name: str) -> int:
+    return 0x7FC0 if dtype_name == "bf16" else 0x7E00
+
+
+def assert_within_contract(actual: np.ndarray, expected: np.ndarray, what: str = "") -> tuple[float, float]:
+    """Pass rule, per element: |a - b| <= 2e-3 OR |a - b| <= 1e-2 * |b|. Returns (max abs, max rel)."""
+    actual = np.asarray(actual, dtype=np.float32)
+    expected = np.asarray(expected, dtype=np.float32)
+    assert actual.shape == expected.shape, (actual.shape, expected.shape)
+    assert np.all(np.isfinite(actual)), f"{what}: non-finite output"
+    err = np.abs(actual - expected)
+    ok = (err <= ABS_TOL) | (err <= REL_TOL * np.abs(expected))
+    max_abs = float(err.max()) if err.size else 0.0
+    rel = err / np.maximum(np.abs(expected), 1e-30)
+    max_rel = float(rel[err > ABS_TOL].max()) if np.any(err > ABS_TOL) else 0.0
+    assert np.all(ok), (f"{what}: {np.count_nonzero(~ok)} of {ok.size} elements outside tolerance; "
+                        f"max abs {max_abs:.3e}, max rel beyond abs bound {max_rel:.3e}")
+    return max_abs, max_rel
+
+
+@dataclass
+class PagedCase:
+    dtype_name: str
+    num_q_heads: int
+    num_kv_heads: int
+    head_dim: int
+    tokens_per_page: int
+    scale: float
+    layout: oracle.PageTableLayout
+    layer_index: int
+    req_slots: list
+    token_indices: list          # history length per request
+    q_lens: list
+    cu_tokens: list
+    q_bits: np.ndarray           # [T, Hq, D] uint16
+    q_f32: np.ndarray            # rounded values
+    pool: np.ndarray             # uint8 bytes of the page pool
+    page_ids: np.ndarray         # uint32 flat table
+    k_f32: list = field(default_factory=list)   # per request [ctx, Hkv, D]
+    v_f32: list = field(default_factory=list)
+
+    @property
+    def page_bytes(self) -> int:
+        return 2 * self.num_kv_heads * self.tokens_per_page * self.head_dim * 2
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.cu_tokens[-1])
+
+    def contexts(self) -> list:
+        return [h + q for h, q in zip(self.token_indices, self.q_lens)]
+
+    def kv_bytes(self) -> int:
+        """Algorithmic KV bytes: every (request, kv head, visible token) K and V row counted once."""
+        return sum(self.contexts()) * 2 * self.num_kv_heads * self.head_dim * 2
+
+    def oracle_output(self, num_threads: int = 0) -> np.ndarray:
+        threads = num_threads or oracle.max_threads()
+        return oracle.projected_gqa(self.cu_tokens, self.token_indices, self.q_f32, self.k_f32, self.v_f32,
+                                    self.head_dim, self.num_q_heads, self.num_kv_heads, self.scale, threads)
+
+
+def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, head_dim: int, histories, q_lens,
+              tokens_per_page: int = 16, num_gqa_layers: int = 1, layer_index: int = 0, num_page_ids_per_block: int = 1,
+              pool_pages: int | None = None, extra_slots: int = 0, poison: bool = True, scale: float | None = None,
+              keep_f32: bool = True, q_std: float = 1.0) -> PagedCase:
+    """Builds requests with ``histories[r]`` cached tokens and ``q_lens[r]`` new tokens (already in the cache,
+    as after the page-write step), a shared pool whose pages are handed out by a seeded permutation, and an
+    unwritten pool filled with NaN bit patterns when ``poison`` (the tail of a last page must not leak)."""
+    rng = np.random.default_rng(seed)
+    num_reqs = len(histories)
+    contexts = [int(h) + int(q) for h, q in zip(histories, q_lens)]
+    pages_needed = [-(-c // tokens_per_page) for c in contexts]
+    max_pages = max(pages_needed)
+    num_blocks = -(-max_pages // num_page_ids_per_block)
+    num_slots = num_reqs + extra_slots
+    layout = oracle.PageTableLayout(num_slots, num_gqa_layers, num_blocks, num_page_ids_per_block)
+    total_pages = sum(pages_needed)
+    if pool_pages is None:
+        pool_pages = total_pages + 3
+    assert pool_pages >= total_pages
+    page_bytes = 2 * num_kv_heads * tokens_per_page * head_dim * 2
+    pool16 = np.full(pool_pages * page_bytes // 2, nan_bits(dtype_name) if poison else 0, dtype=np.uint16)
+    pool = pool16.view(np.uint8)
+    table = np.zeros(layout.num_page_ids(), dtype=np.uint32)
+    # request r lives in slot order shuffled so that slot != request index
+    slots = rng.permutation(num_slots)[:num_reqs].astype(np.uint32)
+    free_pages = rng.permutation(pool_pages).astype(np.uint32)
+    cursor = 0
+    case_k, case_v = [], []
+    for r in range(num_reqs):
+        ids = free_pages[cursor:cursor + pages_needed[r]]
+        cursor += pages_needed[r]
+        base = ((int(slots[r]) * num_gqa_layers + layer_index) * num_blocks) * num_page_ids_per_block
+        table[base:base + ids.size] = ids
+        k = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32)
+        v = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32)
+        k_bits, k_round = round_to(dtype_name, k)
+        v_bits, v_round = round_to(dtype_name, v)
+        oracle.scatter_paged(pool, table, layout, int(slots[r]), layer_index, tokens_per_page, num_kv_heads,
+                             head_dim, 2, 0, k_bits, v_bits)
+        if keep_f32:
+            case_k.append(k_round)
+            case_v.append(v_round)
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + int(q))
+    q = rng.standard_normal((cu[-1], num_q_heads, head_dim), dtype=np.float32) * np.float32(q_std)
+    q_bits, q_round = round_to(dtype_name, q)
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(head_dim))
+    return PagedCase(dtype_name, num_q_heads, num_kv_heads, head_dim, tokens_per_page, scale, layout, layer_index,
+                     slots.tolist(), [int(h) for h in histories], [int(x) for x in q_lens], cu, q_bits, q_round, pool,
+                     table, case_k, case_v)
+
+
+class DeviceCase:
+    """Uploads a ``PagedCase`` and runs it through ``GQAAttention`` (the component seam)."""
+
+    def __init__(self, device, case: PagedCase, max_tokens: int | None = None, policy=None, selector=None):
+        from khalamari_b200.device import Buffer, Dtype, Stream
+        from khalamari_b200.gqa import GQAAttention, GQACore
+        from khalamari_b200.request_page_table import GQAPageTableLayout
+        from khalamari_b200.selector import SelectorPolicy
+
+        self.case = case
+        self.device = device
+        self.dtype = Dtype.Bfloat16 if case.dtype_name == "bf16" else Dtype.Float16
+        self.layout = GQAPageTableLayout(case.layout.num_req_slots, case.layout.num_gqa_layers,
+                                         case.layout.num_blocks, case.layout.num_page_ids_per_block)
+        self.stream = Stream(device)
+        self.q = Buffer.from_slice(device, case.q_bits)
+        self.kv_pages = Buffer.from_slice(device, case.pool)
+        self.page_ids = Buffer.from_slice(device, case.page_ids)
+        row = case.num_q_heads * case.head_dim
+        self.canary = 0x4228 if case.dtype_name == "bf16" else 0x5140  # 42.0
+        self.out_rows = case.num_tokens + 2
+        self.output = Buffer.from_slice(device, np.full(self.out_rows * row, self.canary, dtype=np.uint16))
+        self.attention = GQAAttention(
+            device, GQACore(case.head_dim, case.num_q_heads, case.num_kv_heads, case.scale), self.dtype,
+            case.page_bytes, self.layout, max_tokens or max(case.num_tokens, 1),
+            policy if policy is not None else SelectorPolicy.B200, selector)
+
+    def run(self, selection=None) -> np.ndarray:
+        case = self.case
+        self.attention.prepare(case.req_slots, case.token_indices, case.cu_tokens, selection=selection)
+        self.attention.record_sdpa(self.stream, self.q, self.kv_pages, self.page_ids, self.output, case.layer_index)
+        self.stream.synchronize()
+        assert self.device.check(self.stream) == 0
+        return self.read_output()
+
+    def read_output(self) -> np.ndarray:
+        case = self.case
+        row = case.num_q_heads * case.head_dim
+        bits = self.output.read(0, self.out_rows * row, np.uint16)
+        tail = bits[case.num_tokens * row:]
+        assert np.all(tail == self.canary), "rows past the active tokens were written"
+        return bits_to_f32(case.dtype_name, bits[:case.num_tokens * row]).reshape(case.num_tokens, case.num_q_heads,
+                                                                                 case.head_dim)
