@@ -54,31 +54,69 @@ def contexts_for(spec, rank):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event (throttle) reasons of one GPU through NVML while the bench runs.
+    Reading only; nothing is set. Falls back to nvidia-smi when the NVML binding is missing."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
+    def __init__(self, uuid: str | None, index: int):
+        self.uuid = uuid
         self.index = index
-        self.samples = []
+        self.samples = []  # (time, sm_mhz, reasons bitmask)
+        self.max_mhz = None
         self.stop = threading.Event()
         self.thread = threading.Thread(target=self._run, daemon=True)
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            if uuid:
+                try:
+                    self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+                except Exception:
+                    self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
 
     def _sample(self):
+        now = time.perf_counter()
+        if self.nvml is not None:
+            try:
+                mhz = int(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+                try:
+                    mask = int(self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    mask = int(self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((now, mhz, mask))
+            except Exception:
+                pass
+            return
         try:
-            out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+            out = subprocess.run(
+                ["nvidia-smi", f"--id={self.index}",
+                 "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_power_cap", "--format=csv,noheader,nounits"],
+                capture_output=True, text=True, timeout=10).stdout
             parts = [p.strip() for p in out.strip().split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                mask = 0
+                for bit, text in zip((0x8, 0x40, 0x20, 0x4), parts[2:6]):
+                    if text.lower().startswith("active"):
+                        mask |= bit
+                self.max_mhz = int(float(parts[1]))
+                self.samples.append((now, int(float(parts[0])), mask))
         except Exception:
             pass
 
     def _run(self):
         while not self.stop.is_set():
             self._sample()
-            self.stop.wait(0.2)
+            self.stop.wait(0.01 if self.nvml is not None else 0.2)
 
     def __enter__(self):
         self.thread.start()
@@ -88,14 +126,23 @@ class ClockSampler:
         self.stop.set()
         self.thread.join(timeout=15)
 
-    def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        mhz = sorted(int(float(s[0])) for s in self.samples)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
-                "samples": len(mhz)}
+    def summary(self, begin: float, end: float):
+        """Median SM clock and the reasons seen between two perf_counter() stamps (the timed region); when
+        that window is shorter than three samples, the window is widened to all samples taken under load."""
+        window = [s for s in self.samples if begin <= s[0] <= end]
+        label = "timed region"
+        if len(window) < 3:
+            window = self.samples
+            label = "ramp + timed region + end-to-end loop"
+        if not window:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        mhz = sorted(s[1] for s in window)
+        mask = 0
+        for s in window:
+            mask |= s[2]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": [name for bit, name in self.REASONS.items() if mask & bit], "samples": len(window),
+                "window": label}
 
 
 def build_device_case(device, spec, contexts, torch, seed):
@@ -157,6 +204,9 @@ def run_ours(args):
     if args.partition >= 0:
         spec["partition"] = args.partition
         spec["label"] += f" [partition {args.partition or 'selector'}]"
+    if args.uniform_context:
+        spec["contexts"] = [args.uniform_context] * spec["batch"]
+        spec["label"] += f" [uniform context {args.uniform_context}]"
     contexts = contexts_for(spec, rank)
     q_len = spec["q_len"]
     device = Device(local)
@@ -187,6 +237,8 @@ def run_ours(args):
         step()
     torch.cuda.synchronize()
     device.check(stream)
+    props = torch.cuda.get_device_properties(local)
+    sampler = ClockSampler(str(getattr(props, "uuid", "")) or None, local)
 
     def barrier():
         if world > 1:
@@ -194,7 +246,15 @@ def run_ours(args):
 
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches = 0
-    with ClockSampler(local) as clocks:
+    sampler.__enter__()
+    if True:
+        # untimed ramp: keep the GPU under this load for about half a second so that clocks settle and the
+        # sampler sees them before the (short) timed region starts
+        ramp_end = time.perf_counter() + 0.5
+        while time.perf_counter() < ramp_end:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
         barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -220,9 +280,9 @@ def run_ours(args):
                 events[i][1].record(torch_stream)
             events[i][2].record(torch_stream)
         torch.cuda.synchronize()
-        wall = time.perf_counter() - t0
+        t1 = time.perf_counter()
         barrier()
-        clock_summary = clocks.summary()
+        timed_window = (t0, t1)
     device.check(stream)
     step_ms = [events[i][0].elapsed_time(events[i][2]) for i in range(args.steps)]
     map_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
@@ -250,6 +310,8 @@ def run_ours(args):
     e2e_s = (time.perf_counter() - t0) / e2e_steps
     checksum = float(np.abs(out_host.array.view(np.int16).astype(np.float32)).sum())
     device.check(stream)
+    sampler.__exit__(None, None, None)
+    clock_summary = sampler.summary(*timed_window)
 
     # ---- max over ranks ----------------------------------------------------------------------------
     stats = torch.tensor([ms_per_step, e2e_s * 1e3, float(np.mean(map_ms))], device="cuda", dtype=torch.float64)
@@ -380,6 +442,7 @@ def main():
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")
     parser.add_argument("--pool-pages", type=int, default=0, help="override the page pool size (profiling captures)")
     parser.add_argument("--partition", type=int, default=-1, help="override the split-KV partition (0: selector)")
+    parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")
     args = parser.parse_args()
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result is not None:

@@ -154,25 +154,28 @@ struct MapInstance {
     int stages;
 };
 
-template <typename T, int D, int P, int MT, int KVW, bool HALF>
+template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF>
 static MapInstance make_instance() {
-    using G = MapGeometry<D, P, MT, KVW, HALF>;
-    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, HALF>, G::kThreads, G::kSmemBytes, G::kStageTokens,
+    using G = MapGeometry<D, P, MT, KVW, PS, HALF>;
+    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, PS, HALF>, G::kThreads, G::kSmemBytes, G::kStageTokens,
                        G::kBoxRows, G::kStages};
 }
 
-// Consumer-warp shapes: 4 consumer warps plus the producer (5 warps, up to 255 registers per thread, one
-// consumer warp per SM sub-partition). `rows` = Q rows per task (max_q_tokens x max_q_heads); tasks of at
-// most 8 rows (decode with a group of up to 8 heads) use the half-tile instance, which skips the softmax
-// work of fragment rows 8-15 and uses them to carry the rounding remainder of the probabilities.
+// Consumer-warp shapes. `rows` = Q rows per task (max_q_tokens x max_q_heads); tasks of at most 8 rows
+// (decode with a group of up to 8 heads) use the half-tile instance, which skips the softmax work of
+// fragment rows 8-15 and uses them to carry the rounding remainder of the probabilities.
+// head_dim 128: a stage is 32 KV tokens (two pages); 8 consumer warps = KVW stage groups x 2 warps that
+// take one page each, two warps per SM sub-partition so that one warp's softmax overlaps the other's
+// MMAs. head_dim 256: a stage is 16 KV tokens (one page) and a thread carries a 16 x 256 f32 accumulator
+// (128 registers), so 4 consumer warps run with up to 255 registers each.
 template <typename T, int D, int P>
 static MapInstance pick_rows(uint32_t rows) {
-    constexpr int kConsumers = 4;
-    if (rows <= 8) return make_instance<T, D, P, 1, kConsumers, true>();
-    if (rows <= 16) return make_instance<T, D, P, 1, kConsumers, false>();
-    if (rows <= 32) return make_instance<T, D, P, 2, kConsumers / 2, false>();
-    if (rows <= 64) return make_instance<T, D, P, 4, kConsumers / 4, false>();
-    return make_instance<T, D, P, 8, 1, false>();
+    constexpr int PS = 1;
+    if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();
+    if (rows <= 16) return make_instance<T, D, P, 1, 4, PS, false>();
+    if (rows <= 32) return make_instance<T, D, P, 2, 2, PS, false>();
+    if (rows <= 64) return make_instance<T, D, P, 4, 1, PS, false>();
+    return make_instance<T, D, P, 8, 1, 1, false>();
 }
 
 template <typename T>
@@ -266,13 +269,19 @@ struct ComputeCommon {
         PoolMap entry{};
         entry.ptr = pages.ptr;
         entry.bytes = pages.bytes;
-        const cuuint64_t dims[2] = {head_dim, rows};
-        const cuuint64_t strides[1] = {uint64_t(head_dim) * 2};
-        const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(instance.box_rows)};
-        const cuuint32_t elem_strides[2] = {1, 1};
+        // Four dimensions: {64 columns, pool rows, 64-column halves of a row, K/V plane}. A copy at
+        // (0, first K row of a page chunk, 0, 0) with box {64, rows, halves, 2} brings the K chunk and, one
+        // plane stride (Hkv * P rows) further, the V chunk of the same (page, KV head). Rows are addressed
+        // through their K-plane index only, so the row extent stops one plane short of the pool's end and a
+        // page id beyond the pool falls outside it (the copy then writes zeros).
+        const uint64_t plane_rows = uint64_t(num_kv_heads) * tokens_per_page;
+        const cuuint64_t dims[4] = {64, rows - plane_rows, head_dim / 64, 2};
+        const cuuint64_t strides[3] = {uint64_t(head_dim) * 2, 128, plane_rows * head_dim * 2};
+        const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(instance.box_rows), head_dim / 64, 2};
+        const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
         const CUtensorMapDataType type =
             dtype == KH_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-        const CUresult rc = encode_tiled_fn()(&entry.map, type, 2, pages.ptr, dims, strides, box, elem_strides,
+        const CUresult rc = encode_tiled_fn()(&entry.map, type, 4, pages.ptr, dims, strides, box, elem_strides,
                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rc != CUDA_SUCCESS) raise(KH_INTERNAL, "cuTensorMapEncodeTiled failed with code %d", int(rc));
@@ -328,11 +337,11 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     p.scale_log2e = c.scale * 1.4426950408889634f;
     // Measurement aid: KH_GQA_STREAM_ONLY=1 makes the consumer warps release every K/V stage without
     // computing, which times the paged TMA gather by itself (outputs are then meaningless).
-    static const bool stream_only = [] {
+    static const uint32_t stream_only = [] {
         const char* value = std::getenv("KH_GQA_STREAM_ONLY");
-        return value != nullptr && value[0] == '1';
+        return value != nullptr ? uint32_t(std::atoi(value)) : 0u;
     }();
-    p.stream_only = stream_only ? 1u : 0u;
+    p.stream_only = stream_only;
     if (num_templates == 0) return;
     const uint64_t tasks = uint64_t(num_templates) * c.num_kv_heads * p.head_ranges;
     KH_REQUIRE(tasks <= 0xffffffffull, "GQA SDPA map task count must fit u32");

@@ -14,8 +14,10 @@
 //    small task ring, and
 //  - streams the task's K and V page chunks from the paged pool into a ring of shared-memory stages
 //    with TMA tile copies (128-byte swizzle, one mbarrier per stage, no multicast). A page chunk
-//    [tokens_per_page][head_dim] of one KV head is contiguous in the page layout [K/V][Hkv][P][D];
-//    it is one TMA box per 64-element column half.
+//    [tokens_per_page][head_dim] of one KV head is contiguous in the page layout [K/V][Hkv][P][D]; the
+//    K chunk and the V chunk of one (page, KV head) travel in ONE four-dimensional TMA copy
+//    {64 columns, page rows, column halves, K/V plane} (8 KiB at head_dim 128, 16 KiB at 256): the copy
+//    engine's cost is per instruction, so few large copies are what reaches HBM bandwidth.
 // Math (consumer warps). The Q rows of a task -- (Q tokens of the range) x (Q heads of the KV group)
 // -- are the M dimension of warp-level tensor-core tiles, so every K/V byte is read from HBM once
 // and feeds all of them. S = Q K^T and O += P V run as m16n8k16 MMAs with f32 accumulators; the
@@ -125,6 +127,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2,
+                                            int32_t c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -216,26 +226,29 @@ struct TaskSlot {
 
 // Compile-time geometry of one kernel instance.
 //   D: head dimension (128 or 256). P: tokens per page. MT: 16-row tiles of Q rows per task.
-//   KVW: KV warps per row tile. HALF: only rows 0-7 of the (single) row tile are ever valid.
-//   Consumer warps = MT * KVW; one extra warp produces.
-template <int D, int P, int MT, int KVW, bool HALF>
+//   KVW: KV warp groups per row tile (a stage goes to one group). PS: warps of a group that split one
+//   stage's tokens between them. HALF: only rows 0-7 of the (single) row tile are ever valid.
+//   Consumer warps = MT * KVW * PS; one extra warp produces.
+template <int D, int P, int MT, int KVW, int PS, bool HALF>
 struct MapGeometry {
     static constexpr int kStageTokens = (D == 128) ? 32 : 16;
     static constexpr int kBoxRows = (P < kStageTokens) ? P : kStageTokens;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;  // token boxes per stage
     static constexpr int kColumnHalves = D / 64;                      // 128-byte column groups
-    static constexpr int kBoxBytes = kBoxRows * 128;
-    static constexpr int kPlaneBytes = kStageTokens * D * 2;
-    static constexpr int kStageBytes = 2 * kPlaneBytes;
-    static constexpr int kBoxesPerStage = 2 * kBoxesPerPlane * kColumnHalves;
-    static constexpr int kConsumerWarps = MT * KVW;
+    static constexpr int kBoxBytes = kBoxRows * 128;                  // one column half of one token box
+    static constexpr int kPlaneBoxBytes = kColumnHalves * kBoxBytes;  // K (or V) rows of one token box
+    static constexpr int kCopyBytes = 2 * kPlaneBoxBytes;             // one TMA copy: K and V of one token box
+    static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;
+    static constexpr int kWarpTokens = kStageTokens / PS;            // KV tokens one warp handles per stage
+    static constexpr int kMergeParts = KVW * PS;                     // (m, l, O) states merged per row tile
+    static constexpr int kConsumerWarps = MT * KVW * PS;
     static constexpr int kThreads = (kConsumerWarps + 1) * 32;
     static constexpr int kQRows = MT * 16;
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;  // the producer publishes at most one task ahead of the consumers
     static constexpr int kFragRegs = HALF ? D / 4 : D / 2;        // O accumulator registers a warp parks
     static constexpr int kMergeSlotFloats = (kFragRegs + 4) * 32;  // O fragment + (m, l) x 2 rows, per lane
-    static constexpr int kMergeBytes = (KVW == 1) ? 0 : kConsumerWarps * kMergeSlotFloats * 4;  // one KV warp: no merge
+    static constexpr int kMergeBytes = (kMergeParts == 1) ? 0 : MT * KVW * kMergeSlotFloats * 4;  // one state: no merge
     static constexpr int kPidBytes = 2 * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
     static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 512;
@@ -251,7 +264,9 @@ struct MapGeometry {
     static_assert(D % 64 == 0 && (P == 8 || P == 16 || P == 32), "unsupported page geometry");
     static_assert((KVW & (KVW - 1)) == 0, "KV warps must be a power of two");
     static_assert(!HALF || MT == 1, "half-tile mode needs a single row tile");
-    static_assert((D / 8) % KVW == 0, "output n-tiles must split evenly across KV warps");
+    static_assert((D / 8) % kMergeParts == 0, "output n-tiles must split evenly across the merging warps");
+    static_assert(kWarpTokens % 16 == 0, "a warp handles whole 16-token MMA k-tiles");
+    static_assert(PS == 1 || PS == 2, "a stage is split between at most two warps");
     static_assert(sizeof(TaskSlot) % 8 == 0, "task slots must keep the barriers 8-byte aligned");
 };
 
@@ -310,17 +325,19 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
     return r;
 }
 
-template <typename T, int D, int P, int MT, int KVW, bool HALF>
-__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, HALF>::kThreads, 1)
+template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF>
+__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, PS, HALF>::kThreads, 1)
 sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
                 const MapParams p) {
-    using G = MapGeometry<D, P, MT, KVW, HALF>;
+    using G = MapGeometry<D, P, MT, KVW, PS, HALF>;
     constexpr int ST = G::kStageTokens;
     constexpr int NS = G::kStages;
     constexpr int TQ = G::kTaskSlots;
     constexpr int NCW = G::kConsumerWarps;
-    constexpr int NT = ST / 8;       // S n-tiles (8 KV tokens each) per stage
-    constexpr int KT = ST / 16;      // PV k-tiles (16 KV tokens each) per stage
+    constexpr int WT = G::kWarpTokens;  // KV tokens per warp per stage
+    constexpr int KP = G::kMergeParts;
+    constexpr int NT = WT / 8;       // S n-tiles (8 KV tokens each) per warp per stage
+    constexpr int KT = WT / 16;      // PV k-tiles (16 KV tokens each) per warp per stage
     constexpr int DK = D / 16;       // QK k-steps
     constexpr int DN = D / 8;        // O n-tiles
     constexpr int NROW = HALF ? 1 : 2;  // fragment rows (g, g + 8) that can be valid
@@ -346,10 +363,11 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, MT);
+            mbar_init(empty_bar + 8 * s, MT * PS);
         }
         for (int s = 0; s < TQ; ++s) {
-            mbar_init(task_full_bar + 8 * s, 33);  // 32 lanes' cp.async arrivals + the expect_tx arrival
+            // the expect_tx arrival, plus (when per-token visibility rows are staged) 32 lanes' cp.async arrivals
+            mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
             mbar_init(task_empty_bar + 8 * s, NCW);
         }
         *abort_flag = 0;
@@ -414,7 +432,6 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
-            prefetch_pids(nxt, buf ^ 1);
 
             uint32_t tile_begin, num_tiles;
             task_tiles(cur, tile_begin, num_tiles);
@@ -444,8 +461,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                             asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
                         }
                     }
-                    mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-                    const uint32_t q_boxes = cur.num_toks * NH;
+                    if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+                    const uint32_t q_boxes = p.stream_only >= 3 ? 0u : cur.num_toks * NH;
                     if (lane == 0) {
                         mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
                     }
@@ -461,6 +478,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     ++pushed;
                 }
             }
+            prefetch_pids(nxt, buf ^ 1);  // lands while this task streams
             if (cur.active && num_tiles > 0 && !aborted) {
                 const uint32_t first_page = tile_begin / P;
                 const uint32_t num_pages = (cur.kv_end + P - 1) / P - first_page;
@@ -495,20 +513,17 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         mbar_arrive_expect_tx(full_bar + 8 * slot, boxes_needed * 2 * NH * G::kBoxBytes);
                     }
                     __syncwarp();
-                    if (lane < G::kBoxesPerStage) {
-                        // lane -> (plane, token box, column half)
-                        const int half = lane % NH;
-                        const int box = (lane / NH) % G::kBoxesPerPlane;
-                        const int plane = lane / (NH * G::kBoxesPerPlane);
+                    if (lane < G::kBoxesPerPlane) {
+                        // lane -> token box: one copy brings the K rows and the V rows of the box
+                        const int box = lane;
                         const uint32_t tok = tile_tok + box * G::kBoxRows;
                         if (tok < cur.kv_end) {
                             const uint32_t page_index = tok / P;
                             const uint32_t pid = pid_smem[buf * kMaxPidsPerSegment + (page_index - seg_first)];
                             if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
-                            const uint64_t row = ((uint64_t(pid) * 2 + plane) * p.num_kv_heads + cur.kv_head) * P + tok % P;
-                            const uint32_t dst = smem_addr(ring + slot * G::kStageBytes + plane * G::kPlaneBytes +
-                                                           (box * NH + half) * G::kBoxBytes);
-                            tma_load_2d(dst, &kv_map, half * 64, static_cast<int32_t>(row), full_bar + 8 * slot);
+                            const uint64_t row = (uint64_t(pid) * 2 * p.num_kv_heads + cur.kv_head) * P + tok % P;
+                            const uint32_t dst = smem_addr(ring + slot * G::kStageBytes + box * G::kCopyBytes);
+                            tma_load_4d(dst, &kv_map, 0, static_cast<int32_t>(row), 0, 0, full_bar + 8 * slot);
                         }
                     }
                 }
@@ -531,7 +546,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     task_ring[slot].done = 1;
                     mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
                 }
-                mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+                if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
             }
         }
         // Abort path only: copies already issued may still be landing; wait (bounded) for each ring slot's
@@ -552,8 +567,10 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         }
     } else {
         // ------------------------------ consumer warps ----------------------------------------
-        const int mt = warp % MT;   // row tile
-        const int kw = warp / MT;   // KV warp index within the row tile
+        const int mt = warp % MT;           // row tile
+        const int ps = (warp / MT) % PS;    // which part of a stage's tokens
+        const int kw = warp / (MT * PS);    // KV warp group
+        const int part = kw * PS + ps;      // index among the states merged for this row tile
         const int g = lane >> 2;    // fragment row group
         const int tq = lane & 3;    // thread in quad
         uint32_t stage_counter = 0;
@@ -596,6 +613,19 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             float m_run[2] = {-INFINITY, -INFINITY};
             float l_run[2] = {0.0f, 0.0f};
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * 16 * 128;
+            // Half-tile tasks keep their Q fragments in registers for the whole task (rows 8-15 are zero).
+            uint32_t q_regs[HALF ? DK : 1][2];
+            if constexpr (HALF) {
+#pragma unroll
+                for (int kk = 0; kk < DK; ++kk) {
+                    uint32_t a[4];
+                    const int row = (lm_mat & 1) * 8 + lm_row;
+                    const int chunk = 2 * kk + (lm_mat >> 1);
+                    ldmatrix_x4(a, q_tile + (chunk / 8) * (G::kQRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+                    q_regs[kk][0] = a[0];
+                    q_regs[kk][1] = a[2];
+                }
+            }
 
             // this warp's first tile: the first whose running stage number is congruent to kw modulo KVW
             for (uint32_t tile = (uint32_t(kw) + KVW - stage_counter % KVW) % KVW; tile < t_num_tiles; tile += KVW) {
@@ -608,20 +638,27 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
                     continue;
                 }
-                const uint32_t tile_tok = t_tile_begin + tile * ST;
+                const uint32_t tile_tok = t_tile_begin + tile * ST + ps * WT;  // first token this warp handles
+                if (PS > 1 && tile_tok >= t_kv_end) {
+                    // the tokens of this warp's part of the stage are all past the end: nothing to add
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
+                    continue;
+                }
+                // stage layout: per token box [K: halves x rows x 128 B][V: halves x rows x 128 B]
                 const uint32_t k_base = smem_addr(ring + slot * G::kStageBytes);
-                const uint32_t v_base = k_base + G::kPlaneBytes;
+                const uint32_t v_base = k_base + G::kPlaneBoxBytes;
 
                 // Rows of tokens at or past kv_end may never have been written (or loaded): clear them in V
                 // so that a zero probability times stale bits cannot produce NaN.
-                if (tile_tok + ST > t_kv_end) {
-                    const uint32_t first_bad = t_kv_end - tile_tok;
-                    for (uint32_t idx = first_bad * (D / 8) + lane; idx < uint32_t(ST) * (D / 8); idx += 32) {
-                        const uint32_t r = idx / (D / 8);
+                if (tile_tok + WT > t_kv_end) {
+                    const uint32_t first_bad = t_kv_end - tile_tok;  // within this warp's tokens
+                    for (uint32_t idx = first_bad * (D / 8) + lane; idx < uint32_t(WT) * (D / 8); idx += 32) {
+                        const uint32_t r = ps * WT + idx / (D / 8);  // token row within the stage
                         const uint32_t c = idx % (D / 8);
                         const uint32_t box = r / G::kBoxRows;
-                        const uint32_t addr = v_base + (box * NH + c / 8) * G::kBoxBytes + (r % G::kBoxRows) * 128 +
-                                              (c % 8) * 16;
+                        const uint32_t addr = v_base + box * G::kCopyBytes + (c / 8) * G::kBoxBytes +
+                                              (r % G::kBoxRows) * 128 + (c % 8) * 16;
                         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
@@ -634,7 +671,12 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
                     uint32_t a[4];
-                    {
+                    if constexpr (HALF) {
+                        a[0] = q_regs[kk][0];
+                        a[1] = 0u;
+                        a[2] = q_regs[kk][1];
+                        a[3] = 0u;
+                    } else {
                         const int row = (lm_mat & 1) * 8 + lm_row;
                         const int chunk = 2 * kk + (lm_mat >> 1);
                         ldmatrix_x4(a, q_tile + (chunk / 8) * (G::kQRows * 128) + row * 128 +
@@ -643,11 +685,11 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 #pragma unroll
                     for (int jp = 0; jp < NT / 2; ++jp) {
                         uint32_t b[4];
-                        const int tok = (2 * jp + (lm_mat >> 1)) * 8 + lm_row;  // token within stage
+                        const int tok = ps * WT + (2 * jp + (lm_mat >> 1)) * 8 + lm_row;  // token within stage
                         const int chunk = 2 * kk + (lm_mat & 1);                // 16-byte chunk along D
                         const int box = tok / G::kBoxRows;
                         const int r = tok % G::kBoxRows;
-                        const uint32_t addr = k_base + (box * NH + chunk / 8) * G::kBoxBytes + r * 128 +
+                        const uint32_t addr = k_base + box * G::kCopyBytes + (chunk / 8) * G::kBoxBytes + r * 128 +
                                               (((chunk & 7) ^ (r & 7)) << 4);
                         ldmatrix_x4(b, addr);
                         mma_16816<T>(s[2 * jp], a, b[0], b[1]);
@@ -728,11 +770,11 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 #pragma unroll
                     for (int np = 0; np < DN / 2; ++np) {
                         uint32_t b[4];
-                        const int tok = kt * 16 + (lm_mat & 1) * 8 + lm_row;
+                        const int tok = ps * WT + kt * 16 + (lm_mat & 1) * 8 + lm_row;
                         const int chunk = 2 * np + (lm_mat >> 1);
                         const int box = tok / G::kBoxRows;
                         const int r = tok % G::kBoxRows;
-                        const uint32_t addr = v_base + (box * NH + chunk / 8) * G::kBoxBytes + r * 128 +
+                        const uint32_t addr = v_base + box * G::kCopyBytes + (chunk / 8) * G::kBoxBytes + r * 128 +
                                               (((chunk & 7) ^ (r & 7)) << 4);
                         ldmatrix_x4_trans(b, addr);
                         mma_16816<T>(o[2 * np], pa[kt], b[0], b[1]);
@@ -745,12 +787,17 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 }
 
                 // ---- release the stage
-                if (tile_tok + ST > t_kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (tile_tok + WT > t_kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
             }
             stage_counter += t_num_tiles;
 
+            if (p.stream_only >= 2) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+                continue;
+            }
             if (HALF) {
 #pragma unroll
                 for (int n = 0; n < DN; ++n) {
@@ -765,26 +812,56 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
             }
 
-            // ---- every warp parks its state in shared memory (fragment order: conflict free) ...
+            // ---- the warps park their states in shared memory (fragment order: conflict free) ...
             constexpr int FR = G::kFragRegs;
             float weight[KVW][NROW];
             float inv_l[NROW], m_all[NROW], l_all[NROW];
-            if constexpr (KVW > 1) {
-                float* my_slot = merge + warp * G::kMergeSlotFloats;
+            if constexpr (KP > 1) {
+                // one slot per (KV warp group, row tile); with two warps per group the second parks first and
+                // the first folds it into its own state before parking, which halves the buffer
+                float* my_slot = merge + (kw * MT + mt) * G::kMergeSlotFloats;
+                auto park = [&]() {
+#pragma unroll
+                    for (int n = 0; n < DN; ++n) {
+#pragma unroll
+                        for (int e = 0; e < 2 * NROW; ++e) my_slot[(n * 2 * NROW + e) * 32 + lane] = o[n][e];
+                    }
+#pragma unroll
+                    for (int i = 0; i < NROW; ++i) {
+                        my_slot[(FR + i) * 32 + lane] = m_run[i];
+                        my_slot[(FR + 2 + i) * 32 + lane] = l_run[i];
+                    }
+                };
                 consumer_barrier<1>(NCW * 32);  // the previous task's merge reads are finished
+                if (PS == 1 || ps == 1) park();
+                if constexpr (PS == 2) {
+                    consumer_barrier<3>(NCW * 32);
+                    if (ps == 0) {
+                        float fa[NROW], fb[NROW];
 #pragma unroll
-                for (int n = 0; n < DN; ++n) {
+                        for (int i = 0; i < NROW; ++i) {
+                            const float m_other = my_slot[(FR + i) * 32 + lane];
+                            const float l_other = my_slot[(FR + 2 + i) * 32 + lane];
+                            const float m_new = fmaxf(m_run[i], m_other);
+                            const float b = m_new == -INFINITY ? 0.0f : m_new;
+                            fa[i] = fast_exp2(m_run[i] - b);
+                            fb[i] = fast_exp2(m_other - b);
+                            l_run[i] = l_run[i] * fa[i] + l_other * fb[i];
+                            m_run[i] = m_new;
+                        }
 #pragma unroll
-                    for (int e = 0; e < 2 * NROW; ++e) my_slot[(n * 2 * NROW + e) * 32 + lane] = o[n][e];
-                }
+                        for (int n = 0; n < DN; ++n) {
 #pragma unroll
-                for (int i = 0; i < NROW; ++i) {
-                    my_slot[(FR + i) * 32 + lane] = m_run[i];
-                    my_slot[(FR + 2 + i) * 32 + lane] = l_run[i];
+                            for (int e = 0; e < 2 * NROW; ++e) {
+                                o[n][e] = o[n][e] * fa[e >> 1] + my_slot[(n * 2 * NROW + e) * 32 + lane] * fb[e >> 1];
+                            }
+                        }
+                        park();
+                    }
                 }
                 consumer_barrier<2>(NCW * 32);
 
-                // ---- ... and each thread merges and publishes a slice: n-tiles [kw * DN / KVW, (kw + 1) * DN / KVW)
+                // ---- ... and each thread merges and publishes a slice: n-tiles [part * DN / KP, (part + 1) * DN / KP)
                 // of its row tile's fragment, at its own lane position.
 #pragma unroll
                 for (int i = 0; i < NROW; ++i) {
@@ -815,7 +892,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     inv_l[i] = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
                 }
             }
-            constexpr int NTILES_PER_THREAD = DN / KVW;
+            constexpr int NTILES_PER_THREAD = DN / KP;
 #pragma unroll
             for (int i = 0; i < NROW; ++i) {
                 const uint32_t row = mt * 16 + g + 8 * i;
@@ -826,9 +903,9 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
 #pragma unroll
                 for (int nn = 0; nn < NTILES_PER_THREAD; ++nn) {
-                    const int n = (KVW == 1) ? nn : kw * NTILES_PER_THREAD + nn;  // compile-time index when unsplit
+                    const int n = (KP == 1) ? nn : part * NTILES_PER_THREAD + nn;  // compile-time index when unsplit
                     float v0 = 0.0f, v1 = 0.0f;
-                    if constexpr (KVW > 1) {
+                    if constexpr (KP > 1) {
 #pragma unroll
                         for (int k = 0; k < KVW; ++k) {
                             const float* slot_mem = merge + (k * MT + mt) * G::kMergeSlotFloats;
@@ -849,7 +926,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         *reinterpret_cast<float2*>(p.partial_out + index * D + n * 8 + tq * 2) = make_float2(v0, v1);
                     }
                 }
-                if (!p.direct && kw == 0 && tq == 0) {
+                if (!p.direct && part == 0 && tq == 0) {
                     p.partial_sum[index] = l_all[i];
                     // the running maximum lives in the log2 domain of scale * log2(e); publish natural log
                     p.partial_max[index] = l_all[i] > 0.0f ? m_all[i] * 0.6931471805599453f : -INFINITY;
