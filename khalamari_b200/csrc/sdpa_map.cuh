@@ -111,6 +111,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // reads the sticky status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;  // common case: no shared-memory flag read on the way
     if (*abort_flag) return false;
     for (uint32_t i = 0; i < kWaitLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -267,6 +268,7 @@ struct MapGeometry {
     static_assert((D / 8) % kMergeParts == 0, "output n-tiles must split evenly across the merging warps");
     static_assert(kWarpTokens % 16 == 0, "a warp handles whole 16-token MMA k-tiles");
     static_assert(PS == 1 || PS == 2, "a stage is split between at most two warps");
+    static_assert(kStageTokens % P == 0, "a stage holds whole pages");
     static_assert(sizeof(TaskSlot) % 8 == 0, "task slots must keep the barriers 8-byte aligned");
 };
 
@@ -462,7 +464,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         }
                     }
                     if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-                    const uint32_t q_boxes = p.stream_only >= 3 ? 0u : cur.num_toks * NH;
+                    const uint32_t q_boxes = (p.stream_only == 3) ? 0u : cur.num_toks * NH;
                     if (lane == 0) {
                         mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
                     }
@@ -480,51 +482,85 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             }
             prefetch_pids(nxt, buf ^ 1);  // lands while this task streams
             if (cur.active && num_tiles > 0 && !aborted) {
+                // The tiles are streamed one page-id segment at a time. A segment's ids are staged by the whole
+                // warp (the first segment was prefetched during the previous task); the per-stage loop then runs
+                // in lane 0 alone, with running slot / phase / token counters and 32-bit row arithmetic, because
+                // this loop is the one instruction stream that has to keep the copy engine fed.
+                constexpr uint32_t kTilesPerSegment = uint32_t(kMaxPidsPerSegment) * P / ST;
                 const uint32_t first_page = tile_begin / P;
                 const uint32_t num_pages = (cur.kv_end + P - 1) / P - first_page;
-                uint32_t seg_first = first_page;  // first page whose id is staged in pid_smem[buf]
-                uint32_t seg_count = min(num_pages, uint32_t(kMaxPidsPerSegment));
-                for (uint32_t tile = 0; tile < num_tiles; ++tile, ++stage_counter) {
-                    const uint32_t tile_tok = tile_begin + tile * ST;
-                    // Page span of this stage; restage ids synchronously for very long tasks.
-                    const uint32_t last_page_needed = (min(tile_tok + ST, cur.kv_end) - 1) / P;
-                    if (last_page_needed >= seg_first + seg_count) {
+                const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
+                const uint32_t head_row = cur.kv_head * P;
+                const uint32_t* pids = pid_smem + buf * kMaxPidsPerSegment;
+                for (uint32_t seg_tile = 0; seg_tile < num_tiles && !aborted; seg_tile += kTilesPerSegment) {
+                    const uint32_t seg_first = first_page + seg_tile * (ST / P);
+                    if (seg_tile > 0) {
                         asm volatile("cp.async.wait_group 0;" ::: "memory");
                         __syncwarp();
-                        seg_first = tile_tok / P;
-                        seg_count = min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment));
-                        stage_pids(cur, seg_first, seg_count, buf);
+                        stage_pids(cur, seg_first, min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment)), buf);
                         asm volatile("cp.async.wait_group 0;" ::: "memory");
                         __syncwarp();
                     }
-                    const uint32_t slot = stage_counter % NS;
-                    const uint32_t phase = (stage_counter / NS) & 1;
-                    if (!mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
-                        aborted = true;
-                        break;
-                    }
-                    // Which boxes hold at least one token below kv_end.
-                    uint32_t boxes_needed = 0;
-#pragma unroll
-                    for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                        if (tile_tok + b * G::kBoxRows < cur.kv_end) ++boxes_needed;
-                    }
+                    const uint32_t seg_tiles = min(num_tiles - seg_tile, kTilesPerSegment);
+                    uint32_t failed = 0;
                     if (lane == 0) {
-                        mbar_arrive_expect_tx(full_bar + 8 * slot, boxes_needed * 2 * NH * G::kBoxBytes);
-                    }
-                    __syncwarp();
-                    if (lane < G::kBoxesPerPlane) {
-                        // lane -> token box: one copy brings the K rows and the V rows of the box
-                        const int box = lane;
-                        const uint32_t tok = tile_tok + box * G::kBoxRows;
-                        if (tok < cur.kv_end) {
-                            const uint32_t page_index = tok / P;
-                            const uint32_t pid = pid_smem[buf * kMaxPidsPerSegment + (page_index - seg_first)];
-                            if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
-                            const uint64_t row = (uint64_t(pid) * 2 * p.num_kv_heads + cur.kv_head) * P + tok % P;
-                            const uint32_t dst = smem_addr(ring + slot * G::kStageBytes + box * G::kCopyBytes);
-                            tma_load_4d(dst, &kv_map, 0, static_cast<int32_t>(row), 0, 0, full_bar + 8 * slot);
+                        uint32_t slot = stage_counter % NS;
+                        uint32_t parity = ((stage_counter / NS) & 1) ^ 1;
+                        uint32_t tile_tok = tile_begin + seg_tile * ST;
+                        uint32_t page_in_seg = 0;
+                        for (uint32_t tile = 0; tile < seg_tiles; ++tile) {
+                            const uint32_t bar = full_bar + 8 * slot;
+                            if (!mbar_wait(empty_bar + 8 * slot, parity, abort_flag, p.status)) {
+                                failed = tile + 1;
+                                break;
+                            }
+                            const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
+                            if (tile_tok + ST <= cur.kv_end && p.stream_only < 4) {
+                                mbar_arrive_expect_tx(bar, G::kStageBytes);
+#pragma unroll
+                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                    const uint32_t tok_in_page = (b * G::kBoxRows) % P;
+                                    const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
+                                    if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                    tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
+                                                static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar);
+                                }
+                            } else {
+                                // the task's last stage (or the measurement mode without copies): only boxes that hold
+                                // a token below kv_end are fetched
+                                uint32_t boxes_needed = 0;
+#pragma unroll
+                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                    if (tile_tok + b * G::kBoxRows < cur.kv_end) ++boxes_needed;
+                                }
+                                if (p.stream_only >= 4) boxes_needed = 0;
+                                mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
+#pragma unroll
+                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                    if (uint32_t(b) < boxes_needed) {
+                                        const uint32_t tok_in_page = (b * G::kBoxRows) % P;
+                                        const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
+                                        if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                        tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
+                                                    static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0,
+                                                    bar);
+                                    }
+                                }
+                            }
+                            tile_tok += ST;
+                            page_in_seg += ST / P;
+                            if (++slot == NS) {
+                                slot = 0;
+                                parity ^= 1;
+                            }
                         }
+                    }
+                    failed = __shfl_sync(0xffffffffu, failed, 0);
+                    if (failed) {
+                        aborted = true;
+                        stage_counter += failed - 1;
+                    } else {
+                        stage_counter += seg_tiles;
                     }
                 }
             }
@@ -574,8 +610,19 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         const int g = lane >> 2;    // fragment row group
         const int tq = lane & 3;    // thread in quad
         uint32_t stage_counter = 0;
+        uint32_t my_stage = kw, my_slot = kw, my_parity = 0;
         const int lm_mat = lane >> 3;  // which of the four 8x8 matrices this lane addresses in ldmatrix
         const int lm_row = lane & 7;
+        // ldmatrix lane roles. K (B operand, rows = KV tokens): matrix pair (lm_mat >> 1) picks the 8-token
+        // group, (lm_mat & 1) the 16-byte chunk. V (transposed) and Q (A operand): (lm_mat & 1) picks the
+        // 8-row group, (lm_mat >> 1) the chunk. Rows are taken relative to a 16-token group / 16-row tile.
+        static_assert(G::kBoxRows % 8 == 0 && 16 % G::kBoxRows == 0 || G::kBoxRows == 16, "box rows must tile 16 tokens");
+        const uint32_t k_row = (lm_mat >> 1) * 8 + lm_row;
+        const uint32_t v_row = (lm_mat & 1) * 8 + lm_row;
+        const uint32_t k_lane = (k_row / G::kBoxRows) * G::kCopyBytes + (k_row % G::kBoxRows) * 128;
+        const uint32_t v_lane = (v_row / G::kBoxRows) * G::kCopyBytes + (v_row % G::kBoxRows) * 128;
+        const uint32_t k_xor = (lm_mat & 1) ^ (k_row & 7);
+        const uint32_t v_xor = (lm_mat >> 1) ^ (v_row & 7);
 
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
@@ -594,7 +641,10 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 const uint32_t row = mt * 16 + g + 8 * i;
                 const uint32_t row_tok = row / p.heads_per_task;
                 const uint32_t row_head = row % p.heads_per_task;
-                lo[i] = hi[i] = 0;
+                // rows that hold no (token, head) of this task are never published; leaving them unmasked keeps
+                // the mask test below false for tiles that every real row sees completely
+                lo[i] = 0;
+                hi[i] = 0xffffffffu;
                 if (row_tok < t_num_toks && row_head < t_num_heads) {
                     uint32_t vb = 0, ve = 0xffffffffu;
                     if (p.visible != nullptr) {
@@ -613,27 +663,34 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             float m_run[2] = {-INFINITY, -INFINITY};
             float l_run[2] = {0.0f, 0.0f};
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * 16 * 128;
+            uint32_t q_addr[4];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) q_addr[c4] = q_tile + v_row * 128 + (((2 * c4) ^ v_xor) << 4);
             // Half-tile tasks keep their Q fragments in registers for the whole task (rows 8-15 are zero).
             uint32_t q_regs[HALF ? DK : 1][2];
             if constexpr (HALF) {
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
                     uint32_t a[4];
-                    const int row = (lm_mat & 1) * 8 + lm_row;
-                    const int chunk = 2 * kk + (lm_mat >> 1);
-                    ldmatrix_x4(a, q_tile + (chunk / 8) * (G::kQRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+                    ldmatrix_x4(a, q_addr[kk & 3] + ((2 * kk) / 8) * (G::kQRows * 128));
                     q_regs[kk][0] = a[0];
                     q_regs[kk][1] = a[2];
                 }
             }
 
-            // this warp's first tile: the first whose running stage number is congruent to kw modulo KVW
-            for (uint32_t tile = (uint32_t(kw) + KVW - stage_counter % KVW) % KVW; tile < t_num_tiles; tile += KVW) {
-                const uint32_t counter = stage_counter + tile;
-                const uint32_t slot = counter % NS;
-                const uint32_t phase = (counter / NS) & 1;
+            // This warp consumes the stages whose running number is congruent to kw modulo KVW, across tasks:
+            // my_stage is the next one, my_slot / my_parity its ring slot and barrier parity.
+            for (; my_stage < stage_counter + t_num_tiles; my_stage += KVW) {
+                const uint32_t tile = my_stage - stage_counter;
+                const uint32_t slot = my_slot;
+                const uint32_t phase = my_parity;
+                my_slot += KVW;
+                if (my_slot >= uint32_t(NS)) {
+                    my_slot -= NS;
+                    my_parity ^= 1;
+                }
                 if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p.status)) continue;
-                if (p.stream_only) {
+                if (p.stream_only && p.stream_only < 4) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
                     continue;
@@ -664,10 +721,22 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     __syncwarp();
                 }
 
-                // ---- S = Q K^T
+                // ---- S = Q K^T (raw dot products; the softmax scale is folded into the exponent below)
+                // Swizzled ldmatrix addresses: a 16-byte chunk c of row r sits at chunk (c ^ (r & 7)) of its
+                // 128-byte line. With c = 2 * step + bit, (c & 7) ^ (r & 7) = ((2 * step) & 7) ^ (bit ^ (r & 7)),
+                // so four per-lane bases (one per value of (2 * step) & 7) plus compile-time offsets cover
+                // every load of the tile.
+                uint32_t k_addr[4], v_addr[4];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    k_addr[c4] = k_base + k_lane + (((2 * c4) ^ k_xor) << 4);
+                    v_addr[c4] = v_base + v_lane + (((2 * c4) ^ v_xor) << 4);
+                }
                 float s[NT][4];
 #pragma unroll
                 for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+                const uint32_t knock = p.stream_only >= 4 ? p.stream_only - 4 : 0u;  // measurement aid
+                if (!(knock & 1))
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
                     uint32_t a[4];
@@ -677,52 +746,55 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         a[2] = q_regs[kk][1];
                         a[3] = 0u;
                     } else {
-                        const int row = (lm_mat & 1) * 8 + lm_row;
-                        const int chunk = 2 * kk + (lm_mat >> 1);
-                        ldmatrix_x4(a, q_tile + (chunk / 8) * (G::kQRows * 128) + row * 128 +
-                                           (((chunk & 7) ^ (row & 7)) << 4));
+                        ldmatrix_x4(a, q_addr[kk & 3] + ((2 * kk) / 8) * (G::kQRows * 128));
                     }
 #pragma unroll
                     for (int jp = 0; jp < NT / 2; ++jp) {
                         uint32_t b[4];
-                        const int tok = ps * WT + (2 * jp + (lm_mat >> 1)) * 8 + lm_row;  // token within stage
-                        const int chunk = 2 * kk + (lm_mat & 1);                // 16-byte chunk along D
-                        const int box = tok / G::kBoxRows;
-                        const int r = tok % G::kBoxRows;
-                        const uint32_t addr = k_base + box * G::kCopyBytes + (chunk / 8) * G::kBoxBytes + r * 128 +
-                                              (((chunk & 7) ^ (r & 7)) << 4);
-                        ldmatrix_x4(b, addr);
+                        ldmatrix_x4(b, k_addr[kk & 3] + ((2 * kk) / 8) * G::kBoxBytes +
+                                           ((ps * WT + 16 * jp) / G::kBoxRows) * G::kCopyBytes);
                         mma_16816<T>(s[2 * jp], a, b[0], b[1]);
                         mma_16816<T>(s[2 * jp + 1], a, b[2], b[3]);
                     }
                 }
 
-                // ---- mask, scale, running maximum
-                float tile_max[NROW];
+                // ---- mask (only where a row's visible range cuts the tile) and running maximum
+                if (knock & 2) {
+                    // skip the softmax: feed the raw scores through
 #pragma unroll
-                for (int i = 0; i < NROW; ++i) tile_max[i] = -INFINITY;
+                    for (int j = 0; j < NT; ++j) { s[j][0] *= 1e-9f; s[j][1] *= 1e-9f; }
+                }
+                bool cut = false;
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
+                for (int i = 0; i < NROW; ++i) cut = cut || tile_tok < lo[i] || tile_tok + WT > hi[i];
+                if (__any_sync(0xffffffffu, cut)) {
 #pragma unroll
-                    for (int e = 0; e < 2 * NROW; ++e) {
-                        const int i = e >> 1;
-                        const uint32_t tok = tile_tok + j * 8 + tq * 2 + (e & 1);
-                        const bool visible = tok >= lo[i] && tok < hi[i];
-                        const float value = visible ? s[j][e] * p.scale_log2e : -INFINITY;
-                        s[j][e] = value;
-                        tile_max[i] = fmaxf(tile_max[i], value);
+                    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 2 * NROW; ++e) {
+                            const uint32_t tok = tile_tok + j * 8 + tq * 2 + (e & 1);
+                            if (!(tok >= lo[e >> 1] && tok < hi[e >> 1])) s[j][e] = -INFINITY;
+                        }
                     }
                 }
-                float alpha[NROW], base[NROW];
+                float tile_max[NROW];
+#pragma unroll
+                for (int i = 0; i < NROW; ++i) {
+                    tile_max[i] = fmaxf(s[0][2 * i], s[0][2 * i + 1]);
+#pragma unroll
+                    for (int j = 1; j < NT; ++j) tile_max[i] = fmaxf(tile_max[i], fmaxf(s[j][2 * i], s[j][2 * i + 1]));
+                }
+                float alpha[NROW], shift[NROW];
                 bool rescale = false;
 #pragma unroll
                 for (int i = 0; i < NROW; ++i) {
                     tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
                     tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
                     const float m_new = fmaxf(m_run[i], tile_max[i]);
-                    base[i] = m_new == -INFINITY ? 0.0f : m_new;
+                    const float base = m_new == -INFINITY ? 0.0f : m_new;
                     // nothing has been accumulated while the running maximum is -inf: no rescale needed
-                    alpha[i] = m_run[i] == -INFINITY ? 1.0f : fast_exp2(m_run[i] - base[i]);
+                    alpha[i] = m_run[i] == -INFINITY ? 1.0f : fast_exp2((m_run[i] - base) * p.scale_log2e);
+                    shift[i] = -base * p.scale_log2e;
                     m_run[i] = m_new;
                     rescale = rescale || alpha[i] != 1.0f;
                 }
@@ -736,10 +808,11 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     for (int i = 0; i < NROW; ++i) l_run[i] *= alpha[i];
                 }
 
-                // ---- P = exp2(S - max) as the A operand of P V. A probability rounded to 8 mantissa bits
-                // would cost up to 2^-9 of |p v| per term, which short contexts turn into errors of several
-                // 1e-3; P is therefore split into a rounded part and the rounding remainder (two MMAs per V
-                // fragment), which keeps 16 bits of every probability.
+                // ---- P = exp2(scale * log2(e) * (S - max)) as the A operand of P V. A probability rounded to 8
+                // mantissa bits would cost up to 2^-9 of |p v| per term, which short contexts turn into errors
+                // of several 1e-3; P is therefore split into a rounded part and the rounding remainder, which
+                // keeps 16 bits of every probability. Half-tile tasks carry the remainder in the idle fragment
+                // rows 8-15 (one MMA does both); full tiles issue a second MMA per V fragment.
                 uint32_t pa[KT][4], pb[KT][4];
 #pragma unroll
                 for (int kt = 0; kt < KT; ++kt) {
@@ -747,14 +820,15 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     for (int h = 0; h < 2; ++h) {
                         float pv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                        for (int e = 0; e < 2 * NROW; ++e) pv[e] = fast_exp2(s[2 * kt + h][e] - base[e >> 1]);
+                        for (int e = 0; e < 2 * NROW; ++e) {
+                            pv[e] = fast_exp2(fmaf(s[2 * kt + h][e], p.scale_log2e, shift[e >> 1]));
+                        }
                         l_run[0] += pv[0] + pv[1];
                         if (!HALF) l_run[1] += pv[2] + pv[3];
                         pa[kt][2 * h] = pack2<T>(pv[0], pv[1]);
                         const float2 r01 = unpack2<T>(pa[kt][2 * h]);
                         pb[kt][2 * h] = pack2<T>(pv[0] - r01.x, pv[1] - r01.y);
                         if (HALF) {
-                            // rows 8-15 of the tile are free: they carry the remainder, so one MMA does both
                             pa[kt][2 * h + 1] = pb[kt][2 * h];
                         } else {
                             pa[kt][2 * h + 1] = pack2<T>(pv[2], pv[3]);
@@ -765,18 +839,14 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 }
 
                 // ---- O += P V
+                if (!(knock & 4))
 #pragma unroll
                 for (int kt = 0; kt < KT; ++kt) {
 #pragma unroll
                     for (int np = 0; np < DN / 2; ++np) {
                         uint32_t b[4];
-                        const int tok = ps * WT + kt * 16 + (lm_mat & 1) * 8 + lm_row;
-                        const int chunk = 2 * np + (lm_mat >> 1);
-                        const int box = tok / G::kBoxRows;
-                        const int r = tok % G::kBoxRows;
-                        const uint32_t addr = v_base + box * G::kCopyBytes + (chunk / 8) * G::kBoxBytes + r * 128 +
-                                              (((chunk & 7) ^ (r & 7)) << 4);
-                        ldmatrix_x4_trans(b, addr);
+                        ldmatrix_x4_trans(b, v_addr[np & 3] + ((2 * np) / 8) * G::kBoxBytes +
+                                                 ((ps * WT + 16 * kt) / G::kBoxRows) * G::kCopyBytes);
                         mma_16816<T>(o[2 * np], pa[kt], b[0], b[1]);
                         mma_16816<T>(o[2 * np + 1], pa[kt], b[2], b[3]);
                         if (!HALF) {
@@ -793,7 +863,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             }
             stage_counter += t_num_tiles;
 
-            if (p.stream_only >= 2) {
+            if (p.stream_only >= 2 && p.stream_only < 4) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
                 continue;
@@ -844,8 +914,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                             const float l_other = my_slot[(FR + 2 + i) * 32 + lane];
                             const float m_new = fmaxf(m_run[i], m_other);
                             const float b = m_new == -INFINITY ? 0.0f : m_new;
-                            fa[i] = fast_exp2(m_run[i] - b);
-                            fb[i] = fast_exp2(m_other - b);
+                            fa[i] = fast_exp2((m_run[i] - b) * p.scale_log2e);
+                            fb[i] = fast_exp2((m_other - b) * p.scale_log2e);
                             l_run[i] = l_run[i] * fa[i] + l_other * fb[i];
                             m_run[i] = m_new;
                         }
@@ -875,7 +945,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 #pragma unroll
                     for (int k = 0; k < KVW; ++k) {
                         const float* slot_mem = merge + (k * MT + mt) * G::kMergeSlotFloats;
-                        weight[k][i] = fast_exp2(slot_mem[(FR + i) * 32 + lane] - b);
+                        weight[k][i] = fast_exp2((slot_mem[(FR + i) * 32 + lane] - b) * p.scale_log2e);
                         l_sum += slot_mem[(FR + 2 + i) * 32 + lane] * weight[k][i];
                     }
                     m_all[i] = m_max;
@@ -928,8 +998,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 }
                 if (!p.direct && part == 0 && tq == 0) {
                     p.partial_sum[index] = l_all[i];
-                    // the running maximum lives in the log2 domain of scale * log2(e); publish natural log
-                    p.partial_max[index] = l_all[i] > 0.0f ? m_all[i] * 0.6931471805599453f : -INFINITY;
+                    // the running maximum is a raw dot product; publish the natural-log-domain logit (dot * scale)
+                    p.partial_max[index] = l_all[i] > 0.0f ? m_all[i] * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
                 }
             }
             // ---- hand the task slot (descriptor + Q rows) back to the producer
