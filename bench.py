@@ -3,7 +3,8 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c2|c3|c1]
 
-One step = one attention call (map + LSE reduce) over one batch of synthetic paged decode requests.
+One step = one attention call (split-KV map tasks and the LSE merge, one kernel launch) over one batch of
+synthetic paged decode requests.
 Default workload: batch 64, q_len 1, Hq 64 / Hkv 8 / head_dim 128, bf16, context lengths uniform in
 [1024, 8192] (seed 1), 16-token pages in a 40,000-page pool with random block tables, split-KV partitions
 of 512 tokens. Metric: KV-read GB/s = algorithmic KV bytes (every visible K and V row once) / time.
@@ -226,6 +227,7 @@ def run_ours(args):
     if spec["partition"]:
         variant = next(v for v in attention.selector.variants() if v.kind == 0 and v.thread_block.max_q_tokens == 1)
         selection = attention.select_partitioned(variant, spec["partition"], False, token_indices, cu_tokens)
+    attention.fused = args.fused
     attention.prepare(req_slots, token_indices, cu_tokens, selection=selection)
     shape = attention.metadata.replay_shape()
     kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * 2  # q_len new tokens are already in the cache
@@ -244,7 +246,7 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
     launches = 0
     sampler.__enter__()
     if True:
@@ -260,33 +262,16 @@ def run_ours(args):
         t0 = time.perf_counter()
         for i in range(args.steps):
             events[i][0].record(torch_stream)
-            att = attention
-            meta = att.metadata
-            # the two halves of record_sdpa with an event between them, to time the map kernel by itself
-            if meta.variant().kind == 0:
-                from khalamari_b200 import sliced_kv
-                compute = att._sliced_kv(shape, meta.variant())
-                compute.invoke_map(stream, sliced_kv.MapBuffers(
-                    case["d_q"], case["d_pool"], meta.req_slots(), case["d_table"], meta.sdpa_map_task_templates(),
-                    att.partial_exp_sums, att.partial_max_logits, att.partial_output), 0, shape.num_tokens,
-                    shape.num_sdpa_map_task_templates)
-                events[i][1].record(torch_stream)
-                compute.invoke_reduce(stream, sliced_kv.ReduceBuffers(
-                    att.partial_exp_sums, att.partial_max_logits, att.partial_output, meta.cu_sdpa_partial_outputs(),
-                    case["d_out"]), shape.num_tokens)
-                launches += 2
-            else:
-                launches += step()
-                events[i][1].record(torch_stream)
-            events[i][2].record(torch_stream)
+            launches += step()  # one launch: map tasks plus the in-kernel merge of every completed group
+            events[i][1].record(torch_stream)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         barrier()
         timed_window = (t0, t1)
     device.check(stream)
-    step_ms = [events[i][0].elapsed_time(events[i][2]) for i in range(args.steps)]
-    map_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
-    total_ms = events[0][0].elapsed_time(events[-1][2])
+    step_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
+    map_ms = step_ms  # the step is one kernel launch
+    total_ms = events[0][0].elapsed_time(events[-1][1])
     ms_per_step = total_ms / args.steps
 
     # ---- end to end through the component seam with host buffers -------------------------------------
@@ -442,6 +427,8 @@ def main():
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")
     parser.add_argument("--pool-pages", type=int, default=0, help="override the page pool size (profiling captures)")
     parser.add_argument("--partition", type=int, default=-1, help="override the split-KV partition (0: selector)")
+    parser.add_argument("--fused", action="store_true",
+                        help="map and reduce in one launch (last-arriver merge) instead of the reference's two")
     parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")
     args = parser.parse_args()
     result = run_reference(args) if args.impl == "reference" else run_ours(args)

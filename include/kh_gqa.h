@@ -380,6 +380,23 @@ KH_API kh_status kh_sliced_kv_map(kh_sliced_kv* compute, kh_stream* stream, cons
 KH_API kh_status kh_sliced_kv_reduce(kh_sliced_kv* compute, kh_stream* stream,
                                      const kh_sliced_kv_reduce_buffers* buffers, uint32_t num_active_tokens);
 
+/* Map and reduce in ONE launch: what `invoke_map` followed by `invoke_reduce` computes
+ * (EM/attn/gqa/backend.rs:458-482 records them back to back with a barrier between). Every map task still
+ * publishes its partial through the buffers of `map_buffers`; the thread block that publishes the last partial of a
+ * (token, KV head, Q-head range) group merges that group while the partials are still in L2 and writes `output`.
+ * No block waits for another. A token with a single partial is written directly.
+ * `arrival_counters` is scratch owned by the caller: kh_sliced_kv_arrival_counter_bytes() bytes, zero before the
+ * first call; every call leaves it zero again. Calls that share it must not overlap on the GPU. Every map task
+ * template of an active token must be active (as the selector's metadata guarantees). */
+KH_API kh_status kh_sliced_kv_map_reduce(kh_sliced_kv* compute, kh_stream* stream,
+                                         const kh_sliced_kv_map_buffers* map_buffers,
+                                         const kh_sliced_kv_reduce_buffers* reduce_buffers, kh_buffer_ref arrival_counters,
+                                         uint32_t page_table_index, uint32_t num_active_tokens,
+                                         uint32_t num_active_kv_splits);
+KH_API kh_status kh_sliced_kv_arrival_counter_bytes(const kh_sliced_kv_config* config,
+                                                    const kh_execution_variant* execution,
+                                                    const kh_sliced_kv_shape* shape, uint64_t* out);
+
 /* ---- SlicedQ compute: BM/components/gqa/sdpa/sliced_q.rs ------------------------------------ */
 /* sliced_q::Config (sliced_q.rs:145-153) plus kv_dtype. */
 typedef struct kh_sliced_q_config {
@@ -465,6 +482,17 @@ KH_API kh_status kh_sliced_q_direct(kh_sliced_q* compute, kh_stream* stream,
 /* Compute::invoke_reduce(...).record (sliced_q.rs:484-503, 617-642). */
 KH_API kh_status kh_sliced_q_reduce(kh_sliced_q* compute, kh_stream* stream,
                                     const kh_sliced_q_reduce_buffers* buffers, uint32_t num_active_q_token_tiles);
+
+/* Map and reduce in one launch for the sliced-Q variants (EM/attn/gqa/backend.rs:506-540); same contract as
+ * kh_sliced_kv_map_reduce, with one arrival counter per (Q-token tile, KV head, Q-head range). */
+KH_API kh_status kh_sliced_q_map_reduce(kh_sliced_q* compute, kh_stream* stream,
+                                        const kh_sliced_q_map_buffers* map_buffers,
+                                        const kh_sliced_q_reduce_buffers* reduce_buffers, kh_buffer_ref arrival_counters,
+                                        uint32_t page_table_index, uint32_t num_active_tokens,
+                                        uint32_t num_active_q_token_tiles, uint32_t num_active_kv_splits);
+KH_API kh_status kh_sliced_q_arrival_counter_bytes(const kh_sliced_q_config* config,
+                                                   const kh_execution_variant* execution,
+                                                   const kh_sliced_q_shape* shape, uint64_t* out);
 
 /* ---- device status word: the analogue of SubmissionCheck (BM/metal/stream/check.rs:8-13) ---- */
 /* Reads (after synchronising the stream) and clears the sticky status the kernels of `device`

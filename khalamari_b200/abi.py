@@ -212,12 +212,17 @@ PROTOTYPES = {
     "kh_sliced_kv_destroy": [_vp],
     "kh_sliced_kv_map": [_vp, _vp, P(SlicedKvMapBuffersC), _u32, _u32, _u32],
     "kh_sliced_kv_reduce": [_vp, _vp, P(SlicedKvReduceBuffersC), _u32],
+    "kh_sliced_kv_map_reduce": [_vp, _vp, P(SlicedKvMapBuffersC), P(SlicedKvReduceBuffersC), BufferRef, _u32, _u32, _u32],
+    "kh_sliced_kv_arrival_counter_bytes": [P(SlicedKvConfigC), P(ExecutionVariantC), P(SlicedKvShapeC), P(C.c_uint64)],
     "kh_sliced_q_sizes_get": [P(SlicedQConfigC), P(ExecutionVariantC), P(SlicedQShapeC), P(SlicedQSizesC)],
     "kh_sliced_q_create": [_vp, P(SlicedQConfigC), P(ExecutionVariantC), P(SlicedQShapeC), C.c_int32, P(_vp)],
     "kh_sliced_q_destroy": [_vp],
     "kh_sliced_q_map": [_vp, _vp, P(SlicedQMapBuffersC), _u32, _u32, _u32, _u32],
     "kh_sliced_q_direct": [_vp, _vp, P(SlicedQDirectBuffersC), _u32, _u32, _u32],
     "kh_sliced_q_reduce": [_vp, _vp, P(SlicedQReduceBuffersC), _u32],
+    "kh_sliced_q_map_reduce": [_vp, _vp, P(SlicedQMapBuffersC), P(SlicedQReduceBuffersC), BufferRef, _u32, _u32, _u32,
+                               _u32],
+    "kh_sliced_q_arrival_counter_bytes": [P(SlicedQConfigC), P(ExecutionVariantC), P(SlicedQShapeC), P(C.c_uint64)],
     "kh_device_check": [_vp, _vp, P(_u32)],
     "kh_combine_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, BufferRef, BufferRef, _u32, BufferRef, BufferRef,
                             BufferRef],

@@ -102,40 +102,19 @@ __global__ void __launch_bounds__(128) sdpa_reduce_kernel(const ReduceParams p) 
     const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
     const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
     const uint32_t D = p.head_dim;
+    const uint64_t stride = uint64_t(p.num_q_heads) * p.max_q_tokens;
     for (uint32_t local = threadIdx.x * 4; local < num_toks * D; local += blockDim.x * 4) {
         const uint32_t tok = local / D;
         const uint32_t d = local % D;
-        float global_max = -INFINITY;
-        for (uint32_t i = first; i < last; ++i) {
-            const uint64_t index = (uint64_t(i) * p.num_q_heads + head) * p.max_q_tokens + tok;
-            global_max = fmaxf(global_max, p.partial_max[index]);
-        }
-        float global_sum = 0.0f;
-        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t i = first; i < last; ++i) {
-            const uint64_t index = (uint64_t(i) * p.num_q_heads + head) * p.max_q_tokens + tok;
-            const float sum = p.partial_sum[index];
-            const float mx = p.partial_max[index];
-            const float weight = (sum != 0.0f && isfinite(mx)) ? expf(mx - global_max) * sum : 0.0f;
-            if (weight != 0.0f) {
-                const float4 v = *reinterpret_cast<const float4*>(p.partial_out + index * D + d);
-                acc.x += weight * v.x;
-                acc.y += weight * v.y;
-                acc.z += weight * v.z;
-                acc.w += weight * v.w;
-            }
-            global_sum += weight;
-        }
-        const float inv = global_sum > 0.0f ? 1.0f / global_sum : 0.0f;
-        acc.x *= inv;
-        acc.y *= inv;
-        acc.z *= inv;
-        acc.w *= inv;
+        const uint64_t first_index = (uint64_t(first) * p.num_q_heads + head) * p.max_q_tokens + tok;
+        float merged_sum, merged_max;
+        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first_index, stride,
+                                              last - first, D, d, &merged_sum, &merged_max);
         const uint64_t out_row = uint64_t(tok_begin + tok) * p.num_q_heads + head;
         store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
         if (p.out_sum != nullptr && d == 0) {
-            p.out_sum[out_row] = global_sum;
-            p.out_max[out_row] = global_sum > 0.0f ? global_max : -INFINITY;
+            p.out_sum[out_row] = merged_sum;
+            p.out_max[out_row] = merged_max;
         }
     }
 }
@@ -335,13 +314,13 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     p.pages_per_request_layer = c.layout.num_blocks * c.layout.num_page_ids_per_block;
     p.pool_pages = static_cast<uint32_t>(std::min<uint64_t>(kv_pages.bytes / c.page_bytes, 0xffffffffull));
     p.scale_log2e = c.scale * 1.4426950408889634f;
-    // Measurement aid: KH_GQA_STREAM_ONLY=1 makes the consumer warps release every K/V stage without
-    // computing, which times the paged TMA gather by itself (outputs are then meaningless).
-    static const uint32_t stream_only = [] {
-        const char* value = std::getenv("KH_GQA_STREAM_ONLY");
+    // Measurement aid: KH_GQA_DEBUG=<bits> switches parts of the kernel off (see MapParams::debug) so that the
+    // paged TMA gather, the tensor-core math and the hand-offs can be timed separately.
+    static const uint32_t debug_bits = [] {
+        const char* value = std::getenv("KH_GQA_DEBUG");
         return value != nullptr ? uint32_t(std::atoi(value)) : 0u;
     }();
-    p.stream_only = stream_only;
+    p.debug = debug_bits;
     if (num_templates == 0) return;
     const uint64_t tasks = uint64_t(num_templates) * c.num_kv_heads * p.head_ranges;
     KH_REQUIRE(tasks <= 0xffffffffull, "GQA SDPA map task count must fit u32");
@@ -800,43 +779,88 @@ kh_status kh_sliced_kv_destroy(kh_sliced_kv* compute) {
     return KH_OK;
 }
 
+static void sliced_kv_launch(kh_sliced_kv* compute, kh_stream* stream, const kh_sliced_kv_map_buffers* buffers,
+                             const kh_sliced_kv_reduce_buffers* fused, kh_buffer_ref arrival_counters,
+                             uint32_t page_table_index, uint32_t num_active_tokens, uint32_t num_active_kv_splits) {
+    KH_REQUIRE(compute && stream && buffers, "null argument");
+    const kh_sliced_kv_sizes& z = compute->sizes;
+    const kh_sliced_kv_shape& s = compute->shape;
+    // MapInvocation::validate (sliced_kv.rs:594-612)
+    KH_REQUIRE(page_table_index < compute->config.page_table_layout.num_gqa_layers, "page_table_index %u out of range",
+               page_table_index);
+    KH_REQUIRE(num_active_tokens >= 1 && num_active_tokens <= s.num_total_tokens,
+               "num_active_tokens %u outside [1, %u]", num_active_tokens, s.num_total_tokens);
+    KH_REQUIRE(num_active_kv_splits <= s.num_total_sdpa_map_task_templates, "num_active_kv_splits %u outside [0, %u]",
+               num_active_kv_splits, s.num_total_sdpa_map_task_templates);
+    need(buffers->q, z.q_bytes, "q");
+    need(buffers->kv_pages, compute->config.page_bytes, "kv_pages");
+    need(buffers->req_slots, z.req_slots_bytes, "req_slots");
+    need(buffers->page_ids, z.page_ids_bytes, "page_ids");
+    need(buffers->sdpa_map_task_templates, z.sdpa_map_task_templates_bytes, "sdpa_map_task_templates");
+    need(buffers->partial_exp_sums, z.partial_output_stats_bytes, "partial_exp_sums");
+    need(buffers->partial_max_logits, z.partial_output_stats_bytes, "partial_max_logits");
+    need(buffers->partial_output, z.partial_output_bytes, "partial_output");
+    MapParams p{};
+    p.req_slots = static_cast<const uint32_t*>(buffers->req_slots.ptr);
+    p.page_ids = static_cast<const uint32_t*>(buffers->page_ids.ptr);
+    p.visible = nullptr;
+    p.q_ranges = nullptr;
+    p.templates = static_cast<const uint32_t*>(buffers->sdpa_map_task_templates.ptr);
+    p.partial_out = static_cast<float*>(buffers->partial_output.ptr);
+    p.partial_sum = static_cast<float*>(buffers->partial_exp_sums.ptr);
+    p.partial_max = static_cast<float*>(buffers->partial_max_logits.ptr);
+    p.out = nullptr;
+    p.num_active_tokens = num_active_tokens;
+    p.num_active_q_tiles = num_active_tokens;
+    p.layer_index = page_table_index;
+    p.direct = 0;
+    if (fused != nullptr) {
+        KH_REQUIRE(fused->partial_exp_sums.ptr == buffers->partial_exp_sums.ptr &&
+                       fused->partial_max_logits.ptr == buffers->partial_max_logits.ptr &&
+                       fused->partial_output.ptr == buffers->partial_output.ptr,
+                   "the fused call needs the same partial buffers on its map and reduce sides");
+        need(fused->cu_sdpa_partial_outputs, z.cu_sdpa_partial_outputs_bytes, "cu_sdpa_partial_outputs");
+        need(fused->output, z.q_bytes, "output");
+        const uint32_t head_ranges =
+            div_ceil(compute->config.num_q_heads / compute->config.num_kv_heads, compute->common.variant.max_q_heads);
+        need(arrival_counters, uint64_t(s.num_total_tokens) * compute->config.num_kv_heads * head_ranges * 4,
+             "arrival_counters");
+        p.cu = static_cast<const uint32_t*>(fused->cu_sdpa_partial_outputs.ptr);
+        p.arrivals = static_cast<uint32_t*>(arrival_counters.ptr);
+        p.out = fused->output.ptr;
+    }
+    launch_map(compute->common, stream, p, buffers->q, buffers->kv_pages, num_active_kv_splits);
+}
+
 kh_status kh_sliced_kv_map(kh_sliced_kv* compute, kh_stream* stream, const kh_sliced_kv_map_buffers* buffers,
                            uint32_t page_table_index, uint32_t num_active_tokens, uint32_t num_active_kv_splits) {
     return guarded([&]() -> kh_status {
-        KH_REQUIRE(compute && stream && buffers, "null argument");
-        const kh_sliced_kv_sizes& z = compute->sizes;
-        const kh_sliced_kv_shape& s = compute->shape;
-        // MapInvocation::validate (sliced_kv.rs:594-612)
-        KH_REQUIRE(page_table_index < compute->config.page_table_layout.num_gqa_layers,
-                   "page_table_index %u out of range", page_table_index);
-        KH_REQUIRE(num_active_tokens >= 1 && num_active_tokens <= s.num_total_tokens,
-                   "num_active_tokens %u outside [1, %u]", num_active_tokens, s.num_total_tokens);
-        KH_REQUIRE(num_active_kv_splits <= s.num_total_sdpa_map_task_templates,
-                   "num_active_kv_splits %u outside [0, %u]", num_active_kv_splits,
-                   s.num_total_sdpa_map_task_templates);
-        need(buffers->q, z.q_bytes, "q");
-        need(buffers->kv_pages, compute->config.page_bytes, "kv_pages");
-        need(buffers->req_slots, z.req_slots_bytes, "req_slots");
-        need(buffers->page_ids, z.page_ids_bytes, "page_ids");
-        need(buffers->sdpa_map_task_templates, z.sdpa_map_task_templates_bytes, "sdpa_map_task_templates");
-        need(buffers->partial_exp_sums, z.partial_output_stats_bytes, "partial_exp_sums");
-        need(buffers->partial_max_logits, z.partial_output_stats_bytes, "partial_max_logits");
-        need(buffers->partial_output, z.partial_output_bytes, "partial_output");
-        MapParams p{};
-        p.req_slots = static_cast<const uint32_t*>(buffers->req_slots.ptr);
-        p.page_ids = static_cast<const uint32_t*>(buffers->page_ids.ptr);
-        p.visible = nullptr;
-        p.q_ranges = nullptr;
-        p.templates = static_cast<const uint32_t*>(buffers->sdpa_map_task_templates.ptr);
-        p.partial_out = static_cast<float*>(buffers->partial_output.ptr);
-        p.partial_sum = static_cast<float*>(buffers->partial_exp_sums.ptr);
-        p.partial_max = static_cast<float*>(buffers->partial_max_logits.ptr);
-        p.out = nullptr;
-        p.num_active_tokens = num_active_tokens;
-        p.num_active_q_tiles = num_active_tokens;
-        p.layer_index = page_table_index;
-        p.direct = 0;
-        launch_map(compute->common, stream, p, buffers->q, buffers->kv_pages, num_active_kv_splits);
+        sliced_kv_launch(compute, stream, buffers, nullptr, kh_buffer_ref{}, page_table_index, num_active_tokens,
+                         num_active_kv_splits);
+        return KH_OK;
+    });
+}
+
+kh_status kh_sliced_kv_map_reduce(kh_sliced_kv* compute, kh_stream* stream, const kh_sliced_kv_map_buffers* map_buffers,
+                                  const kh_sliced_kv_reduce_buffers* reduce_buffers, kh_buffer_ref arrival_counters,
+                                  uint32_t page_table_index, uint32_t num_active_tokens,
+                                  uint32_t num_active_kv_splits) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(reduce_buffers != nullptr, "null argument");
+        sliced_kv_launch(compute, stream, map_buffers, reduce_buffers, arrival_counters, page_table_index,
+                         num_active_tokens, num_active_kv_splits);
+        return KH_OK;
+    });
+}
+
+kh_status kh_sliced_kv_arrival_counter_bytes(const kh_sliced_kv_config* config, const kh_execution_variant* execution,
+                                             const kh_sliced_kv_shape* shape, uint64_t* out) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(config && execution && shape && out, "null argument");
+        sliced_kv_sizes(*config, *shape);
+        KH_REQUIRE(execution->max_q_heads > 0, "execution variant has no Q heads");
+        const uint32_t head_ranges = div_ceil(config->num_q_heads / config->num_kv_heads, execution->max_q_heads);
+        *out = uint64_t(shape->num_total_tokens) * config->num_kv_heads * head_ranges * 4;
         return KH_OK;
     });
 }
@@ -915,6 +939,7 @@ kh_status kh_sliced_q_destroy(kh_sliced_q* compute) {
 
 static void sliced_q_launch(kh_sliced_q* compute, kh_stream* stream, const kh_sliced_q_direct_buffers& in,
                             kh_buffer_ref partial_sums, kh_buffer_ref partial_max, bool direct,
+                            const kh_sliced_q_reduce_buffers* fused, kh_buffer_ref arrival_counters,
                             uint32_t page_table_index, uint32_t num_active_tokens, uint32_t num_active_q_token_tiles,
                             uint32_t num_active_kv_splits) {
     const kh_sliced_q_sizes& z = compute->sizes;
@@ -959,6 +984,21 @@ static void sliced_q_launch(kh_sliced_q* compute, kh_stream* stream, const kh_sl
     p.num_active_q_tiles = num_active_q_token_tiles;
     p.layer_index = page_table_index;
     p.direct = direct ? 1u : 0u;
+    if (fused != nullptr) {
+        KH_REQUIRE(!direct, "direct SDPA has no Reduce stage");
+        KH_REQUIRE(fused->partial_exp_sums.ptr == partial_sums.ptr && fused->partial_max_logits.ptr == partial_max.ptr &&
+                       fused->partial_output.ptr == in.output.ptr && fused->q_token_ranges.ptr == in.q_token_ranges.ptr,
+                   "the fused call needs the same partial and range buffers on its map and reduce sides");
+        need(fused->cu_sdpa_partial_outputs, (uint64_t(s.num_total_q_token_tiles) + 1) * 4, "cu_sdpa_partial_outputs");
+        need(fused->output, z.q_bytes, "output");
+        const uint32_t head_ranges =
+            div_ceil(compute->config.num_q_heads / compute->config.num_kv_heads, compute->common.variant.max_q_heads);
+        need(arrival_counters, uint64_t(s.num_total_q_token_tiles) * compute->config.num_kv_heads * head_ranges * 4,
+             "arrival_counters");
+        p.cu = static_cast<const uint32_t*>(fused->cu_sdpa_partial_outputs.ptr);
+        p.arrivals = static_cast<uint32_t*>(arrival_counters.ptr);
+        p.out = fused->output.ptr;
+    }
     launch_map(compute->common, stream, p, in.q, in.kv_pages, num_active_kv_splits);
 }
 
@@ -976,8 +1016,42 @@ kh_status kh_sliced_q_map(kh_sliced_q* compute, kh_stream* stream, const kh_slic
                                       buffers->q_token_ranges,
                                       buffers->sdpa_map_task_templates,
                                       buffers->partial_output};
+        sliced_q_launch(compute, stream, in, buffers->partial_exp_sums, buffers->partial_max_logits, false, nullptr,
+                        kh_buffer_ref{}, page_table_index, num_active_tokens, num_active_q_token_tiles,
+                        num_active_kv_splits);
+        return KH_OK;
+    });
+}
+
+kh_status kh_sliced_q_map_reduce(kh_sliced_q* compute, kh_stream* stream, const kh_sliced_q_map_buffers* buffers,
+                                 const kh_sliced_q_reduce_buffers* reduce_buffers, kh_buffer_ref arrival_counters,
+                                 uint32_t page_table_index, uint32_t num_active_tokens,
+                                 uint32_t num_active_q_token_tiles, uint32_t num_active_kv_splits) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(compute && stream && buffers && reduce_buffers, "null argument");
+        KH_REQUIRE(!compute->direct, "this compute was created for direct output");
+        kh_sliced_q_direct_buffers in{buffers->q,
+                                      buffers->kv_pages,
+                                      buffers->req_slots,
+                                      buffers->page_ids,
+                                      buffers->visible_kv_token_ranges,
+                                      buffers->q_token_ranges,
+                                      buffers->sdpa_map_task_templates,
+                                      buffers->partial_output};
         sliced_q_launch(compute, stream, in, buffers->partial_exp_sums, buffers->partial_max_logits, false,
-                        page_table_index, num_active_tokens, num_active_q_token_tiles, num_active_kv_splits);
+                        reduce_buffers, arrival_counters, page_table_index, num_active_tokens,
+                        num_active_q_token_tiles, num_active_kv_splits);
+        return KH_OK;
+    });
+}
+
+kh_status kh_sliced_q_arrival_counter_bytes(const kh_sliced_q_config* config, const kh_execution_variant* execution,
+                                            const kh_sliced_q_shape* shape, uint64_t* out) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(config && execution && shape && out, "null argument");
+        sliced_q_sizes(*config, *execution, *shape);
+        const uint32_t head_ranges = div_ceil(config->num_q_heads / config->num_kv_heads, execution->max_q_heads);
+        *out = uint64_t(shape->num_total_q_token_tiles) * config->num_kv_heads * head_ranges * 4;
         return KH_OK;
     });
 }
@@ -988,8 +1062,8 @@ kh_status kh_sliced_q_direct(kh_sliced_q* compute, kh_stream* stream, const kh_s
     return guarded([&]() -> kh_status {
         KH_REQUIRE(compute && stream && buffers, "null argument");
         KH_REQUIRE(compute->direct, "this compute was created for Map/Reduce output");
-        sliced_q_launch(compute, stream, *buffers, kh_buffer_ref{}, kh_buffer_ref{}, true, page_table_index,
-                        num_active_tokens, num_active_q_token_tiles, num_active_q_token_tiles);
+        sliced_q_launch(compute, stream, *buffers, kh_buffer_ref{}, kh_buffer_ref{}, true, nullptr, kh_buffer_ref{},
+                        page_table_index, num_active_tokens, num_active_q_token_tiles, num_active_q_token_tiles);
         return KH_OK;
     });
 }

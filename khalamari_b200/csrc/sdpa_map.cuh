@@ -62,7 +62,13 @@ struct MapParams {
     uint32_t pool_pages;
     float scale_log2e;                // scale * log2(e)
     uint32_t direct;                  // 1: write final output, 0: write partials
-    uint32_t stream_only;             // measurement aid: consumers release every stage without computing
+    const uint32_t* cu;               // fused reduce: [ranges + 1] first partial (= template) of every Q range; null: off
+    uint32_t* arrivals;               // fused reduce: one zeroed counter per (Q range, KV head, head range)
+    // Measurement aid (KH_GQA_DEBUG, 0 in normal use; outputs are meaningless when set). Bits: 1 consumers release
+    // every stage without computing; 2 skip the task-end merge and publish; 4 skip the Q copies; 8 issue no K/V
+    // copies (consumers run on stale shared memory); 16 / 32 / 64 skip QK / softmax / PV; 128 never run the
+    // in-kernel group merge; 256 do not count arrivals.
+    uint32_t debug;
 };
 
 constexpr uint32_t kStatusWaitExpired = 1u;
@@ -209,6 +215,92 @@ __device__ __forceinline__ void consumer_barrier(int threads) {
     asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(threads) : "memory");
 }
 
+template <typename T>
+__device__ __forceinline__ void store_out4(T* dst, float4 v) {
+    uint2 packed = make_uint2(pack2<T>(v.x, v.y), pack2<T>(v.z, v.w));
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+// Partial-state merge of one output vector (four columns of one (token, head) row): the reducer's formula
+// (docs/gqa_sdpa_selection.md:443-460 of the reference; gqa_sdpa_sliced_kv_reduce.metal:30-55):
+// max = max_i m_i, weight_i = exp(m_i - max) * l_i (0 for an empty partial), out = sum_i weight_i o_i / sum_i weight_i.
+// Partials are taken eight at a time with all their loads issued together (the merge runs while the memory system
+// is saturated by K/V streaming, so dependent loads are what costs), carrying (max, sum, numerator) between groups.
+// L2-only loads: the partials may have been written by other SMs during this launch.
+__device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, const float* partial_max,
+                                                     const float* partial_out, uint64_t first_index,
+                                                     uint64_t index_stride, uint32_t count, uint32_t head_dim,
+                                                     uint32_t d, float* out_sum, float* out_max) {
+    float run_max = -INFINITY, run_sum = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t base = 0; base < count; base += 8) {
+        float mx[8], sm[8];
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool valid = base + j < count;
+            const uint64_t index = first_index + uint64_t(base + j) * index_stride;
+            mx[j] = valid ? __ldcg(partial_max + index) : -INFINITY;
+            sm[j] = valid ? __ldcg(partial_sum + index) : 0.0f;
+            v[j] = valid ? __ldcg(reinterpret_cast<const float4*>(partial_out + index * head_dim + d))
+                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        float new_max = run_max;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) new_max = fmaxf(new_max, mx[j]);
+        const float keep = run_max == -INFINITY ? 0.0f : expf(run_max - new_max);
+        acc.x *= keep;
+        acc.y *= keep;
+        acc.z *= keep;
+        acc.w *= keep;
+        run_sum *= keep;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float weight = (sm[j] != 0.0f && isfinite(mx[j])) ? expf(mx[j] - new_max) * sm[j] : 0.0f;
+            if (weight != 0.0f) {  // an empty partial's output row is never used, whatever its bits
+                acc.x += weight * v[j].x;
+                acc.y += weight * v[j].y;
+                acc.z += weight * v[j].z;
+                acc.w += weight * v[j].w;
+            }
+            run_sum += weight;
+        }
+        run_max = new_max;
+    }
+    const float inv = run_sum > 0.0f ? 1.0f / run_sum : 0.0f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    if (out_sum != nullptr) {
+        *out_sum = run_sum;
+        *out_max = run_sum > 0.0f ? run_max : -INFINITY;
+    }
+    return acc;
+}
+
+// Merges the partials [part_begin, part_begin + part_count) of the rows (num_toks tokens x num_heads heads) of
+// one task group and writes the final output. Called by every consumer thread of the CTA that completed the group.
+template <typename T, int D>
+__device__ __forceinline__ void reduce_group(const MapParams& p, uint32_t tok_begin, uint32_t num_toks,
+                                             uint32_t head_begin, uint32_t num_heads, uint32_t part_begin,
+                                             uint32_t part_count, uint32_t tid, uint32_t threads) {
+    constexpr uint32_t kVecs = D / 4;
+    const uint32_t rows = num_toks * num_heads;
+    const uint64_t stride = uint64_t(p.num_q_heads) * p.max_q_tokens;
+    for (uint32_t idx = tid; idx < rows * kVecs; idx += threads) {
+        const uint32_t row = idx / kVecs;
+        const uint32_t d = (idx % kVecs) * 4;
+        const uint32_t tok = row / num_heads;
+        const uint32_t head = head_begin + row % num_heads;
+        const uint64_t first = (uint64_t(part_begin) * p.num_q_heads + head) * p.max_q_tokens + tok;
+        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first, stride, part_count, D,
+                                              d, nullptr, nullptr);
+        T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(tok_begin + tok) * p.num_q_heads + head) * D + d;
+        store_out4<T>(dst, acc);
+    }
+}
+
 // Task descriptor as the producer publishes it to the consumers (shared memory).
 struct TaskSlot {
     uint32_t tmpl;
@@ -221,7 +313,10 @@ struct TaskSlot {
     uint32_t tile_begin;   // kv_begin rounded down to a stage boundary
     uint32_t num_tiles;
     uint32_t done;         // 1: no more tasks for this CTA
-    uint32_t pad[2];
+    uint32_t group;        // fused reduce: arrival counter of this task's (Q range, KV head, head range)
+    uint32_t part_begin;   // fused reduce: first partial (template) of the Q range
+    uint32_t part_count;   // fused reduce: partials of the Q range
+    uint32_t pad;
     uint32_t visible[2 * kMaxTaskTokens];  // per Q token [begin, end), only when MapParams::visible is set
 };
 
@@ -275,6 +370,7 @@ struct MapGeometry {
 // Per-lane decoded task (producer registers).
 struct TaskInfo {
     uint32_t tmpl, head_begin, num_heads, tok_begin, num_toks, kv_begin, kv_end, req_slot, kv_head, active;
+    uint32_t group, part_begin, part_count;
 };
 
 // Decodes flat task index -> template, KV head, head range, and applies the reference kernels'
@@ -284,6 +380,7 @@ __device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint64_t tas
     TaskInfo t;
     t.tmpl = t.head_begin = t.num_heads = t.tok_begin = t.num_toks = t.kv_begin = t.kv_end = t.req_slot = t.kv_head = 0;
     t.active = 0;
+    t.group = t.part_begin = t.part_count = 0;
     if (task >= total_tasks) return t;
     const uint32_t cells = p.num_kv_heads * p.head_ranges;
     t.tmpl = uint32_t(task) / cells;
@@ -308,6 +405,11 @@ __device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint64_t tas
     t.kv_begin = p.templates[t.tmpl * 3 + 1];
     t.kv_end = p.templates[t.tmpl * 3 + 2];
     t.req_slot = p.req_slots[t.tok_begin];
+    if (p.cu != nullptr) {
+        t.part_begin = p.cu[q_range];
+        t.part_count = p.cu[q_range + 1] - t.part_begin;
+        t.group = (q_range * p.num_kv_heads + t.kv_head) * p.head_ranges + range;
+    }
     t.active = 1;
     return t;
 }
@@ -324,6 +426,9 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
     r.req_slot = __shfl_sync(0xffffffffu, t.req_slot, lane);
     r.kv_head = __shfl_sync(0xffffffffu, t.kv_head, lane);
     r.active = __shfl_sync(0xffffffffu, t.active, lane);
+    r.group = __shfl_sync(0xffffffffu, t.group, lane);
+    r.part_begin = __shfl_sync(0xffffffffu, t.part_begin, lane);
+    r.part_count = __shfl_sync(0xffffffffu, t.part_count, lane);
     return r;
 }
 
@@ -354,6 +459,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 2 * TQ);
+    volatile uint32_t* last_flag = abort_flag + 1;  // fused reduce: "this CTA completed its group"
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -455,6 +561,9 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         ts->tile_begin = tile_begin;
                         ts->num_tiles = num_tiles;
                         ts->done = 0;
+                        ts->group = cur.group;
+                        ts->part_begin = cur.part_begin;
+                        ts->part_count = cur.part_count;
                     }
                     if (p.visible != nullptr) {
                         for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
@@ -464,7 +573,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         }
                     }
                     if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-                    const uint32_t q_boxes = (p.stream_only == 3) ? 0u : cur.num_toks * NH;
+                    const uint32_t q_boxes = (p.debug & 4) ? 0u : cur.num_toks * NH;
                     if (lane == 0) {
                         mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
                     }
@@ -515,7 +624,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                                 break;
                             }
                             const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
-                            if (tile_tok + ST <= cur.kv_end && p.stream_only < 4) {
+                            if (tile_tok + ST <= cur.kv_end && !(p.debug & 8)) {
                                 mbar_arrive_expect_tx(bar, G::kStageBytes);
 #pragma unroll
                                 for (int b = 0; b < G::kBoxesPerPlane; ++b) {
@@ -533,7 +642,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                                 for (int b = 0; b < G::kBoxesPerPlane; ++b) {
                                     if (tile_tok + b * G::kBoxRows < cur.kv_end) ++boxes_needed;
                                 }
-                                if (p.stream_only >= 4) boxes_needed = 0;
+                                if (p.debug & 8) boxes_needed = 0;
                                 mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
 #pragma unroll
                                 for (int b = 0; b < G::kBoxesPerPlane; ++b) {
@@ -633,6 +742,10 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             const uint32_t t_tok_begin = ts->tok_begin, t_num_toks = ts->num_toks;
             const uint32_t t_kv_begin = ts->kv_begin, t_kv_end = ts->kv_end;
             const uint32_t t_tile_begin = ts->tile_begin, t_num_tiles = ts->num_tiles;
+            const uint32_t t_group = ts->group, t_part_begin = ts->part_begin, t_part_count = ts->part_count;
+            // fused reduce: a Q range with a single partial needs no merge, its task writes the final output
+            const bool fused = p.cu != nullptr;
+            const bool write_final = p.direct != 0 || (fused && t_part_count == 1);
 
             // ---- per-thread row bounds: rows g and g + 8 of row tile mt
             uint32_t lo[NROW], hi[NROW];
@@ -690,7 +803,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     my_parity ^= 1;
                 }
                 if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p.status)) continue;
-                if (p.stream_only && p.stream_only < 4) {
+                if (p.debug & 1) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
                     continue;
@@ -735,7 +848,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 float s[NT][4];
 #pragma unroll
                 for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-                const uint32_t knock = p.stream_only >= 4 ? p.stream_only - 4 : 0u;  // measurement aid
+                const uint32_t knock = (p.debug >> 4) & 7;  // measurement aid
                 if (!(knock & 1))
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
@@ -863,7 +976,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             }
             stage_counter += t_num_tiles;
 
-            if (p.stream_only >= 2 && p.stream_only < 4) {
+            if (p.debug & 2) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
                 continue;
@@ -988,7 +1101,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     }
                     v0 *= inv_l[i];
                     v1 *= inv_l[i];
-                    if (p.direct) {
+                    if (write_final) {
                         T* dst = reinterpret_cast<T*>(p.out) +
                                  (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + n * 8 + tq * 2;
                         *reinterpret_cast<uint32_t*>(dst) = pack2<T>(v0, v1);
@@ -996,10 +1109,29 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         *reinterpret_cast<float2*>(p.partial_out + index * D + n * 8 + tq * 2) = make_float2(v0, v1);
                     }
                 }
-                if (!p.direct && part == 0 && tq == 0) {
+                if (!write_final && part == 0 && tq == 0) {
                     p.partial_sum[index] = l_all[i];
                     // the running maximum is a raw dot product; publish the natural-log-domain logit (dot * scale)
                     p.partial_max[index] = l_all[i] > 0.0f ? m_all[i] * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
+                }
+            }
+            // ---- fused reduce: the CTA that publishes the last partial of a (Q range, KV head, head range)
+            // group merges the group's partials (they are hot in L2) and writes the final output. Nobody waits:
+            // every CTA counts its arrival and moves on; the last one does the merge and re-zeroes the counter.
+            if (fused && t_part_count > 1) {
+                consumer_barrier<3>(NCW * 32);     // every consumer thread has issued its partial stores
+                if (threadIdx.x == 0) {
+                    __threadfence();               // cumulative: orders the whole CTA's stores before the count
+                    const uint32_t seen = (p.debug & 256) ? 0u : atomicAdd(p.arrivals + t_group, 1u);
+                    const uint32_t last = (seen + 1 == t_part_count && !(p.debug & 128)) ? 1u : 0u;
+                    if (last) p.arrivals[t_group] = 0;
+                    *last_flag = last;
+                }
+                consumer_barrier<3>(NCW * 32);
+                if (*last_flag) {
+                    __threadfence();
+                    reduce_group<T, D>(p, t_tok_begin, t_num_toks, t_head_begin, t_num_heads, t_part_begin, t_part_count,
+                                       threadIdx.x, NCW * 32);
                 }
             }
             // ---- hand the task slot (descriptor + Q rows) back to the producer

@@ -63,6 +63,12 @@ class GQAAttention:
         self.partial_exp_sums = Buffer.new_zeroed(device, states * 4)
         self.partial_max_logits = Buffer.new_zeroed(device, states * 4)
         self.partial_output = Buffer.new_zeroed(device, states * core.head_dim * 4)
+        # arrival counters of the fused map + reduce launch: one per (Q-token tile, KV head, Q-head range);
+        # zero here, and every launch leaves them zero
+        self.arrival_counters = Buffer.new_zeroed(device, max(limits.max_tokens, 1) * core.num_q_heads * 4)
+        # False: map and reduce as two launches, the reference's form and the faster one on a saturated memory
+        # system; True: one launch whose last-arriving CTA of a partial range merges it
+        self.fused = False
         self._computes = {}
         self.selection: Selection | None = None
 
@@ -117,13 +123,19 @@ class GQAAttention:
         execution = meta.variant()
         if execution.kind == sdpa.MapKernelKind.SlicedKv:
             compute = self._sliced_kv(shape, execution)
-            compute.invoke_map(stream, sliced_kv.MapBuffers(
+            map_buffers = sliced_kv.MapBuffers(
                 q, kv_pages, meta.req_slots(), page_ids, meta.sdpa_map_task_templates(), self.partial_exp_sums,
-                self.partial_max_logits, self.partial_output), gqa_layer_index, shape.num_tokens,
-                shape.num_sdpa_map_task_templates)
-            compute.invoke_reduce(stream, sliced_kv.ReduceBuffers(
+                self.partial_max_logits, self.partial_output)
+            reduce_buffers = sliced_kv.ReduceBuffers(
                 self.partial_exp_sums, self.partial_max_logits, self.partial_output, meta.cu_sdpa_partial_outputs(),
-                output), shape.num_tokens)
+                output)
+            if self.fused:
+                compute.invoke_map_reduce(stream, map_buffers, reduce_buffers, self.arrival_counters, gqa_layer_index,
+                                          shape.num_tokens, shape.num_sdpa_map_task_templates)
+                return 1
+            compute.invoke_map(stream, map_buffers, gqa_layer_index, shape.num_tokens,
+                               shape.num_sdpa_map_task_templates)
+            compute.invoke_reduce(stream, reduce_buffers, shape.num_tokens)
             return 2
         if meta.direct_output():
             compute = self._sliced_q(shape, execution, True)
@@ -132,13 +144,19 @@ class GQAAttention:
                 meta.sdpa_map_task_templates(), output), gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles)
             return 1
         compute = self._sliced_q(shape, execution, False)
-        compute.invoke_map(stream, sliced_q.MapBuffers(
+        map_buffers = sliced_q.MapBuffers(
             q, kv_pages, meta.req_slots(), page_ids, meta.visible_kv_token_ranges(), meta.q_token_ranges(),
-            meta.sdpa_map_task_templates(), self.partial_output, self.partial_exp_sums, self.partial_max_logits),
-            gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates)
-        compute.invoke_reduce(stream, sliced_q.ReduceBuffers(
+            meta.sdpa_map_task_templates(), self.partial_output, self.partial_exp_sums, self.partial_max_logits)
+        reduce_buffers = sliced_q.ReduceBuffers(
             self.partial_output, self.partial_exp_sums, self.partial_max_logits, meta.q_token_ranges(),
-            meta.cu_sdpa_partial_outputs(), output), shape.num_q_token_tiles)
+            meta.cu_sdpa_partial_outputs(), output)
+        if self.fused:
+            compute.invoke_map_reduce(stream, map_buffers, reduce_buffers, self.arrival_counters, gqa_layer_index,
+                                      shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates)
+            return 1
+        compute.invoke_map(stream, map_buffers, gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles,
+                           shape.num_sdpa_map_task_templates)
+        compute.invoke_reduce(stream, reduce_buffers, shape.num_q_token_tiles)
         return 2
 
     # -- end-to-end call with host buffers -----------------------------------------------------------

@@ -143,6 +143,20 @@ class Compute:
     def invoke_reduce(self, stream: Stream, buffers: ReduceBuffers, num_active_tokens: int) -> None:
         abi.call("kh_sliced_kv_reduce", self.handle, stream.handle, C.byref(buffers.to_c()), num_active_tokens)
 
+    def arrival_counter_bytes(self) -> int:
+        out = C.c_uint64()
+        abi.call("kh_sliced_kv_arrival_counter_bytes", C.byref(self.config.to_c()), C.byref(self.execution.to_c()),
+                 C.byref(self.shape.to_c()), C.byref(out))
+        return out.value
+
+    def invoke_map_reduce(self, stream: Stream, map_buffers: MapBuffers, reduce_buffers: ReduceBuffers,
+                          arrival_counters: Buffer, page_table_index: int, num_active_tokens: int,
+                          num_active_kv_splits: int) -> None:
+        """``invoke_map`` + ``invoke_reduce`` in one launch (the last block of every group merges it)."""
+        abi.call("kh_sliced_kv_map_reduce", self.handle, stream.handle, C.byref(map_buffers.to_c()),
+                 C.byref(reduce_buffers.to_c()), arrival_counters.ref, page_table_index, num_active_tokens,
+                 num_active_kv_splits)
+
     def __del__(self):
         try:
             if self.handle:

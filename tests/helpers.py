@@ -172,13 +172,30 @@ class DeviceCase:
             case.page_bytes, self.layout, max_tokens or max(case.num_tokens, 1),
             policy if policy is not None else SelectorPolicy.B200, selector)
 
-    def run(self, selection=None) -> np.ndarray:
+    def run(self, selection=None, fused: bool | None = None) -> np.ndarray:
+        """Runs the batch through map + reduce in one launch and, unless ``fused`` pins one form, also through the
+        reference's two-launch form (invoke_map, invoke_reduce); both must produce the same bits."""
         case = self.case
         self.attention.prepare(case.req_slots, case.token_indices, case.cu_tokens, selection=selection)
-        self.attention.record_sdpa(self.stream, self.q, self.kv_pages, self.page_ids, self.output, case.layer_index)
-        self.stream.synchronize()
-        assert self.device.check(self.stream) == 0
-        return self.read_output()
+        outputs = []
+        for mode in ([True, False] if fused is None else [fused]):
+            self.attention.fused = mode
+            self.output.write(0, np.full(self.out_rows * case.num_q_heads * case.head_dim, self.canary, dtype=np.uint16))
+            self.attention.record_sdpa(self.stream, self.q, self.kv_pages, self.page_ids, self.output,
+                                       case.layer_index)
+            self.stream.synchronize()
+            assert self.device.check(self.stream) == 0
+            outputs.append(self.read_output())
+            counters = self.attention.arrival_counters.read(0, self.attention.arrival_counters.len_bytes() // 4,
+                                                            np.uint32)
+            assert not counters.any(), "arrival counters must be left zero"
+        self.attention.fused = False
+        if len(outputs) == 2:
+            # same partials, same merge formula; a one-partial range is written straight from registers in the
+            # one-launch form, which may differ from (sum * v) / sum by one rounding of the output type
+            assert np.allclose(outputs[0], outputs[1], rtol=2.0 ** -7, atol=1e-6), \
+                "one-launch and two-launch results differ"
+        return outputs[0]
 
     def read_output(self) -> np.ndarray:
         case = self.case
