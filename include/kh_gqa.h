@@ -397,6 +397,42 @@ KH_API kh_status kh_sliced_kv_arrival_counter_bytes(const kh_sliced_kv_config* c
                                                     const kh_execution_variant* execution,
                                                     const kh_sliced_kv_shape* shape, uint64_t* out);
 
+/* ---- SlicedKv attention on scratch the library holds: no allocation on any call ---------------
+ * No counterpart in the reference, whose layer owners allocate the partial-state scratch themselves
+ * (EM/attn/gqa/scratch.rs:49-83). This entry is for a host that cannot hand the library device memory for the
+ * partials and must not have it allocate either: an executor whose device arena is sized and frozen at start-up, a
+ * step loop with a latency bound (a device allocation or free synchronises the whole GPU), or a caller that is
+ * already inside a region where allocation is not allowed. It computes what kh_sliced_kv_map followed by
+ * kh_sliced_kv_reduce compute, bit for bit, with the partial statistics and partial outputs in one array that is part
+ * of the loaded library image (KH_STATIC_PARTIALS_BYTES per GPU, present from module load, never freed).
+ *  - Limit: num_active_kv_splits * num_q_heads * (head_dim + 2) * 4 bytes (rounded up to 256-byte sections) must
+ *    fit KH_STATIC_PARTIALS_BYTES; a larger batch is refused with KH_RESOURCE_EXHAUSTED and the message names the
+ *    bytes needed - use kh_sliced_kv_map / kh_sliced_kv_reduce with buffers of your own for those.
+ *  - The first call on each GPU looks up the array's address (set-up; no launch is involved), and the first call
+ *    of a compute object with a new Q buffer or KV pool encodes their tensor maps on the host. Make one call per
+ *    GPU and buffer pair before any stream capture or timed region; later calls only launch kernels.
+ *  - All calls on one GPU share the array. Nothing in it has to be zero: the map stage writes every partial that
+ *    the reduce stage of the same call reads. Two calls whose kernels can overlap on the GPU (different streams
+ *    without an ordering between them) race on it; calls ordered on one stream, or by events, are safe. */
+#define KH_STATIC_PARTIALS_BYTES (32u << 20)
+
+typedef struct kh_sliced_kv_static_buffers {
+    kh_buffer_ref q;
+    kh_buffer_ref kv_pages;
+    kh_buffer_ref req_slots;
+    kh_buffer_ref page_ids;
+    kh_buffer_ref sdpa_map_task_templates;
+    kh_buffer_ref cu_sdpa_partial_outputs;
+    kh_buffer_ref output;
+} kh_sliced_kv_static_buffers;
+
+KH_API kh_status kh_sliced_kv_attend_static(kh_sliced_kv* compute, kh_stream* stream,
+                                            const kh_sliced_kv_static_buffers* buffers, uint32_t page_table_index,
+                                            uint32_t num_active_tokens, uint32_t num_active_kv_splits);
+/* Bytes of the shared array a call with these counts needs (the quantity checked against the limit). */
+KH_API kh_status kh_sliced_kv_static_bytes_needed(const kh_sliced_kv_config* config, uint32_t num_active_kv_splits,
+                                                  uint64_t* out);
+
 /* ---- SlicedQ compute: BM/components/gqa/sdpa/sliced_q.rs ------------------------------------ */
 /* sliced_q::Config (sliced_q.rs:145-153) plus kv_dtype. */
 typedef struct kh_sliced_q_config {

@@ -112,6 +112,14 @@ class SlicedKvReduceBuffersC(C.Structure):
         "partial_exp_sums", "partial_max_logits", "partial_output", "cu_sdpa_partial_outputs", "output")]
 
 
+class SlicedKvStaticBuffersC(C.Structure):
+    _fields_ = [(name, BufferRef) for name in (
+        "q", "kv_pages", "req_slots", "page_ids", "sdpa_map_task_templates", "cu_sdpa_partial_outputs", "output")]
+
+
+STATIC_PARTIALS_BYTES = 32 << 20  # KH_STATIC_PARTIALS_BYTES
+
+
 class SlicedKvSizesC(C.Structure):
     _fields_ = [("q_bytes", C.c_uint64), ("req_slots_bytes", C.c_uint64), ("page_ids_bytes", C.c_uint64),
                 ("sdpa_map_task_templates_bytes", C.c_uint64), ("cu_sdpa_partial_outputs_bytes", C.c_uint64),
@@ -214,6 +222,8 @@ PROTOTYPES = {
     "kh_sliced_kv_reduce": [_vp, _vp, P(SlicedKvReduceBuffersC), _u32],
     "kh_sliced_kv_map_reduce": [_vp, _vp, P(SlicedKvMapBuffersC), P(SlicedKvReduceBuffersC), BufferRef, _u32, _u32, _u32],
     "kh_sliced_kv_arrival_counter_bytes": [P(SlicedKvConfigC), P(ExecutionVariantC), P(SlicedKvShapeC), P(C.c_uint64)],
+    "kh_sliced_kv_attend_static": [_vp, _vp, P(SlicedKvStaticBuffersC), _u32, _u32, _u32],
+    "kh_sliced_kv_static_bytes_needed": [P(SlicedKvConfigC), _u32, P(C.c_uint64)],
     "kh_sliced_q_sizes_get": [P(SlicedQConfigC), P(ExecutionVariantC), P(SlicedQShapeC), P(SlicedQSizesC)],
     "kh_sliced_q_create": [_vp, P(SlicedQConfigC), P(ExecutionVariantC), P(SlicedQShapeC), C.c_int32, P(_vp)],
     "kh_sliced_q_destroy": [_vp],

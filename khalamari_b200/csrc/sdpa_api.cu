@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <vector>
 
 #include "common.h"
@@ -1147,3 +1148,118 @@ kh_status kh_combine_partials(kh_device* device, kh_stream* stream, uint32_t num
 }
 
 }  // extern "C"
+
+// ---- SlicedKv attention on library-held scratch ------------------------------------------------
+// The partial statistics and partial outputs of one map + reduce pair live in an array of the module image:
+// nothing is allocated or freed on any call. Section layout for `rows` = active templates * Q heads, each section
+// starting on a 256-byte boundary: [exp sums: rows f32][max logits: rows f32][partial output: rows * D f32].
+namespace kh {
+
+constexpr uint64_t kStaticPartialFloats = KH_STATIC_PARTIALS_BYTES / 4;
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+
+constexpr int kStaticMaxDevices = 64;
+static float* g_static_partials_at[kStaticMaxDevices];  // address of the array on each GPU, looked up once
+static std::mutex g_static_mutex;
+
+static uint64_t static_section_floats(uint64_t rows) { return (rows + 63) / 64 * 64; }
+
+static uint64_t static_bytes_needed(uint32_t num_q_heads, uint32_t head_dim, uint32_t num_active_kv_splits) {
+    const uint64_t rows = uint64_t(num_active_kv_splits) * num_q_heads;
+    return (2 * static_section_floats(rows) + static_section_floats(rows * head_dim)) * 4;
+}
+
+static float* static_partials_on(const kh_device* device) {
+    KH_REQUIRE(device->ordinal >= 0 && device->ordinal < kStaticMaxDevices,
+               "device ordinal %d is beyond the %d GPUs the shared partial array is tracked for", device->ordinal,
+               kStaticMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    float*& slot = g_static_partials_at[device->ordinal];
+    if (slot == nullptr) {
+        use_device(device);
+        float* address = nullptr;
+        KH_CUDA(cudaGetSymbolAddress((void**)&address, g_static_partials));
+        KH_REQUIRE(address != nullptr && (reinterpret_cast<uintptr_t>(address) & 255) == 0,
+                   "the shared partial array has no 256-byte aligned device address");
+        slot = address;
+    }
+    return slot;
+}
+
+}  // namespace kh
+
+kh_status kh_sliced_kv_static_bytes_needed(const kh_sliced_kv_config* config, uint32_t num_active_kv_splits,
+                                           uint64_t* out) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(config && out, "null argument");
+        sliced_kv_sizes(*config, kh_sliced_kv_shape{1, 1});
+        *out = static_bytes_needed(config->num_q_heads, config->head_dim, num_active_kv_splits);
+        return KH_OK;
+    });
+}
+
+kh_status kh_sliced_kv_attend_static(kh_sliced_kv* compute, kh_stream* stream,
+                                     const kh_sliced_kv_static_buffers* buffers, uint32_t page_table_index,
+                                     uint32_t num_active_tokens, uint32_t num_active_kv_splits) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(compute && stream && buffers, "null argument");
+        const kh_sliced_kv_config& config = compute->config;
+        const kh_sliced_kv_sizes& z = compute->sizes;
+        const kh_sliced_kv_shape& s = compute->shape;
+        KH_REQUIRE(stream->device == compute->common.device, "stream does not belong to the compute's device");
+        KH_REQUIRE(page_table_index < config.page_table_layout.num_gqa_layers, "page_table_index %u out of range",
+                   page_table_index);
+        KH_REQUIRE(num_active_tokens >= 1 && num_active_tokens <= s.num_total_tokens,
+                   "num_active_tokens %u outside [1, %u]", num_active_tokens, s.num_total_tokens);
+        KH_REQUIRE(num_active_kv_splits <= s.num_total_sdpa_map_task_templates,
+                   "num_active_kv_splits %u outside [0, %u]", num_active_kv_splits,
+                   s.num_total_sdpa_map_task_templates);
+        const uint64_t bytes = static_bytes_needed(config.num_q_heads, config.head_dim, num_active_kv_splits);
+        if (bytes > KH_STATIC_PARTIALS_BYTES) {
+            raise(KH_RESOURCE_EXHAUSTED,
+                  "%u map task templates x %u Q heads x head_dim %u need %llu bytes of partial state; the shared array "
+                  "holds %u: call kh_sliced_kv_map and kh_sliced_kv_reduce with your own partial buffers",
+                  num_active_kv_splits, config.num_q_heads, config.head_dim, (unsigned long long)bytes,
+                  unsigned(KH_STATIC_PARTIALS_BYTES));
+        }
+        need(buffers->q, z.q_bytes, "q");
+        need(buffers->kv_pages, config.page_bytes, "kv_pages");
+        need(buffers->req_slots, z.req_slots_bytes, "req_slots");
+        need(buffers->page_ids, z.page_ids_bytes, "page_ids");
+        need(buffers->sdpa_map_task_templates, z.sdpa_map_task_templates_bytes, "sdpa_map_task_templates");
+        need(buffers->cu_sdpa_partial_outputs, z.cu_sdpa_partial_outputs_bytes, "cu_sdpa_partial_outputs");
+        need(buffers->output, z.q_bytes, "output");
+
+        float* base = static_partials_on(compute->common.device);
+        const uint64_t rows = uint64_t(num_active_kv_splits) * config.num_q_heads;
+        float* exp_sums = base;
+        float* max_logits = exp_sums + static_section_floats(rows);
+        float* partial_output = max_logits + static_section_floats(rows);
+
+        MapParams p{};
+        p.req_slots = static_cast<const uint32_t*>(buffers->req_slots.ptr);
+        p.page_ids = static_cast<const uint32_t*>(buffers->page_ids.ptr);
+        p.templates = static_cast<const uint32_t*>(buffers->sdpa_map_task_templates.ptr);
+        p.partial_out = partial_output;
+        p.partial_sum = exp_sums;
+        p.partial_max = max_logits;
+        p.num_active_tokens = num_active_tokens;
+        p.num_active_q_tiles = num_active_tokens;
+        p.layer_index = page_table_index;
+        launch_map(compute->common, stream, p, buffers->q, buffers->kv_pages, num_active_kv_splits);
+
+        ReduceParams r{};
+        r.partial_sum = exp_sums;
+        r.partial_max = max_logits;
+        r.partial_out = partial_output;
+        r.cu = static_cast<const uint32_t*>(buffers->cu_sdpa_partial_outputs.ptr);
+        r.out = buffers->output.ptr;
+        r.num_q_heads = config.num_q_heads;
+        r.head_dim = config.head_dim;
+        r.max_q_tokens = 1;
+        r.num_active_ranges = num_active_tokens;
+        r.num_active_tokens = num_active_tokens;
+        launch_reduce(config.dtype, r, num_active_tokens, stream->stream);
+        return KH_OK;
+    });
+}

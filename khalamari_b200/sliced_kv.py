@@ -100,6 +100,23 @@ class ReduceBuffers:
             *[getattr(self, name).ref for name, _ in abi.SlicedKvReduceBuffersC._fields_])
 
 
+@dataclass
+class StaticBuffers:
+    """Buffers of ``Compute.invoke_attend_static``: those of map and reduce without the partial state."""
+
+    q: Buffer
+    kv_pages: Buffer
+    req_slots: Buffer
+    page_ids: Buffer
+    sdpa_map_task_templates: Buffer
+    cu_sdpa_partial_outputs: Buffer
+    output: Buffer
+
+    def to_c(self) -> abi.SlicedKvStaticBuffersC:
+        return abi.SlicedKvStaticBuffersC(
+            *[getattr(self, name).ref for name, _ in abi.SlicedKvStaticBuffersC._fields_])
+
+
 class Scratch:
     """``Scratch`` (sliced_kv.rs:256-305): partial statistics and partial output (f32 here)."""
 
@@ -156,6 +173,18 @@ class Compute:
         abi.call("kh_sliced_kv_map_reduce", self.handle, stream.handle, C.byref(map_buffers.to_c()),
                  C.byref(reduce_buffers.to_c()), arrival_counters.ref, page_table_index, num_active_tokens,
                  num_active_kv_splits)
+
+    def static_bytes_needed(self, num_active_kv_splits: int) -> int:
+        out = C.c_uint64()
+        abi.call("kh_sliced_kv_static_bytes_needed", C.byref(self.config.to_c()), num_active_kv_splits, C.byref(out))
+        return out.value
+
+    def invoke_attend_static(self, stream: Stream, buffers: StaticBuffers, page_table_index: int,
+                             num_active_tokens: int, num_active_kv_splits: int) -> None:
+        """``invoke_map`` + ``invoke_reduce`` with the partial state in the array the library holds
+        (``abi.STATIC_PARTIALS_BYTES`` per GPU): no allocation on any call, one call in flight per GPU."""
+        abi.call("kh_sliced_kv_attend_static", self.handle, stream.handle, C.byref(buffers.to_c()), page_table_index,
+                 num_active_tokens, num_active_kv_splits)
 
     def __del__(self):
         try:
