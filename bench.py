@@ -47,6 +47,20 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_map_kernel launch over its algorithmic K/V bytes, from the
+# committed capture of the decode workload at batch 16 (profiles/sdpa_map_kernel_decode_b16_full.md: 317.62 MB over
+# 309.67 MB); traffic grows with the tokens processed, so the ratio carries to the full batch.
+MAP_TRAFFIC_PER_KV_BYTE = 317.62 / 309.67
+
+
+def traffic_estimate(spec, kv_bytes):
+    """Bytes one map-kernel launch moves to and from DRAM, scaled from the profiler capture; only for the decode
+    workload that was captured (None elsewhere)."""
+    if spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512:
+        return int(kv_bytes * MAP_TRAFFIC_PER_KV_BYTE)
+    return None
+
+
 def contexts_for(spec, rank):
     if "contexts" in spec:
         return list(spec["contexts"])
@@ -232,8 +246,8 @@ def run_ours(args):
     shape = attention.metadata.replay_shape()
     kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * 2  # q_len new tokens are already in the cache
 
-    def step():
-        return attention.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
+    def step(after_map=None):
+        return attention.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0, after_map)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -246,13 +260,14 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    # per step: start, end of the map kernel, end of the step (after the reduce kernel)
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches = 0
     sampler.__enter__()
     if True:
         # untimed ramp: keep the GPU under this load for about half a second so that clocks settle and the
         # sampler sees them before the (short) timed region starts
-        ramp_end = time.perf_counter() + 0.5
+        ramp_end = time.perf_counter() + args.ramp_ms * 1e-3
         while time.perf_counter() < ramp_end:
             for _ in range(20):
                 step()
@@ -262,16 +277,19 @@ def run_ours(args):
         t0 = time.perf_counter()
         for i in range(args.steps):
             events[i][0].record(torch_stream)
-            launches += step()  # one launch: map tasks plus the in-kernel merge of every completed group
-            events[i][1].record(torch_stream)
+            launches += step(lambda i=i: events[i][1].record(torch_stream))
+            events[i][2].record(torch_stream)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         barrier()
         timed_window = (t0, t1)
     device.check(stream)
-    step_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
-    map_ms = step_ms  # the step is one kernel launch
-    total_ms = events[0][0].elapsed_time(events[-1][1])
+    step_ms = [events[i][0].elapsed_time(events[i][2]) for i in range(args.steps)]
+    if args.fused or attention.metadata.direct_output():
+        map_ms = step_ms  # the step is one kernel launch
+    else:
+        map_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
+    total_ms = events[0][0].elapsed_time(events[-1][2])
     ms_per_step = total_ms / args.steps
 
     # ---- end to end through the component seam with host buffers -------------------------------------
@@ -323,7 +341,7 @@ def run_ours(args):
             "tokens_per_s": round(total_tokens / (ms_per_step * 1e-3), 1),
             "hbm_frac": round(value / world / peak, 4),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"of {peak_kind}",
+                         "frac": round(achieved / peak, 4), "traffic": traffic_estimate(spec, kv_bytes), "peak_source": f"of {peak_kind}",
                          "kernel": "sdpa_map_kernel", "kernel_ms": round(map_ms_mean, 5)},
             "e2e": {"value": round(total_kv_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 5),
@@ -427,6 +445,8 @@ def main():
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")
     parser.add_argument("--pool-pages", type=int, default=0, help="override the page pool size (profiling captures)")
     parser.add_argument("--partition", type=int, default=-1, help="override the split-KV partition (0: selector)")
+    parser.add_argument("--ramp-ms", type=float, default=500.0,
+                        help="untimed load before the timed steps so that clocks settle (0 for profiler runs)")
     parser.add_argument("--fused", action="store_true",
                         help="map and reduce in one launch (last-arriver merge) instead of the reference's two")
     parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")

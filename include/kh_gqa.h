@@ -550,6 +550,15 @@ KH_API kh_status kh_combine_partials(kh_device* device, kh_stream* stream, uint3
                                      kh_buffer_ref partial_output, kh_dtype out_dtype, kh_buffer_ref output,
                                      kh_buffer_ref out_exp_sums, kh_buffer_ref out_max_logits);
 
+/* The same merge over records gathered from several GPUs. Each GPU contributes one record of
+ * num_rows * (head_dim + 2) f32: [exp sums: num_rows][max logits: num_rows][output: num_rows x head_dim], which
+ * is what kh_combine_partials writes when its three outputs point into one buffer at those offsets; `packed`
+ * holds `num_partials` such records back to back, the layout an all-gather of one record per rank leaves in
+ * local memory. One collective per attention call, then this merge on local memory; no peer memory is read. */
+KH_API kh_status kh_combine_packed_partials(kh_device* device, kh_stream* stream, uint32_t num_partials,
+                                            uint32_t num_rows, uint32_t head_dim, kh_buffer_ref packed,
+                                            kh_dtype out_dtype, kh_buffer_ref output);
+
 #ifdef __cplusplus
 }
 #endif

@@ -236,6 +236,7 @@ PROTOTYPES = {
     "kh_device_check": [_vp, _vp, P(_u32)],
     "kh_combine_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, BufferRef, BufferRef, _u32, BufferRef, BufferRef,
                             BufferRef],
+    "kh_combine_packed_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, _u32, BufferRef],
 }
 _SPECIAL = {
     "kh_last_error": ([C.c_char_p, C.c_size_t], C.c_size_t),

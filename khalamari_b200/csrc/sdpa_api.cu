@@ -65,6 +65,8 @@ struct ReduceParams {
     uint32_t num_active_ranges;
     uint32_t num_active_tokens;
     uint32_t fixed_partials;
+    uint64_t stat_stride;      // floats between consecutive partials of a row; 0: dense [partial][Hq][maxq]
+    uint64_t out_stride;       // same for the partial outputs; 0: dense [partial][Hq][maxq][D]
 };
 
 template <typename T>
@@ -103,14 +105,15 @@ __global__ void __launch_bounds__(128) sdpa_reduce_kernel(const ReduceParams p) 
     const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
     const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
     const uint32_t D = p.head_dim;
-    const uint64_t stride = uint64_t(p.num_q_heads) * p.max_q_tokens;
+    const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads) * p.max_q_tokens;
+    const uint64_t out_stride = p.out_stride != 0 ? p.out_stride : stride * D;
     for (uint32_t local = threadIdx.x * 4; local < num_toks * D; local += blockDim.x * 4) {
         const uint32_t tok = local / D;
         const uint32_t d = local % D;
         const uint64_t first_index = (uint64_t(first) * p.num_q_heads + head) * p.max_q_tokens + tok;
         float merged_sum, merged_max;
         const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first_index, stride,
-                                              last - first, D, d, &merged_sum, &merged_max);
+                                              out_stride, last - first, D, d, &merged_sum, &merged_max);
         const uint64_t out_row = uint64_t(tok_begin + tok) * p.num_q_heads + head;
         store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
         if (p.out_sum != nullptr && d == 0) {
@@ -1137,6 +1140,40 @@ kh_status kh_combine_partials(kh_device* device, kh_stream* stream, uint32_t num
         p.out = output.ptr;
         p.out_sum = chain ? static_cast<float*>(out_exp_sums.ptr) : nullptr;
         p.out_max = chain ? static_cast<float*>(out_max_logits.ptr) : nullptr;
+        p.num_q_heads = num_rows;
+        p.head_dim = head_dim;
+        p.max_q_tokens = 1;
+        p.num_active_ranges = 1;
+        p.num_active_tokens = 1;
+        launch_reduce(out_dtype, p, 1, stream->stream);
+        return KH_OK;
+    });
+}
+
+kh_status kh_combine_packed_partials(kh_device* device, kh_stream* stream, uint32_t num_partials, uint32_t num_rows,
+                                     uint32_t head_dim, kh_buffer_ref packed, kh_dtype out_dtype,
+                                     kh_buffer_ref output) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(device && stream, "null argument");
+        KH_REQUIRE(stream->device == device, "stream does not belong to the device");
+        KH_REQUIRE(num_partials > 0 && num_rows > 0 && head_dim > 0, "combine needs partials, rows and a head dimension");
+        KH_REQUIRE(dtype_size(out_dtype) >= 2, "unsupported output dtype");
+        KH_REQUIRE(num_rows % 4 == 0 && head_dim % 4 == 0,
+                   "packed partials need rows and head_dim that are multiples of 4 (16-byte aligned sections)");
+        KH_REQUIRE((reinterpret_cast<uintptr_t>(packed.ptr) & 15) == 0, "packed partials must be 16-byte aligned");
+        const uint64_t record = uint64_t(num_rows) * (uint64_t(head_dim) + 2);
+        need(packed, uint64_t(num_partials) * record * 4, "packed");
+        need(output, uint64_t(num_rows) * head_dim * dtype_size(out_dtype), "output");
+        use_device(device);
+        const float* base = static_cast<const float*>(packed.ptr);
+        ReduceParams p{};
+        p.partial_sum = base;
+        p.partial_max = base + num_rows;
+        p.partial_out = base + 2 * uint64_t(num_rows);
+        p.fixed_partials = num_partials;
+        p.stat_stride = record;
+        p.out_stride = record;
+        p.out = output.ptr;
         p.num_q_heads = num_rows;
         p.head_dim = head_dim;
         p.max_q_tokens = 1;

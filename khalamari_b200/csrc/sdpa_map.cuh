@@ -226,11 +226,12 @@ __device__ __forceinline__ void store_out4(T* dst, float4 v) {
 // max = max_i m_i, weight_i = exp(m_i - max) * l_i (0 for an empty partial), out = sum_i weight_i o_i / sum_i weight_i.
 // Partials are taken eight at a time with all their loads issued together (the merge runs while the memory system
 // is saturated by K/V streaming, so dependent loads are what costs), carrying (max, sum, numerator) between groups.
+// Partial j of the row sits `j * index_stride` statistics and `j * out_stride` output floats after the first.
 // L2-only loads: the partials may have been written by other SMs during this launch.
 __device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, const float* partial_max,
                                                      const float* partial_out, uint64_t first_index,
-                                                     uint64_t index_stride, uint32_t count, uint32_t head_dim,
-                                                     uint32_t d, float* out_sum, float* out_max) {
+                                                     uint64_t index_stride, uint64_t out_stride, uint32_t count,
+                                                     uint32_t head_dim, uint32_t d, float* out_sum, float* out_max) {
     float run_max = -INFINITY, run_sum = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (uint32_t base = 0; base < count; base += 8) {
@@ -240,9 +241,10 @@ __device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, c
         for (int j = 0; j < 8; ++j) {
             const bool valid = base + j < count;
             const uint64_t index = first_index + uint64_t(base + j) * index_stride;
+            const uint64_t out_index = first_index * head_dim + uint64_t(base + j) * out_stride + d;
             mx[j] = valid ? __ldcg(partial_max + index) : -INFINITY;
             sm[j] = valid ? __ldcg(partial_sum + index) : 0.0f;
-            v[j] = valid ? __ldcg(reinterpret_cast<const float4*>(partial_out + index * head_dim + d))
+            v[j] = valid ? __ldcg(reinterpret_cast<const float4*>(partial_out + out_index))
                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
         float new_max = run_max;
@@ -294,8 +296,8 @@ __device__ __forceinline__ void reduce_group(const MapParams& p, uint32_t tok_be
         const uint32_t tok = row / num_heads;
         const uint32_t head = head_begin + row % num_heads;
         const uint64_t first = (uint64_t(part_begin) * p.num_q_heads + head) * p.max_q_tokens + tok;
-        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first, stride, part_count, D,
-                                              d, nullptr, nullptr);
+        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first, stride, stride * D,
+                                              part_count, D, d, nullptr, nullptr);
         T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(tok_begin + tok) * p.num_q_heads + head) * D + d;
         store_out4<T>(dst, acc);
     }

@@ -116,8 +116,9 @@ class GQAAttention:
 
     # -- GQA::record_sdpa (backend.rs:438-542) -----------------------------------------------------
     def record_sdpa(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer, output: Buffer,
-                    gqa_layer_index: int = 0) -> int:
-        """Enqueues the selected branch on ``stream`` and returns how many kernels it launched."""
+                    gqa_layer_index: int = 0, after_map=None) -> int:
+        """Enqueues the selected branch on ``stream`` and returns how many kernels it launched. ``after_map``,
+        when given, is called between the map and the reduce launch (a timing hook: record an event there)."""
         meta = self.metadata
         shape = meta.replay_shape()
         execution = meta.variant()
@@ -135,6 +136,8 @@ class GQAAttention:
                 return 1
             compute.invoke_map(stream, map_buffers, gqa_layer_index, shape.num_tokens,
                                shape.num_sdpa_map_task_templates)
+            if after_map is not None:
+                after_map()
             compute.invoke_reduce(stream, reduce_buffers, shape.num_tokens)
             return 2
         if meta.direct_output():
@@ -156,6 +159,8 @@ class GQAAttention:
             return 1
         compute.invoke_map(stream, map_buffers, gqa_layer_index, shape.num_tokens, shape.num_q_token_tiles,
                            shape.num_sdpa_map_task_templates)
+        if after_map is not None:
+            after_map()
         compute.invoke_reduce(stream, reduce_buffers, shape.num_q_token_tiles)
         return 2
 
