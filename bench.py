@@ -33,6 +33,8 @@ WORKLOADS = {
                pool_pages=40000, label="paged decode B64 Hq64/Hkv8/D128 bf16 ctx U[1024,8192] P16 part512"),
     "c3": dict(batch=32, q_len=4, hq=24, hkv=4, d=256, dtype="bf16", lo=4096, hi=32768, seed=2, partition=0,
                pool_pages=0, label="verify B32 q4 Hq24/Hkv4/D256 bf16 prefix U[4096,32768] P16"),
+    "c4": dict(batch=1, q_len=1, hq=16, hkv=2, d=256, dtype="bf16", lo=0, hi=0, seed=3, partition=0, pool_pages=0,
+               contexts=[1048576], label="one sequence, decode, Hq16/Hkv2/D256 bf16 P16, pages split in token order"),
     "c1": dict(batch=4, q_len=1, hq=16, hkv=2, d=256, dtype="f16", lo=0, hi=0, seed=0, partition=0, pool_pages=0,
                contexts=[128, 517, 1024, 2048], label="decode B4 Hq16/Hkv2/D256 fp16 ctx {128,517,1024,2048} P16"),
 }
@@ -360,6 +362,125 @@ def run_ours(args):
     return result
 
 
+def run_split_sequence(args):
+    """Workload c4: ONE long sequence whose pages are split in token order over the ranks (strong scaling). A step
+    is: local split-KV map, local merge into this rank's record, all-gather of the records (NCCL), merge of the
+    gathered records on every rank. Without --context the sequence holds 1,048,576 tokens."""
+    import torch
+    import torch.distributed as dist
+
+    from khalamari_b200 import split_kv
+    from khalamari_b200.device import Device, Dtype, Stream
+    from khalamari_b200.gqa import GQAAttention, GQACore
+    from khalamari_b200.request_page_table import GQAPageTableLayout
+    from khalamari_b200.selector import SelectorPolicy
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    spec = dict(WORKLOADS["c4"])
+    context = args.context or spec["contexts"][0]
+    begin, end = split_kv.split_context(context, world, PAGE)[rank]
+    local_len = end - begin
+    device = Device(local)
+    case = build_device_case(device, spec, [max(local_len, 1)], torch, spec["seed"] + 1000 * rank)
+    torch_stream = torch.cuda.current_stream()
+    stream = Stream(device, torch_stream.cuda_stream)
+    layout = GQAPageTableLayout(1, 1, case["num_blocks"], 1)
+    attention = GQAAttention(device, GQACore(spec["d"], spec["hq"], spec["hkv"], 1.0 / 16.0), Dtype.Bfloat16,
+                             2 * spec["hkv"] * PAGE * spec["d"] * 2, layout, 1, SelectorPolicy.B200)
+    decode = split_kv.SplitKvDecode(device, attention, world)
+    decode.prepare(0, local_len, args.partition if args.partition > 0 else None)
+    kv_bytes_local = local_len * 2 * spec["hkv"] * spec["d"] * 2
+
+    def step():
+        return decode.record_step(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
+
+    def local_only():
+        return decode.record_local(stream, case["d_q"], case["d_pool"], case["d_table"], 0)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    device.check(stream)
+    props = torch.cuda.get_device_properties(local)
+    sampler = ClockSampler(str(getattr(props, "uuid", "")) or None, local)
+    sampler.__enter__()
+    ramp_end = time.perf_counter() + args.ramp_ms * 1e-3
+    while time.perf_counter() < ramp_end:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    launches = 0
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        events[i][0].record(torch_stream)
+        launches += step()
+        events[i][1].record(torch_stream)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    step_ms = [a.elapsed_time(b) for a, b in events]
+    ms_per_step = events[0][0].elapsed_time(events[-1][1]) / args.steps
+    # the local part alone (map + local merge), to separate kernel time from the exchange
+    local_events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    for i in range(args.steps):
+        local_events[i][0].record(torch_stream)
+        local_only()
+        local_events[i][1].record(torch_stream)
+    torch.cuda.synchronize()
+    local_ms = float(np.mean([a.elapsed_time(b) for a, b in local_events]))
+    device.check(stream)
+    sampler.__exit__(None, None, None)
+    clock_summary = sampler.summary(t0, t1)
+    checksum = float(case["out"].float().abs().sum().item())
+    stats = torch.tensor([ms_per_step, local_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms_per_step, local_ms = stats.tolist()
+    result = None
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        total_bytes = context * 2 * spec["hkv"] * spec["d"] * 2
+        value = total_bytes / (ms_per_step * 1e-3) / 1e9
+        achieved = kv_bytes_local / (local_ms * 1e-3) / 1e9
+        record_bytes = split_kv.record_floats(spec["hq"], spec["d"]) * 4
+        result = {
+            "metric": "GQA decode KV-read GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": spec["label"], "context_tokens": context, "tokens_per_gpu": local_len,
+                       "map_tasks": attention.metadata.replay_shape().num_sdpa_map_task_templates * spec["hkv"],
+                       "l2": "inputs (KV pages read per step) larger than L2; no flush" if kv_bytes_local > 126e6
+                       else "per-GPU KV pages fit L2: not an HBM measurement",
+                       "parallelism": f"split-KV over {world} GPUs, all-gather of {record_bytes} B per rank"},
+            "tokens_per_s": round(1.0 / (ms_per_step * 1e-3), 1),
+            "hbm_frac": round(value / world / peak, 4),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel": "sdpa_map_kernel + local merge (rank 0)", "kernel_ms": round(local_ms, 5)},
+            "exchange_ms": round(ms_per_step - local_ms, 5),
+            "gpu_launches": launches, "clocks": clock_summary,
+            "step_ms_min_median_max": [round(min(step_ms), 5), round(sorted(step_ms)[len(step_ms) // 2], 5),
+                                       round(max(step_ms), 5)],
+            "output_checksum": checksum,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
 def cpu_inputs(spec, contexts, sample_requests, seed):
     rng = np.random.default_rng(seed)
     import oracle
@@ -450,8 +571,14 @@ def main():
     parser.add_argument("--fused", action="store_true",
                         help="map and reduce in one launch (last-arriver merge) instead of the reference's two")
     parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")
+    parser.add_argument("--context", type=int, default=0, help="workload c4: tokens of the one sequence")
     args = parser.parse_args()
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        result = run_reference(args)
+    elif args.workload == "c4":
+        result = run_split_sequence(args)
+    else:
+        result = run_ours(args)
     if result is not None:
         print(json.dumps(result), flush=True)
 

@@ -90,8 +90,12 @@ __device__ __forceinline__ void store4<__half>(__half* dst, float4 v) {
     *reinterpret_cast<uint2*>(dst) = packed;
 }
 
+constexpr uint32_t kReduceMaxThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(128) sdpa_reduce_kernel(const ReduceParams p) {
+__global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const ReduceParams p) {
+    __shared__ float4 shared_acc[kReduceMaxThreads];
+    __shared__ float2 shared_stat[kReduceMaxThreads];
     const uint32_t head = blockIdx.x;
     const uint32_t range = blockIdx.y;
     if (range >= p.num_active_ranges) return;
@@ -107,19 +111,59 @@ __global__ void __launch_bounds__(128) sdpa_reduce_kernel(const ReduceParams p) 
     const uint32_t D = p.head_dim;
     const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads) * p.max_q_tokens;
     const uint64_t out_stride = p.out_stride != 0 ? p.out_stride : stride * D;
-    for (uint32_t local = threadIdx.x * 4; local < num_toks * D; local += blockDim.x * 4) {
-        const uint32_t tok = local / D;
-        const uint32_t d = local % D;
-        const uint64_t first_index = (uint64_t(first) * p.num_q_heads + head) * p.max_q_tokens + tok;
-        float merged_sum, merged_max;
-        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first_index, stride,
-                                              out_stride, last - first, D, d, &merged_sum, &merged_max);
-        const uint64_t out_row = uint64_t(tok_begin + tok) * p.num_q_heads + head;
-        store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
-        if (p.out_sum != nullptr && d == 0) {
-            p.out_sum[out_row] = merged_sum;
-            p.out_max[out_row] = merged_max;
+    const uint32_t slots = num_toks * D / 4;  // float4 columns of this block's rows
+    // When the block has at least twice as many threads as columns, the partials of a row are divided among
+    // `subsets` thread groups (contiguous shares), merged through shared memory: the loads of a long partial
+    // list run side by side instead of one batch after another.
+    const uint32_t subsets = slots * 2 <= blockDim.x ? blockDim.x / slots : 1;
+    if (subsets == 1) {
+        for (uint32_t slot = threadIdx.x; slot < slots; slot += blockDim.x) {
+            const uint32_t tok = slot * 4 / D;
+            const uint32_t d = slot * 4 % D;
+            const uint64_t first_index = (uint64_t(first) * p.num_q_heads + head) * p.max_q_tokens + tok;
+            float merged_sum, merged_max;
+            const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first_index, stride,
+                                                  out_stride, last - first, D, d, &merged_sum, &merged_max);
+            const uint64_t out_row = uint64_t(tok_begin + tok) * p.num_q_heads + head;
+            store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
+            if (p.out_sum != nullptr && d == 0) {
+                p.out_sum[out_row] = merged_sum;
+                p.out_max[out_row] = merged_max;
+            }
         }
+        return;
+    }
+    const uint32_t slot = threadIdx.x % slots;
+    const uint32_t subset = threadIdx.x / slots;
+    const uint32_t tok = slot * 4 / D;
+    const uint32_t d = slot * 4 % D;
+    const uint32_t count = last - first;
+    const uint32_t share = (count + subsets - 1) / subsets;
+    MergeState state = merge_state_empty();
+    if (subset < subsets) {
+        const uint32_t begin = min(subset * share, count);
+        const uint32_t mine = min(share, count - begin);
+        const uint64_t first_index = (uint64_t(first) * p.num_q_heads + head) * p.max_q_tokens + tok;
+        merge_partials_accumulate(state, p.partial_sum + uint64_t(begin) * stride, p.partial_max + uint64_t(begin) * stride,
+                                  p.partial_out + uint64_t(begin) * out_stride, first_index, stride, out_stride, mine,
+                                  D, d);
+    }
+    shared_acc[threadIdx.x] = state.acc;
+    shared_stat[threadIdx.x] = make_float2(state.sum, state.max);
+    __syncthreads();
+    if (subset != 0) return;
+    for (uint32_t other = 1; other < subsets; ++other) {
+        const uint32_t source = other * slots + slot;
+        const float2 stat = shared_stat[source];
+        merge_state_combine(state, MergeState{shared_acc[source], stat.x, stat.y});
+    }
+    float merged_sum, merged_max;
+    const float4 acc = merge_state_finish(state, &merged_sum, &merged_max);
+    const uint64_t out_row = uint64_t(tok_begin + tok) * p.num_q_heads + head;
+    store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
+    if (p.out_sum != nullptr && d == 0) {
+        p.out_sum[out_row] = merged_sum;
+        p.out_max[out_row] = merged_max;
     }
 }
 
@@ -336,7 +380,9 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
 template <typename T>
 static void launch_reduce_typed(const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {
     dim3 grid(p.num_q_heads, num_ranges, 1);
-    sdpa_reduce_kernel<T><<<grid, 128, 0, stream>>>(p);
+    // a fixed, long partial list per row (the cross-slice and cross-GPU merges) gets the widest block
+    const uint32_t threads = (p.cu == nullptr && p.fixed_partials > 32) ? kReduceMaxThreads : 128;
+    sdpa_reduce_kernel<T><<<grid, threads, 0, stream>>>(p);
 }
 
 static void launch_reduce(kh_dtype dtype, const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {

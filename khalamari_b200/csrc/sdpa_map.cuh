@@ -13,7 +13,7 @@
 //  - publishes the task descriptor and the task's Q rows (TMA tile copy, 128-byte swizzle) into a
 //    small task ring, and
 //  - streams the task's K and V page chunks from the paged pool into a ring of shared-memory stages
-//    with TMA tile copies (128-byte swizzle, one mbarrier per stage, no multicast). A page chunk
+//    with TMA tile copies (128-byte swizzle, one mbarrier per stage, every copy private to its CTA). A page chunk
 //    [tokens_per_page][head_dim] of one KV head is contiguous in the page layout [K/V][Hkv][P][D]; the
 //    K chunk and the V chunk of one (page, KV head) travel in ONE four-dimensional TMA copy
 //    {64 columns, page rows, column halves, K/V plane} (8 KiB at head_dim 128, 16 KiB at 256): the copy
@@ -75,6 +75,8 @@ constexpr uint32_t kStatusWaitExpired = 1u;
 constexpr uint32_t kStatusPageOutOfPool = 2u;
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr int kMaxPidsPerSegment = 160;  // page ids staged per task segment (2048 tokens of 16 + slack)
+constexpr uint32_t kBalanceMaxTemplates = 16384;  // above this, tasks are dealt round-robin (many tasks per CTA anyway)
+constexpr uint32_t kTaskOverheadTokens = 48;      // fixed cost of a task, in KV tokens of streaming time
 constexpr int kMaxTaskTokens = 32;       // Q tokens per task (the reference caps the tile at 32, sdpa.rs:117)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
@@ -228,12 +230,24 @@ __device__ __forceinline__ void store_out4(T* dst, float4 v) {
 // is saturated by K/V streaming, so dependent loads are what costs), carrying (max, sum, numerator) between groups.
 // Partial j of the row sits `j * index_stride` statistics and `j * out_stride` output floats after the first.
 // L2-only loads: the partials may have been written by other SMs during this launch.
-__device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, const float* partial_max,
-                                                     const float* partial_out, uint64_t first_index,
-                                                     uint64_t index_stride, uint64_t out_stride, uint32_t count,
-                                                     uint32_t head_dim, uint32_t d, float* out_sum, float* out_max) {
-    float run_max = -INFINITY, run_sum = 0.0f;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+struct MergeState {
+    float4 acc;    // sum of weight_i * o_i, relative to `max`
+    float sum;     // sum of weight_i
+    float max;     // running maximum; -inf while nothing has been merged
+};
+
+__device__ __forceinline__ MergeState merge_state_empty() {
+    return MergeState{make_float4(0.0f, 0.0f, 0.0f, 0.0f), 0.0f, -INFINITY};
+}
+
+// Folds `count` partials of one row into `state`.
+__device__ __forceinline__ void merge_partials_accumulate(MergeState& state, const float* partial_sum,
+                                                          const float* partial_max, const float* partial_out,
+                                                          uint64_t first_index, uint64_t index_stride,
+                                                          uint64_t out_stride, uint32_t count, uint32_t head_dim,
+                                                          uint32_t d) {
+    float run_max = state.max, run_sum = state.sum;
+    float4 acc = state.acc;
     for (uint32_t base = 0; base < count; base += 8) {
         float mx[8], sm[8];
         float4 v[8];
@@ -269,16 +283,42 @@ __device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, c
         }
         run_max = new_max;
     }
-    const float inv = run_sum > 0.0f ? 1.0f / run_sum : 0.0f;
-    acc.x *= inv;
-    acc.y *= inv;
-    acc.z *= inv;
-    acc.w *= inv;
+    state.acc = acc;
+    state.sum = run_sum;
+    state.max = run_max;
+}
+
+// Folds another state of the same row into `state` (both relative to their own maxima).
+__device__ __forceinline__ void merge_state_combine(MergeState& state, const MergeState& other) {
+    const float new_max = fmaxf(state.max, other.max);
+    const float keep = state.max == -INFINITY ? 0.0f : expf(state.max - new_max);
+    const float take = other.max == -INFINITY ? 0.0f : expf(other.max - new_max);
+    state.acc.x = state.acc.x * keep + other.acc.x * take;
+    state.acc.y = state.acc.y * keep + other.acc.y * take;
+    state.acc.z = state.acc.z * keep + other.acc.z * take;
+    state.acc.w = state.acc.w * keep + other.acc.w * take;
+    state.sum = state.sum * keep + other.sum * take;
+    state.max = new_max;
+}
+
+// Normalised output of a merged row; writes the merged statistics when asked.
+__device__ __forceinline__ float4 merge_state_finish(const MergeState& state, float* out_sum, float* out_max) {
+    const float inv = state.sum > 0.0f ? 1.0f / state.sum : 0.0f;
     if (out_sum != nullptr) {
-        *out_sum = run_sum;
-        *out_max = run_sum > 0.0f ? run_max : -INFINITY;
+        *out_sum = state.sum;
+        *out_max = state.sum > 0.0f ? state.max : -INFINITY;
     }
-    return acc;
+    return make_float4(state.acc.x * inv, state.acc.y * inv, state.acc.z * inv, state.acc.w * inv);
+}
+
+__device__ __forceinline__ float4 merge_partials_vec(const float* partial_sum, const float* partial_max,
+                                                     const float* partial_out, uint64_t first_index,
+                                                     uint64_t index_stride, uint64_t out_stride, uint32_t count,
+                                                     uint32_t head_dim, uint32_t d, float* out_sum, float* out_max) {
+    MergeState state = merge_state_empty();
+    merge_partials_accumulate(state, partial_sum, partial_max, partial_out, first_index, index_stride, out_stride,
+                              count, head_dim, d);
+    return merge_state_finish(state, out_sum, out_max);
 }
 
 // Merges the partials [part_begin, part_begin + part_count) of the rows (num_toks tokens x num_heads heads) of
@@ -492,6 +532,58 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 
     const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
 
+    // ---- which tasks this CTA runs. Tasks are numbered template-major. With few enough templates every CTA
+    // scans them all (12 bytes each) and takes one CONTIGUOUS run of tasks whose cost - KV tokens plus a fixed
+    // per-task term - is its 1/gridDim share of the total: task k belongs to the CTA c with
+    // c * W / grid <= cost of tasks [0, k) < (c + 1) * W / grid. No CTA carries more than its share plus one
+    // task, where dealing tasks round-robin leaves the CTAs that drew the long slices several percent behind.
+    // Contiguous tasks are also neighbours in the page table. Above the limit tasks are dealt round-robin.
+    uint32_t* task_range = const_cast<uint32_t*>(last_flag) + 1;  // [begin, end) of this CTA's run
+    const bool balanced = p.num_templates <= kBalanceMaxTemplates;
+    if (balanced) {
+        const uint32_t cells = p.num_kv_heads * p.head_ranges;
+        uint64_t* scan = reinterpret_cast<uint64_t*>(ring);  // the ring is idle until the producer starts
+        const uint32_t chunk = (p.num_templates + G::kThreads - 1) / G::kThreads;
+        const uint32_t first = min(threadIdx.x * chunk, p.num_templates);
+        const uint32_t last = min(first + chunk, p.num_templates);
+        auto cost_of = [&](uint32_t t) -> uint64_t {
+            const uint32_t kv_begin = p.templates[t * 3 + 1];
+            const uint32_t kv_end = p.templates[t * 3 + 2];
+            if (p.templates[t * 3] == 0xffffffffu || kv_end <= kv_begin) return 1;
+            return uint64_t(kv_end - kv_begin) + kTaskOverheadTokens;
+        };
+        uint64_t local = 0;
+        for (uint32_t t = first; t < last; ++t) local += cost_of(t);
+        scan[threadIdx.x] = local;
+        if (threadIdx.x == 0) {
+            task_range[0] = 0;
+            task_range[1] = 0;
+        }
+        __syncthreads();
+        uint64_t before = 0, total = 0;
+        for (uint32_t i = 0; i < uint32_t(G::kThreads); ++i) {
+            const uint64_t v = scan[i];
+            if (i < threadIdx.x) before += v;
+            total += v;
+        }
+        const uint64_t whole = total * cells;
+        const uint64_t lo = whole / gridDim.x * blockIdx.x + whole % gridDim.x * blockIdx.x / gridDim.x;
+        const uint64_t hi = whole / gridDim.x * (blockIdx.x + 1) + whole % gridDim.x * (blockIdx.x + 1) / gridDim.x;
+        // first task whose preceding cost reaches x: inside the template whose cost interval (S, E] holds x
+        uint64_t start = before * cells;
+        for (uint32_t t = first; t < last; ++t) {
+            const uint64_t c = cost_of(t);
+            const uint64_t end = start + c * cells;
+            if (lo > start && lo <= end) task_range[0] = t * cells + uint32_t((lo - start + c - 1) / c);
+            if (hi > start && hi <= end) task_range[1] = t * cells + uint32_t((hi - start + c - 1) / c);
+            start = end;
+        }
+        __syncthreads();  // also: the scan scratch (the ring) is read for the last time before this barrier
+    }
+    const uint32_t task_base = balanced ? task_range[0] : blockIdx.x;
+    const uint32_t task_step = balanced ? 1u : gridDim.x;
+    const uint32_t task_limit = balanced ? task_range[1] : total_tasks;
+
     if (warp == NCW) {
         // ------------------------------ producer warp -----------------------------------------
         uint32_t stage_counter = 0;
@@ -525,7 +617,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         };
         // Lane l decodes this CTA's task number first_index + l.
         auto decode_batch = [&](uint32_t first_index) {
-            return decode_task(p, blockIdx.x + (uint64_t(first_index) + lane) * gridDim.x, total_tasks);
+            return decode_task(p, task_base + (uint64_t(first_index) + lane) * task_step, task_limit);
         };
 
         // Two batches of 32 decoded tasks live in registers.
@@ -535,8 +627,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         prefetch_pids(cur, buf);
         bool aborted = false;
         for (uint32_t index = 0;; ++index) {
-            const uint64_t task = blockIdx.x + uint64_t(index) * gridDim.x;
-            if (task >= total_tasks) break;
+            const uint64_t task = task_base + uint64_t(index) * task_step;
+            if (task >= task_limit) break;
             // next task's descriptor: from the current batch, or lane 0 of the next one
             const uint32_t next_lane = (index + 1) & 31;
             const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
