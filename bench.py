@@ -411,11 +411,11 @@ def run_split_sequence(args):
     props = torch.cuda.get_device_properties(local)
     sampler = ClockSampler(str(getattr(props, "uuid", "")) or None, local)
     sampler.__enter__()
-    ramp_end = time.perf_counter() + args.ramp_ms * 1e-3
-    while time.perf_counter() < ramp_end:
-        for _ in range(10):
-            step()
-        torch.cuda.synchronize()
+    # untimed load so that clocks settle. Every step holds a collective, so all ranks must run the SAME number
+    # of steps: a count, not a time limit (about args.ramp_ms at 0.5 ms per step).
+    for _ in range(int(args.ramp_ms * 2)):
+        step()
+    torch.cuda.synchronize()
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
     launches = 0
     if world > 1:
@@ -495,6 +495,12 @@ def cpu_inputs(spec, contexts, sample_requests, seed):
     return cu, ti, q, ks, vs
 
 
+def host_threads():
+    """Cores this process may run on. Launchers such as torchrun export OMP_NUM_THREADS=1, which is a default for
+    their workers and not a limit of the machine, so the OpenMP default is not used."""
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
 def cpu_pass(spec, inputs, threads):
     import oracle
     cu, ti, q, ks, vs = inputs
@@ -508,7 +514,7 @@ def cpu_baseline(spec, contexts, sample_requests):
     """The CPU restatement of the reference's GQA SDPA (oracle/, kind "port") on the host cores, contiguous
     per-request K/V as the reference's CPU path takes them, one pass over a bounded sample."""
     import oracle
-    threads = oracle.max_threads()
+    threads = host_threads()
     # keep the sample near 10-30 s of CPU work: about 0.4 core-seconds per 4.6k-token Hq64/D128 request
     work = sum(contexts[:sample_requests]) * spec["hq"] * spec["d"] * spec["q_len"]
     budget = 2.0e11 * threads / 8
@@ -532,7 +538,7 @@ def run_reference(args):
     import oracle
     spec = WORKLOADS[args.workload]
     contexts = contexts_for(spec, 0)
-    threads = oracle.max_threads()
+    threads = host_threads()
     sample = max(1, min(len(contexts), 8))
     inputs = cpu_inputs(spec, contexts, sample, spec["seed"])
     for _ in range(min(args.warmup, 1)):
