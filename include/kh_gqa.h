@@ -530,6 +530,54 @@ KH_API kh_status kh_sliced_q_arrival_counter_bytes(const kh_sliced_q_config* con
                                                    const kh_execution_variant* execution,
                                                    const kh_sliced_q_shape* shape, uint64_t* out);
 
+/* ---- KV page write: BM/components/gqa/kv_page_write.rs, gqa_kv_page_write.metal:32-80 ------- */
+/* kv_page_write::Config (kv_page_write.rs:62-68) plus the stored element type. The reference stores FP8 E4M3FN
+ * (`kv_dtype` = KH_DTYPE_FP8_E4M3FN, conversion of BM/components/gqa/fp8.rs:19-44: nearest-even, saturating at
+ * 448, NaN kept); `kv_dtype == dtype` stores the source bits unchanged, the page format the attention kernels
+ * of this library read. tokens per page = page_bytes / (2 * num_kv_heads * head_dim * sizeof(kv_dtype)). */
+typedef struct kh_kv_page_write_config {
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t page_bytes;
+    kh_dtype dtype;    /* flat_k / flat_v element type: Bfloat16 (the reference's) or Float16 */
+    kh_dtype kv_dtype;
+} kh_kv_page_write_config;
+
+/* kv_page_write::Shape (kv_page_write.rs:123-127). */
+typedef struct kh_kv_page_write_shape {
+    uint32_t num_total_token_writes;
+    kh_page_table_layout page_table_layout;
+} kh_kv_page_write_shape;
+
+/* kv_page_write::Buffers (kv_page_write.rs:143-151), binding order 0..5 of Invocation::record (:211-216):
+ * flat_k / flat_v are [writes][Hkv][D]; write i goes to request slot req_slots[i], absolute token position
+ * flat_token_indices[i]. */
+typedef struct kh_kv_page_write_buffers {
+    kh_buffer_ref pages;
+    kh_buffer_ref flat_k;
+    kh_buffer_ref flat_v;
+    kh_buffer_ref req_slots;
+    kh_buffer_ref flat_token_indices;
+    kh_buffer_ref page_ids;
+} kh_kv_page_write_buffers;
+
+typedef struct kh_kv_page_write kh_kv_page_write;
+
+/* Compute::new (kv_page_write.rs:158-167). */
+KH_API kh_status kh_kv_page_write_create(kh_device* device, const kh_kv_page_write_config* config,
+                                         kh_kv_page_write** out);
+KH_API kh_status kh_kv_page_write_destroy(kh_kv_page_write* compute);
+/* Config::num_tokens_per_page (kv_page_write.rs:80-92). */
+KH_API kh_status kh_kv_page_write_tokens_per_page(const kh_kv_page_write_config* config, uint32_t* out);
+/* Compute::invoke(...).record (kv_page_write.rs:169-236): writes the first num_active_token_writes entries.
+ * A page id beyond the pool is not written and sets bit 1 of the device status word. */
+KH_API kh_status kh_kv_page_write_invoke(kh_kv_page_write* compute, kh_stream* stream,
+                                         const kh_kv_page_write_shape* shape, const kh_kv_page_write_buffers* buffers,
+                                         uint32_t num_active_token_writes, uint32_t page_table_index);
+/* bf16_to_fp8_e4m3 / fp8_e4m3_to_bf16 (BM/components/gqa/fp8.rs:19-58) on bit patterns, host side. */
+KH_API uint8_t kh_fp8_e4m3_from_bf16(uint16_t bf16_bits);
+KH_API uint16_t kh_fp8_e4m3_to_bf16(uint8_t fp8_bits);
+
 /* ---- device status word: the analogue of SubmissionCheck (BM/metal/stream/check.rs:8-13) ---- */
 /* Reads (after synchronising the stream) and clears the sticky status the kernels of `device`
  * write: 0 = clean; bit 0 = a bounded wait inside a kernel ran out; bit 1 = a page id addressed

@@ -112,6 +112,20 @@ class SlicedKvReduceBuffersC(C.Structure):
         "partial_exp_sums", "partial_max_logits", "partial_output", "cu_sdpa_partial_outputs", "output")]
 
 
+class KvPageWriteConfigC(C.Structure):
+    _fields_ = [("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("page_bytes", C.c_uint32),
+                ("dtype", C.c_uint32), ("kv_dtype", C.c_uint32)]
+
+
+class KvPageWriteShapeC(C.Structure):
+    _fields_ = [("num_total_token_writes", C.c_uint32), ("page_table_layout", PageTableLayoutC)]
+
+
+class KvPageWriteBuffersC(C.Structure):
+    _fields_ = [(name, BufferRef) for name in (
+        "pages", "flat_k", "flat_v", "req_slots", "flat_token_indices", "page_ids")]
+
+
 class SlicedKvStaticBuffersC(C.Structure):
     _fields_ = [(name, BufferRef) for name in (
         "q", "kv_pages", "req_slots", "page_ids", "sdpa_map_task_templates", "cu_sdpa_partial_outputs", "output")]
@@ -236,11 +250,17 @@ PROTOTYPES = {
     "kh_device_check": [_vp, _vp, P(_u32)],
     "kh_combine_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, BufferRef, BufferRef, _u32, BufferRef, BufferRef,
                             BufferRef],
+    "kh_kv_page_write_create": [_vp, P(KvPageWriteConfigC), P(_vp)],
+    "kh_kv_page_write_destroy": [_vp],
+    "kh_kv_page_write_tokens_per_page": [P(KvPageWriteConfigC), P(C.c_uint32)],
+    "kh_kv_page_write_invoke": [_vp, _vp, P(KvPageWriteShapeC), P(KvPageWriteBuffersC), _u32, _u32],
     "kh_combine_packed_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, _u32, BufferRef],
 }
 _SPECIAL = {
     "kh_last_error": ([C.c_char_p, C.c_size_t], C.c_size_t),
     "kh_version": ([], C.c_char_p),
+    "kh_fp8_e4m3_from_bf16": ([C.c_uint16], C.c_uint8),
+    "kh_fp8_e4m3_to_bf16": ([C.c_uint8], C.c_uint16),
 }
 
 _lib = None

@@ -13,8 +13,8 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libkhcuda_gqa.so"
-SOURCES = ["host_sdpa.cpp", "sdpa_api.cu"]
-HEADERS = ["common.h", "host_sdpa.h", "sdpa_map.cuh", "../../include/kh_gqa.h"]
+SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "kv_page_write.cu"]
+HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "sdpa_map.cuh", "../../include/kh_gqa.h"]
 
 
 def nvcc_path() -> str:

@@ -13,36 +13,11 @@
 #include <vector>
 
 #include "common.h"
+#include "cuda_objects.h"
 #include "host_sdpa.h"
 #include "sdpa_map.cuh"
 
-struct kh_device {
-    int32_t ordinal;
-    int32_t sm_count;
-    uint32_t* status;  // device status word
-};
-
-struct kh_stream {
-    kh_device* device;
-    cudaStream_t stream;
-    bool owned;
-};
-
 namespace kh {
-
-#define KH_CUDA(call)                                                                                         \
-    do {                                                                                                      \
-        cudaError_t kh_cuda_err = (call);                                                                     \
-        if (kh_cuda_err != cudaSuccess) {                                                                     \
-            ::kh::raise(kh_cuda_err == cudaErrorMemoryAllocation ? KH_RESOURCE_EXHAUSTED : KH_UNAVAILABLE,    \
-                        "%s failed: %s", #call, cudaGetErrorString(kh_cuda_err));                             \
-        }                                                                                                     \
-    } while (0)
-
-static void use_device(const kh_device* device) {
-    KH_REQUIRE(device != nullptr, "device is null");
-    KH_CUDA(cudaSetDevice(device->ordinal));
-}
 
 // ---------------------------------------------------------------------------------------------
 // Reduce kernel: the partial-state merge of the reference's reducers
@@ -336,12 +311,6 @@ static void init_common(ComputeCommon& c, kh_device* device, kh_dtype dtype, kh_
     c.instance = pick_instance(dtype, head_dim, c.tokens_per_page, variant.max_q_tokens * variant.max_q_heads);
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.instance.kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, c.instance.smem_bytes));
-}
-
-static void need(kh_buffer_ref buffer, uint64_t bytes, const char* name) {
-    KH_REQUIRE(buffer.ptr != nullptr, "%s buffer is null", name);
-    KH_REQUIRE(buffer.bytes >= bytes, "%s buffer holds %llu bytes but %llu are required", name,
-               (unsigned long long)buffer.bytes, (unsigned long long)bytes);
 }
 
 static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buffer_ref q, kh_buffer_ref kv_pages,

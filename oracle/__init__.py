@@ -82,6 +82,10 @@ def lib() -> ctypes.CDLL:
             ctypes.c_float, _f32p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float),
         ]
         handle.kh_oracle_partial_row.restype = None
+        handle.kh_oracle_fp8_from_bf16.argtypes = [ctypes.c_uint16]
+        handle.kh_oracle_fp8_from_bf16.restype = ctypes.c_uint8
+        handle.kh_oracle_fp8_to_bf16.argtypes = [ctypes.c_uint8]
+        handle.kh_oracle_fp8_to_bf16.restype = ctypes.c_uint16
         handle.kh_oracle_round_bf16.argtypes = [_f32p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p]
         handle.kh_oracle_round_bf16.restype = None
         handle.kh_oracle_generated_values.argtypes = [ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int32, _f32p]
@@ -257,6 +261,20 @@ def fixture_values(count: int, scale: float, pattern_offset: int) -> np.ndarray:
     out = np.empty(count, dtype=np.float32)
     lib().kh_oracle_fixture_values(count, float(scale), pattern_offset, out)
     return out
+
+
+def fp8_from_bf16_bits(bits) -> np.ndarray:
+    """FP8 E4M3FN encoding of bf16 bit patterns (fp8.rs:19-44), element by element."""
+    flat = np.ascontiguousarray(bits, dtype=np.uint16).reshape(-1)
+    fn = lib().kh_oracle_fp8_from_bf16
+    return np.array([fn(int(b)) for b in flat], dtype=np.uint8).reshape(np.shape(bits))
+
+
+def fp8_to_bf16_bits(bits) -> np.ndarray:
+    """bf16 bit patterns of FP8 E4M3FN codes (fp8.rs:46-58)."""
+    flat = np.ascontiguousarray(bits, dtype=np.uint8).reshape(-1)
+    fn = lib().kh_oracle_fp8_to_bf16
+    return np.array([fn(int(b)) for b in flat], dtype=np.uint16).reshape(np.shape(bits))
 
 
 def max_threads() -> int:

@@ -234,6 +234,53 @@ KH_ORACLE_API int kh_oracle_scatter_paged(uint8_t* kv_pages, uint64_t kv_pages_b
 }
 
 /* ------------------------------------------------------------------------------------------
+ * FP8 E4M3FN storage codec of the reference's KV cache,
+ *   crates/inference-backend-metal/src/components/gqa/fp8.rs:19-58
+ * restated with the same arithmetic (log2 / floor / powers of two / round-ties-even in f32).
+ * One fixed unit scale; finite and infinite magnitudes >= 448 saturate to 0x7e; NaN -> 0x7f.
+ * ---------------------------------------------------------------------------------------- */
+static float oracle_bf16_bits_to_f32(uint16_t bits) {
+    const uint32_t wide = (uint32_t)bits << 16;
+    float value;
+    memcpy(&value, &wide, 4);
+    return value;
+}
+
+KH_ORACLE_API uint8_t kh_oracle_fp8_from_bf16(uint16_t bf16_bits) {
+    const float value = oracle_bf16_bits_to_f32(bf16_bits);
+    const uint8_t sign = (bf16_bits & 0x8000u) ? 0x80 : 0;
+    const float magnitude = fabsf(value);
+    if (isnan(magnitude)) return sign | 0x7f;
+    if (!isfinite(magnitude) || magnitude >= 448.0f) return sign | 0x7e;
+    if (magnitude < 0.015625f) {
+        const uint32_t mantissa = (uint32_t)nearbyintf(magnitude * 512.0f); /* ties to even */
+        return sign | (uint8_t)(mantissa < 8u ? mantissa : 8u);
+    }
+    int exponent = (int)floorf(log2f(magnitude));
+    uint32_t mantissa = (uint32_t)nearbyintf((magnitude * exp2f((float)-exponent) - 1.0f) * 8.0f);
+    if (mantissa == 8u) {
+        exponent += 1;
+        mantissa = 0;
+    }
+    const int encoded = exponent + 7;
+    if (encoded > 15 || (encoded == 15 && mantissa >= 7u)) return sign | 0x7e;
+    return sign | (uint8_t)((uint32_t)encoded << 3) | (uint8_t)mantissa;
+}
+
+/* fp8.rs:46-58: returns the bf16 bits of the decoded value. */
+KH_ORACLE_API uint16_t kh_oracle_fp8_to_bf16(uint8_t bits) {
+    const uint32_t exponent = (bits >> 3) & 0x0fu;
+    const uint32_t mantissa = bits & 0x07u;
+    const uint16_t sign = (bits & 0x80u) ? 0x8000 : 0;
+    if (exponent == 15 && mantissa == 7) return sign | 0x7fc0;
+    const float magnitude = exponent == 0 ? (float)mantissa / 512.0f
+                                          : (1.0f + (float)mantissa / 8.0f) * exp2f((float)exponent - 7.0f);
+    uint32_t wide;
+    memcpy(&wide, &magnitude, 4); /* exact in bf16: at most 4 significant bits */
+    return sign | (uint16_t)(wide >> 16);
+}
+
+/* ------------------------------------------------------------------------------------------
  * Partial-state merge (split-KV reduce), docs/gqa_sdpa_selection.md:443-460 and
  *   crates/inference-backend-metal/src/components/metal/gqa_sdpa_sliced_kv_reduce.metal:30-55
  *   crates/inference-backend-metal/src/components/metal/gqa_sdpa_sliced_q_reduce.metal:26-62

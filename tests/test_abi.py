@@ -13,7 +13,7 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert len(declared) >= 55
     for name in declared:
         assert hasattr(handle, name), name
-    bound = set(abi.PROTOTYPES) | {"kh_last_error", "kh_version"}
+    bound = set(abi.PROTOTYPES) | set(abi._SPECIAL)
     assert set(declared) == bound, set(declared) ^ bound
 
 
