@@ -358,7 +358,7 @@ struct TaskSlot {
     uint32_t group;        // fused reduce: arrival counter of this task's (Q range, KV head, head range)
     uint32_t part_begin;   // fused reduce: first partial (template) of the Q range
     uint32_t part_count;   // fused reduce: partials of the Q range
-    uint32_t pad;
+    uint32_t carry;        // bit 0: continue from the previous task's running state; bit 1: hand the state on
     uint32_t visible[2 * kMaxTaskTokens];  // per Q token [begin, end), only when MapParams::visible is set
 };
 
@@ -615,10 +615,32 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             const uint32_t num_pages = (t.kv_end + P - 1) / P - first_page;
             stage_pids(t, first_page, min(num_pages, uint32_t(kMaxPidsPerSegment)), which);
         };
-        // Lane l decodes this CTA's task number first_index + l.
-        auto decode_batch = [&](uint32_t first_index) {
-            return decode_task(p, task_base + (uint64_t(first_index) + lane) * task_step, task_limit);
+        // Order in which this CTA visits its contiguous run [task_base, task_limit) of template-major tasks: cell by
+        // cell (cell = KV head x Q-head range), and within a cell template after template. Neighbours in this order
+        // are consecutive KV slices of the same Q rows, so the consumers can carry their running state from one
+        // task into the next instead of merging and publishing at every slice boundary.
+        const uint32_t cells = p.num_kv_heads * p.head_ranges;
+        const bool by_cell = balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) != 0;
+        const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
+        const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
+        auto visit_to_task = [&](uint64_t visit) -> uint64_t {
+            if (!by_cell) return task_base + visit * task_step;
+            if (visit >= task_limit - task_base) return task_limit;
+            uint32_t before = 0;
+            for (uint32_t c = 0; c < cells; ++c) {
+                const uint32_t first_row = c >= run_c0 ? run_r0 : run_r0 + 1;
+                const uint32_t end_row = c < run_c1 ? run_r1 + 1 : run_r1;  // one past the cell's last row
+                const uint32_t count = end_row > first_row ? end_row - first_row : 0;
+                if (visit < before + count) return uint64_t(first_row + (uint32_t(visit) - before)) * cells + c;
+                before += count;
+            }
+            return task_limit;
         };
+        // Lane l decodes this CTA's visit number first_index + l.
+        auto decode_batch = [&](uint32_t first_index) {
+            return decode_task(p, visit_to_task(uint64_t(first_index) + lane), task_limit);
+        };
+        uint32_t carry_in = 0;
 
         // Two batches of 32 decoded tasks live in registers.
         TaskInfo batch_cur = decode_batch(0);
@@ -627,8 +649,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         prefetch_pids(cur, buf);
         bool aborted = false;
         for (uint32_t index = 0;; ++index) {
-            const uint64_t task = task_base + uint64_t(index) * task_step;
-            if (task >= task_limit) break;
+            if (visit_to_task(index) >= task_limit) break;
             // next task's descriptor: from the current batch, or lane 0 of the next one
             const uint32_t next_lane = (index + 1) & 31;
             const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
@@ -637,6 +658,14 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 
             uint32_t tile_begin, num_tiles;
             task_tiles(cur, tile_begin, num_tiles);
+            // the next task continues this one: same Q rows, same request, its KV range starts where this one ends
+            const uint32_t carry_out =
+                (by_cell && p.direct == 0 && p.cu == nullptr && cur.active && nxt.active && nxt.tok_begin == cur.tok_begin &&
+                 nxt.num_toks == cur.num_toks && nxt.head_begin == cur.head_begin && nxt.num_heads == cur.num_heads &&
+                 nxt.req_slot == cur.req_slot && nxt.kv_begin == cur.kv_end && cur.kv_end > cur.kv_begin &&
+                 nxt.kv_end > nxt.kv_begin)
+                    ? 1u
+                    : 0u;
             if (cur.active && !aborted) {
                 // ---- publish the task: descriptor, visibility rows, Q rows
                 const uint32_t slot = pushed % TQ;
@@ -658,6 +687,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         ts->group = cur.group;
                         ts->part_begin = cur.part_begin;
                         ts->part_count = cur.part_count;
+                        ts->carry = carry_in | (carry_out << 1);
                     }
                     if (p.visible != nullptr) {
                         for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
@@ -768,6 +798,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 }
             }
             // advance
+            carry_in = carry_out;
             cur = nxt;
             buf ^= 1;
             if (next_lane == 0) {
@@ -827,6 +858,11 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         const uint32_t k_xor = (lm_mat & 1) ^ (k_row & 7);
         const uint32_t v_xor = (lm_mat >> 1) ^ (v_row & 7);
 
+        float o[DN][4];
+        float m_run[2] = {-INFINITY, -INFINITY};
+        float l_run[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int n = 0; n < DN; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
             if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p.status)) break;
@@ -864,11 +900,15 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 }
             }
 
-            float o[DN][4];
+            // A task that continues the KV range of the previous one for the same Q rows (the producer says so)
+            // keeps the running (m, l, O); every other task starts from nothing.
+            const uint32_t t_carry = ts->carry;
+            if (!(t_carry & 1u)) {
 #pragma unroll
-            for (int n = 0; n < DN; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-            float m_run[2] = {-INFINITY, -INFINITY};
-            float l_run[2] = {0.0f, 0.0f};
+                for (int n = 0; n < DN; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+                m_run[0] = m_run[1] = -INFINITY;
+                l_run[0] = l_run[1] = 0.0f;
+            }
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * 16 * 128;
             uint32_t q_addr[4];
 #pragma unroll
@@ -1071,6 +1111,26 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             stage_counter += t_num_tiles;
 
             if (p.debug & 2) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+                continue;
+            }
+            if (t_carry & 2u) {
+                // The next task of this CTA continues these rows: nothing is merged or published now. This
+                // task's template still gets a partial, an empty one (weight zero in every merge).
+                if (part == 0 && tq == 0) {
+#pragma unroll
+                    for (int i = 0; i < NROW; ++i) {
+                        const uint32_t row = mt * 16 + g + 8 * i;
+                        const uint32_t row_tok = row / p.heads_per_task;
+                        const uint32_t row_head = row % p.heads_per_task;
+                        if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
+                        const uint64_t index =
+                            (uint64_t(t_tmpl) * p.num_q_heads + t_head_begin + row_head) * p.max_q_tokens + row_tok;
+                        p.partial_sum[index] = 0.0f;
+                        p.partial_max[index] = -INFINITY;
+                    }
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
                 continue;
