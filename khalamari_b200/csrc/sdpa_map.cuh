@@ -67,7 +67,8 @@ struct MapParams {
     // Measurement aid (KH_GQA_DEBUG, 0 in normal use; outputs are meaningless when set). Bits: 1 consumers release
     // every stage without computing; 2 skip the task-end merge and publish; 4 skip the Q copies; 8 issue no K/V
     // copies (consumers run on stale shared memory); 16 / 32 / 64 skip QK / softmax / PV; 128 never run the
-    // in-kernel group merge; 256 do not count arrivals.
+    // in-kernel group merge; 256 do not count arrivals; 512 visit tasks template-major and never carry the running
+    // state from one task to the next (outputs stay valid).
     uint32_t debug;
 };
 
@@ -359,6 +360,8 @@ struct TaskSlot {
     uint32_t part_begin;   // fused reduce: first partial (template) of the Q range
     uint32_t part_count;   // fused reduce: partials of the Q range
     uint32_t carry;        // bit 0: continue from the previous task's running state; bit 1: hand the state on
+    uint32_t kv_head;      // for the stream warp: KV head whose rows are streamed
+    uint32_t req_slot;     // for the stream warp: request slot (page ids of later segments)
     uint32_t visible[2 * kMaxTaskTokens];  // per Q token [begin, end), only when MapParams::visible is set
 };
 
@@ -380,14 +383,14 @@ struct MapGeometry {
     static constexpr int kWarpTokens = kStageTokens / PS;            // KV tokens one warp handles per stage
     static constexpr int kMergeParts = KVW * PS;                     // (m, l, O) states merged per row tile
     static constexpr int kConsumerWarps = MT * KVW * PS;
-    static constexpr int kThreads = (kConsumerWarps + 1) * 32;
+    static constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + stream warp + task warp
     static constexpr int kQRows = MT * 16;
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;  // the producer publishes at most one task ahead of the consumers
     static constexpr int kFragRegs = HALF ? D / 4 : D / 2;        // O accumulator registers a warp parks
     static constexpr int kMergeSlotFloats = (kFragRegs + 4) * 32;  // O fragment + (m, l) x 2 rows, per lane
     static constexpr int kMergeBytes = (kMergeParts == 1) ? 0 : MT * KVW * kMergeSlotFloats * 4;  // one state: no merge
-    static constexpr int kPidBytes = 2 * kMaxPidsPerSegment * 4;
+    static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
     static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 512;
     static constexpr int kSmemLimit = 227 * 1024 - 1024 /* alignment slack */;
@@ -500,7 +503,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 2 * TQ);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 3 * TQ);
     volatile uint32_t* last_flag = abort_flag + 1;  // fused reduce: "this CTA completed its group"
 
     const int warp = threadIdx.x >> 5;
@@ -509,6 +512,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     const uint32_t empty_bar = smem_addr(bars + NS);
     const uint32_t task_full_bar = smem_addr(bars + 2 * NS);
     const uint32_t task_empty_bar = smem_addr(bars + 2 * NS + TQ);
+    const uint32_t stream_full_bar = smem_addr(bars + 2 * NS + 2 * TQ);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -518,7 +522,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         for (int s = 0; s < TQ; ++s) {
             // the expect_tx arrival, plus (when per-token visibility rows are staged) 32 lanes' cp.async arrivals
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
-            mbar_init(task_empty_bar + 8 * s, NCW);
+            mbar_init(task_empty_bar + 8 * s, NCW + 1);  // every consumer warp and the stream warp
+            mbar_init(stream_full_bar + 8 * s, 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -584,43 +589,20 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     const uint32_t task_step = balanced ? 1u : gridDim.x;
     const uint32_t task_limit = balanced ? task_range[1] : total_tasks;
 
-    if (warp == NCW) {
-        // ------------------------------ producer warp -----------------------------------------
-        uint32_t stage_counter = 0;
+    if (warp == NCW + 1) {
+        // ------------------------------ task warp ---------------------------------------------
+        // Decodes this CTA's tasks (32 at a time, one per lane) and publishes them one task ahead of the
+        // stream warp: descriptor, per-token visibility rows and Q rows for the consumers, the page ids of the
+        // task's first segment for the stream warp. Everything here has global-memory latency in it; keeping it
+        // off the stream warp is what lets that warp issue K/V copies without a pause at task boundaries.
         uint32_t pushed = 0;  // task-ring pushes so far
-        int buf = 0;
 
-        // Stages the page ids of pages [first_page, first_page + count) of a task into pid_smem[which].
-        auto stage_pids = [&](const TaskInfo& t, uint32_t first_page, uint32_t count, int which) {
-            const uint64_t base = (uint64_t(t.req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
-            for (uint32_t i = lane; i < count; i += 32) {
-                const uint32_t dst = smem_addr(pid_smem + which * kMaxPidsPerSegment + i);
-                const uint32_t* src = p.page_ids + base + first_page + i;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        auto task_tiles = [&](const TaskInfo& t, uint32_t& tile_begin, uint32_t& num_tiles) {
-            tile_begin = num_tiles = 0;
-            if (t.active && t.kv_end > t.kv_begin) {
-                tile_begin = t.kv_begin / ST * ST;
-                num_tiles = (t.kv_end - tile_begin + ST - 1) / ST;
-            }
-        };
-        auto prefetch_pids = [&](const TaskInfo& t, int which) {
-            uint32_t tile_begin, num_tiles;
-            task_tiles(t, tile_begin, num_tiles);
-            if (num_tiles == 0) return;
-            const uint32_t first_page = tile_begin / P;
-            const uint32_t num_pages = (t.kv_end + P - 1) / P - first_page;
-            stage_pids(t, first_page, min(num_pages, uint32_t(kMaxPidsPerSegment)), which);
-        };
         // Order in which this CTA visits its contiguous run [task_base, task_limit) of template-major tasks: cell by
         // cell (cell = KV head x Q-head range), and within a cell template after template. Neighbours in this order
         // are consecutive KV slices of the same Q rows, so the consumers can carry their running state from one
         // task into the next instead of merging and publishing at every slice boundary.
         const uint32_t cells = p.num_kv_heads * p.head_ranges;
-        const bool by_cell = balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) != 0;
+        const bool by_cell = balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) == 0;
         const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
         const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
         auto visit_to_task = [&](uint64_t visit) -> uint64_t {
@@ -646,18 +628,18 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         TaskInfo batch_cur = decode_batch(0);
         TaskInfo batch_next = decode_batch(32);
         TaskInfo cur = shfl_task(batch_cur, 0);
-        prefetch_pids(cur, buf);
         bool aborted = false;
         for (uint32_t index = 0;; ++index) {
             if (visit_to_task(index) >= task_limit) break;
             // next task's descriptor: from the current batch, or lane 0 of the next one
             const uint32_t next_lane = (index + 1) & 31;
             const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncwarp();
 
-            uint32_t tile_begin, num_tiles;
-            task_tiles(cur, tile_begin, num_tiles);
+            uint32_t tile_begin = 0, num_tiles = 0;
+            if (cur.active && cur.kv_end > cur.kv_begin) {
+                tile_begin = cur.kv_begin / ST * ST;
+                num_tiles = (cur.kv_end - tile_begin + ST - 1) / ST;
+            }
             // the next task continues this one: same Q rows, same request, its KV range starts where this one ends
             const uint32_t carry_out =
                 (by_cell && p.direct == 0 && p.cu == nullptr && cur.active && nxt.active && nxt.tok_begin == cur.tok_begin &&
@@ -667,12 +649,14 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     ? 1u
                     : 0u;
             if (cur.active && !aborted) {
-                // ---- publish the task: descriptor, visibility rows, Q rows
                 const uint32_t slot = pushed % TQ;
                 const uint32_t phase = (pushed / TQ) & 1;
+                // the slot is free once the consumers AND the stream warp are done with the task it held
                 if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) aborted = true;
                 if (!aborted) {
                     TaskSlot* ts = task_ring + slot;
+                    const uint32_t first_page = tile_begin / P;
+                    const uint32_t num_pages = num_tiles ? (cur.kv_end + P - 1) / P - first_page : 0;
                     if (lane == 0) {
                         ts->tmpl = cur.tmpl;
                         ts->head_begin = cur.head_begin;
@@ -688,6 +672,20 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         ts->part_begin = cur.part_begin;
                         ts->part_count = cur.part_count;
                         ts->carry = carry_in | (carry_out << 1);
+                        ts->kv_head = cur.kv_head;
+                        ts->req_slot = cur.req_slot;
+                    }
+                    // page ids of the first segment (the stream warp stages later segments of a very long task itself)
+                    {
+                        const uint64_t base =
+                            (uint64_t(cur.req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
+                        const uint32_t count = min(num_pages, uint32_t(kMaxPidsPerSegment));
+                        for (uint32_t i = lane; i < count; i += 32) {
+                            const uint32_t dst = smem_addr(pid_smem + slot * kMaxPidsPerSegment + i);
+                            const uint32_t* src = p.page_ids + base + first_page + i;
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                        }
+                        asm volatile("cp.async.commit_group;" ::: "memory");
                     }
                     if (p.visible != nullptr) {
                         for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
@@ -710,27 +708,78 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                         const uint32_t row = (cur.tok_begin + tok) * p.num_q_heads + cur.head_begin;
                         tma_load_2d(dst, &q_map, half * 64, static_cast<int32_t>(row), task_full_bar + 8 * slot);
                     }
+                    // the page ids have landed: hand the task to the stream warp
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(stream_full_bar + 8 * slot);
                     ++pushed;
                 }
             }
-            prefetch_pids(nxt, buf ^ 1);  // lands while this task streams
-            if (cur.active && num_tiles > 0 && !aborted) {
-                // The tiles are streamed one page-id segment at a time. A segment's ids are staged by the whole
-                // warp (the first segment was prefetched during the previous task); the per-stage loop then runs
-                // in lane 0 alone, with running slot / phase / token counters and 32-bit row arithmetic, because
-                // this loop is the one instruction stream that has to keep the copy engine fed.
+            // advance
+            carry_in = carry_out;
+            cur = nxt;
+            if (next_lane == 0) {
+                batch_cur = batch_next;
+                batch_next = decode_batch(index + 1 + 32);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // ---- tell the consumers and the stream warp there is nothing more
+        if (!aborted) {
+            const uint32_t slot = pushed % TQ;
+            const uint32_t phase = (pushed / TQ) & 1;
+            if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
+                if (lane == 0) {
+                    task_ring[slot].done = 1;
+                    mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
+                    mbar_arrive(stream_full_bar + 8 * slot);
+                }
+                if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+            }
+        }
+        // Abort path only: Q copies already issued may still be landing; wait (bounded) for them.
+        if (*abort_flag) {
+            for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
+                const uint32_t c = pushed - 1 - back;
+                for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                    if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == NCW) {
+        // ------------------------------ stream warp -------------------------------------------
+        // Issues the K/V copies of one published task after the other into the stage ring. The per-stage loop runs
+        // in lane 0 alone, with running slot / phase / token counters and 32-bit row arithmetic: this loop is the
+        // one instruction stream that has to keep the copy engine fed, and it reads shared memory only.
+        uint32_t stage_counter = 0;
+        bool aborted = false;
+        const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
+        for (uint32_t taken = 0; !aborted; ++taken) {
+            const uint32_t tslot = taken % TQ;
+            if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+            const TaskSlot* ts = task_ring + tslot;
+            if (ts->done) break;
+            const uint32_t tile_begin = ts->tile_begin, num_tiles = ts->num_tiles, kv_end = ts->kv_end;
+            const uint32_t head_row = ts->kv_head * P;
+            if (num_tiles > 0) {
                 constexpr uint32_t kTilesPerSegment = uint32_t(kMaxPidsPerSegment) * P / ST;
                 const uint32_t first_page = tile_begin / P;
-                const uint32_t num_pages = (cur.kv_end + P - 1) / P - first_page;
-                const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
-                const uint32_t head_row = cur.kv_head * P;
-                const uint32_t* pids = pid_smem + buf * kMaxPidsPerSegment;
+                const uint32_t num_pages = (kv_end + P - 1) / P - first_page;
+                const uint32_t* pids = pid_smem + tslot * kMaxPidsPerSegment;
                 for (uint32_t seg_tile = 0; seg_tile < num_tiles && !aborted; seg_tile += kTilesPerSegment) {
-                    const uint32_t seg_first = first_page + seg_tile * (ST / P);
                     if (seg_tile > 0) {
-                        asm volatile("cp.async.wait_group 0;" ::: "memory");
+                        // a task longer than one segment: restage the next run of page ids (whole warp)
+                        const uint32_t seg_first = first_page + seg_tile * (ST / P);
+                        const uint32_t count = min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment));
+                        const uint64_t base =
+                            (uint64_t(ts->req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
                         __syncwarp();
-                        stage_pids(cur, seg_first, min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment)), buf);
+                        for (uint32_t i = lane; i < count; i += 32) {
+                            const uint32_t dst = smem_addr(pid_smem + tslot * kMaxPidsPerSegment + i);
+                            const uint32_t* src = p.page_ids + base + seg_first + i;
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                        }
+                        asm volatile("cp.async.commit_group;" ::: "memory");
                         asm volatile("cp.async.wait_group 0;" ::: "memory");
                         __syncwarp();
                     }
@@ -748,7 +797,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                                 break;
                             }
                             const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
-                            if (tile_tok + ST <= cur.kv_end && !(p.debug & 8)) {
+                            if (tile_tok + ST <= kv_end && !(p.debug & 8)) {
                                 mbar_arrive_expect_tx(bar, G::kStageBytes);
 #pragma unroll
                                 for (int b = 0; b < G::kBoxesPerPlane; ++b) {
@@ -764,7 +813,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                                 uint32_t boxes_needed = 0;
 #pragma unroll
                                 for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                                    if (tile_tok + b * G::kBoxRows < cur.kv_end) ++boxes_needed;
+                                    if (tile_tok + b * G::kBoxRows < kv_end) ++boxes_needed;
                                 }
                                 if (p.debug & 8) boxes_needed = 0;
                                 mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
@@ -797,27 +846,9 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     }
                 }
             }
-            // advance
-            carry_in = carry_out;
-            cur = nxt;
-            buf ^= 1;
-            if (next_lane == 0) {
-                batch_cur = batch_next;
-                batch_next = decode_batch(index + 1 + 32);
-            }
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        // ---- tell the consumers there is nothing more
-        if (!aborted) {
-            const uint32_t slot = pushed % TQ;
-            const uint32_t phase = (pushed / TQ) & 1;
-            if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
-                if (lane == 0) {
-                    task_ring[slot].done = 1;
-                    mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
-                }
-                if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-            }
+            // done with the task's descriptor and page ids
+            __syncwarp();
+            if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
         }
         // Abort path only: copies already issued may still be landing; wait (bounded) for each ring slot's
         // last issued phase before the CTA may retire.
@@ -826,12 +857,6 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 const uint32_t c = stage_counter - 1 - back;
                 for (uint32_t i = 0; i < kWaitLimit; ++i) {
                     if (mbar_try_wait(full_bar + 8 * (c % NS), (c / NS) & 1)) break;
-                }
-            }
-            for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
-                const uint32_t c = pushed - 1 - back;
-                for (uint32_t i = 0; i < kWaitLimit; ++i) {
-                    if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
                 }
             }
         }
