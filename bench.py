@@ -35,6 +35,9 @@ WORKLOADS = {
                pool_pages=0, label="verify B32 q4 Hq24/Hkv4/D256 bf16 prefix U[4096,32768] P16"),
     "c4": dict(batch=1, q_len=1, hq=16, hkv=2, d=256, dtype="bf16", lo=0, hi=0, seed=3, partition=0, pool_pages=0,
                contexts=[1048576], label="one sequence, decode, Hq16/Hkv2/D256 bf16 P16, pages split in token order"),
+    # prefill half of configuration 5: eight causal 2,048-token chunks appended to prefixes U[0, 30720]
+    "c5p": dict(batch=8, q_len=2048, hq=64, hkv=8, d=128, dtype="bf16", lo=2048, hi=32768, seed=4, partition=0,
+                pool_pages=0, label="chunked prefill B8 chunk 2048 Hq64/Hkv8/D128 bf16 prefix U[0,30720] P16"),
     "c1": dict(batch=4, q_len=1, hq=16, hkv=2, d=256, dtype="f16", lo=0, hi=0, seed=0, partition=0, pool_pages=0,
                contexts=[128, 517, 1024, 2048], label="decode B4 Hq16/Hkv2/D256 fp16 ctx {128,517,1024,2048} P16"),
 }
@@ -61,6 +64,13 @@ def traffic_estimate(spec, kv_bytes):
     if spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512:
         return int(kv_bytes * MAP_TRAFFIC_PER_KV_BYTE)
     return None
+
+
+def attention_flops(spec, contexts):
+    """4 * Hq * D flops per (query token, visible KV token) pair of one rank's batch (QK^T and PV)."""
+    q = spec["q_len"]
+    pairs = sum(q * (c - q) + q * (q + 1) // 2 for c in contexts)
+    return 4.0 * spec["hq"] * spec["d"] * pairs
 
 
 def contexts_for(spec, rank):
@@ -341,6 +351,7 @@ def run_ours(args):
                        "kv_tokens_per_gpu": int(sum(contexts)), "map_tasks": shape.num_sdpa_map_task_templates * spec["hkv"],
                        "l2": "inputs (KV pages read per step) larger than L2; no flush", "parallelism": f"dp{world} by request"},
             "tokens_per_s": round(total_tokens / (ms_per_step * 1e-3), 1),
+            "tflops": round(attention_flops(spec, contexts) / (ms_per_step * 1e-3) / 1e12, 2),
             "hbm_frac": round(value / world / peak, 4),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": traffic_estimate(spec, kv_bytes), "peak_source": f"of {peak_kind}",
