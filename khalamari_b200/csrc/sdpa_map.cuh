@@ -477,6 +477,319 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
     return r;
 }
 
+// What the producer-side warps of a kernel instance need: where the rings and barriers live, and which tasks this
+// CTA runs. Built once per thread after the prologue.
+struct ProducerContext {
+    uint8_t* ring;             // K/V stage ring
+    uint8_t* q_ring;           // Q rows of the published tasks
+    uint32_t* pid_smem;        // [task slots][kMaxPidsPerSegment] page ids of a task's current segment
+    TaskSlot* task_ring;
+    uint32_t full_bar, empty_bar, task_full_bar, task_empty_bar, stream_full_bar;  // shared-memory addresses
+    volatile uint32_t* abort_flag;
+    uint32_t task_base, task_step, task_limit;
+    bool balanced;             // the CTA owns one contiguous run of tasks
+    bool allow_carry;          // consumers can continue a running state across tasks
+    int lane;
+};
+
+// ------------------------------ task warp ---------------------------------------------
+// Decodes this CTA's tasks (32 at a time, one per lane) and publishes them one task ahead of the stream warp:
+// descriptor, per-token visibility rows and Q rows for the consumers, the page ids of the task's first segment
+// for the stream warp. Everything here has global-memory latency in it; keeping it off the stream warp is what
+// lets that warp issue K/V copies without a pause at task boundaries.
+template <typename G, int P>
+__device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensorMap& q_map, const ProducerContext& c) {
+    constexpr int ST = G::kStageTokens;
+    constexpr int TQ = G::kTaskSlots;
+    constexpr int NH = G::kColumnHalves;
+    uint8_t* const q_ring = c.q_ring;
+    uint32_t* const pid_smem = c.pid_smem;
+    TaskSlot* const task_ring = c.task_ring;
+    const uint32_t task_full_bar = c.task_full_bar, task_empty_bar = c.task_empty_bar, stream_full_bar = c.stream_full_bar;
+    volatile uint32_t* const abort_flag = c.abort_flag;
+    const uint32_t task_base = c.task_base, task_step = c.task_step, task_limit = c.task_limit;
+    const bool balanced = c.balanced;
+    const int lane = c.lane;
+    uint32_t pushed = 0;  // task-ring pushes so far
+
+    // Order in which this CTA visits its contiguous run [task_base, task_limit) of template-major tasks: cell by
+    // cell (cell = KV head x Q-head range), and within a cell template after template. Neighbours in this order
+    // are consecutive KV slices of the same Q rows, so the consumers can carry their running state from one
+    // task into the next instead of merging and publishing at every slice boundary.
+    const uint32_t cells = p.num_kv_heads * p.head_ranges;
+    const bool by_cell = c.allow_carry && balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) == 0;
+    const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
+    const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
+    auto visit_to_task = [&](uint64_t visit) -> uint64_t {
+        if (!by_cell) return task_base + visit * task_step;
+        if (visit >= task_limit - task_base) return task_limit;
+        uint32_t before = 0;
+        for (uint32_t c = 0; c < cells; ++c) {
+            const uint32_t first_row = c >= run_c0 ? run_r0 : run_r0 + 1;
+            const uint32_t end_row = c < run_c1 ? run_r1 + 1 : run_r1;  // one past the cell's last row
+            const uint32_t count = end_row > first_row ? end_row - first_row : 0;
+            if (visit < before + count) return uint64_t(first_row + (uint32_t(visit) - before)) * cells + c;
+            before += count;
+        }
+        return task_limit;
+    };
+    // Lane l decodes this CTA's visit number first_index + l.
+    auto decode_batch = [&](uint32_t first_index) {
+        return decode_task(p, visit_to_task(uint64_t(first_index) + lane), task_limit);
+    };
+    uint32_t carry_in = 0;
+
+    // Two batches of 32 decoded tasks live in registers.
+    TaskInfo batch_cur = decode_batch(0);
+    TaskInfo batch_next = decode_batch(32);
+    TaskInfo cur = shfl_task(batch_cur, 0);
+    bool aborted = false;
+    for (uint32_t index = 0;; ++index) {
+        if (visit_to_task(index) >= task_limit) break;
+        // next task's descriptor: from the current batch, or lane 0 of the next one
+        const uint32_t next_lane = (index + 1) & 31;
+        const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
+
+        uint32_t tile_begin = 0, num_tiles = 0;
+        if (cur.active && cur.kv_end > cur.kv_begin) {
+            tile_begin = cur.kv_begin / ST * ST;
+            num_tiles = (cur.kv_end - tile_begin + ST - 1) / ST;
+        }
+        // the next task continues this one: same Q rows, same request, its KV range starts where this one ends
+        const uint32_t carry_out =
+            (by_cell && p.direct == 0 && p.cu == nullptr && cur.active && nxt.active && nxt.tok_begin == cur.tok_begin &&
+             nxt.num_toks == cur.num_toks && nxt.head_begin == cur.head_begin && nxt.num_heads == cur.num_heads &&
+             nxt.req_slot == cur.req_slot && nxt.kv_begin == cur.kv_end && cur.kv_end > cur.kv_begin &&
+             nxt.kv_end > nxt.kv_begin)
+                ? 1u
+                : 0u;
+        if (cur.active && !aborted) {
+            const uint32_t slot = pushed % TQ;
+            const uint32_t phase = (pushed / TQ) & 1;
+            // the slot is free once the consumers AND the stream warp are done with the task it held
+            if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) aborted = true;
+            if (!aborted) {
+                TaskSlot* ts = task_ring + slot;
+                const uint32_t first_page = tile_begin / P;
+                const uint32_t num_pages = num_tiles ? (cur.kv_end + P - 1) / P - first_page : 0;
+                if (lane == 0) {
+                    ts->tmpl = cur.tmpl;
+                    ts->head_begin = cur.head_begin;
+                    ts->num_heads = cur.num_heads;
+                    ts->tok_begin = cur.tok_begin;
+                    ts->num_toks = cur.num_toks;
+                    ts->kv_begin = cur.kv_begin;
+                    ts->kv_end = cur.kv_end;
+                    ts->tile_begin = tile_begin;
+                    ts->num_tiles = num_tiles;
+                    ts->done = 0;
+                    ts->group = cur.group;
+                    ts->part_begin = cur.part_begin;
+                    ts->part_count = cur.part_count;
+                    ts->carry = carry_in | (carry_out << 1);
+                    ts->kv_head = cur.kv_head;
+                    ts->req_slot = cur.req_slot;
+                }
+                // page ids of the first segment (the stream warp stages later segments of a very long task itself)
+                {
+                    const uint64_t base =
+                        (uint64_t(cur.req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
+                    const uint32_t count = min(num_pages, uint32_t(kMaxPidsPerSegment));
+                    for (uint32_t i = lane; i < count; i += 32) {
+                        const uint32_t dst = smem_addr(pid_smem + slot * kMaxPidsPerSegment + i);
+                        const uint32_t* src = p.page_ids + base + first_page + i;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                }
+                if (p.visible != nullptr) {
+                    for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
+                        const uint32_t dst = smem_addr(&ts->visible[i]);
+                        const uint32_t* src = p.visible + uint64_t(cur.tok_begin) * 2 + i;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                    }
+                }
+                if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+                const uint32_t q_boxes = (p.debug & 4) ? 0u : cur.num_toks * NH;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
+                }
+                __syncwarp();
+                for (uint32_t b = lane; b < q_boxes; b += 32) {
+                    const uint32_t tok = b / NH;
+                    const uint32_t half = b % NH;
+                    const uint32_t dst = smem_addr(q_ring + slot * G::kQBytes + half * (G::kQRows * 128) +
+                                                   tok * p.heads_per_task * 128);
+                    const uint32_t row = (cur.tok_begin + tok) * p.num_q_heads + cur.head_begin;
+                    tma_load_2d(dst, &q_map, half * 64, static_cast<int32_t>(row), task_full_bar + 8 * slot);
+                }
+                // the page ids have landed: hand the task to the stream warp
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(stream_full_bar + 8 * slot);
+                ++pushed;
+            }
+        }
+        // advance
+        carry_in = carry_out;
+        cur = nxt;
+        if (next_lane == 0) {
+            batch_cur = batch_next;
+            batch_next = decode_batch(index + 1 + 32);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ---- tell the consumers and the stream warp there is nothing more
+    if (!aborted) {
+        const uint32_t slot = pushed % TQ;
+        const uint32_t phase = (pushed / TQ) & 1;
+        if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
+            if (lane == 0) {
+                task_ring[slot].done = 1;
+                mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
+                mbar_arrive(stream_full_bar + 8 * slot);
+            }
+            if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
+        }
+    }
+    // Abort path only: Q copies already issued may still be landing; wait (bounded) for them.
+    if (*abort_flag) {
+        for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
+            const uint32_t c = pushed - 1 - back;
+            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
+            }
+        }
+    }
+}
+
+// ------------------------------ stream warp -------------------------------------------
+// Issues the K/V copies of one published task after the other into the stage ring. The per-stage loop runs in
+// lane 0 alone, with running slot / phase / token counters and 32-bit row arithmetic: this loop is the one
+// instruction stream that has to keep the copy engine fed, and it reads shared memory only.
+template <typename G, int P>
+__device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtensorMap& kv_map, const ProducerContext& c) {
+    constexpr int ST = G::kStageTokens;
+    constexpr int NS = G::kStages;
+    constexpr int TQ = G::kTaskSlots;
+    uint8_t* const ring = c.ring;
+    uint32_t* const pid_smem = c.pid_smem;
+    TaskSlot* const task_ring = c.task_ring;
+    const uint32_t full_bar = c.full_bar, empty_bar = c.empty_bar, task_empty_bar = c.task_empty_bar;
+    const uint32_t stream_full_bar = c.stream_full_bar;
+    volatile uint32_t* const abort_flag = c.abort_flag;
+    const int lane = c.lane;
+    uint32_t stage_counter = 0;
+    bool aborted = false;
+    const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
+    for (uint32_t taken = 0; !aborted; ++taken) {
+        const uint32_t tslot = taken % TQ;
+        if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+        const TaskSlot* ts = task_ring + tslot;
+        if (ts->done) break;
+        const uint32_t tile_begin = ts->tile_begin, num_tiles = ts->num_tiles, kv_end = ts->kv_end;
+        const uint32_t head_row = ts->kv_head * P;
+        if (num_tiles > 0) {
+            constexpr uint32_t kTilesPerSegment = uint32_t(kMaxPidsPerSegment) * P / ST;
+            const uint32_t first_page = tile_begin / P;
+            const uint32_t num_pages = (kv_end + P - 1) / P - first_page;
+            const uint32_t* pids = pid_smem + tslot * kMaxPidsPerSegment;
+            for (uint32_t seg_tile = 0; seg_tile < num_tiles && !aborted; seg_tile += kTilesPerSegment) {
+                if (seg_tile > 0) {
+                    // a task longer than one segment: restage the next run of page ids (whole warp)
+                    const uint32_t seg_first = first_page + seg_tile * (ST / P);
+                    const uint32_t count = min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment));
+                    const uint64_t base =
+                        (uint64_t(ts->req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
+                    __syncwarp();
+                    for (uint32_t i = lane; i < count; i += 32) {
+                        const uint32_t dst = smem_addr(pid_smem + tslot * kMaxPidsPerSegment + i);
+                        const uint32_t* src = p.page_ids + base + seg_first + i;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncwarp();
+                }
+                const uint32_t seg_tiles = min(num_tiles - seg_tile, kTilesPerSegment);
+                uint32_t failed = 0;
+                if (lane == 0) {
+                    uint32_t slot = stage_counter % NS;
+                    uint32_t parity = ((stage_counter / NS) & 1) ^ 1;
+                    uint32_t tile_tok = tile_begin + seg_tile * ST;
+                    uint32_t page_in_seg = 0;
+                    for (uint32_t tile = 0; tile < seg_tiles; ++tile) {
+                        const uint32_t bar = full_bar + 8 * slot;
+                        if (!mbar_wait(empty_bar + 8 * slot, parity, abort_flag, p.status)) {
+                            failed = tile + 1;
+                            break;
+                        }
+                        const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
+                        if (tile_tok + ST <= kv_end && !(p.debug & 8)) {
+                            mbar_arrive_expect_tx(bar, G::kStageBytes);
+#pragma unroll
+                            for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                const uint32_t tok_in_page = (b * G::kBoxRows) % P;
+                                const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
+                                if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
+                                            static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar);
+                            }
+                        } else {
+                            // the task's last stage (or the measurement mode without copies): only boxes that hold
+                            // a token below kv_end are fetched
+                            uint32_t boxes_needed = 0;
+#pragma unroll
+                            for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                if (tile_tok + b * G::kBoxRows < kv_end) ++boxes_needed;
+                            }
+                            if (p.debug & 8) boxes_needed = 0;
+                            mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
+#pragma unroll
+                            for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                                if (uint32_t(b) < boxes_needed) {
+                                    const uint32_t tok_in_page = (b * G::kBoxRows) % P;
+                                    const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
+                                    if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                    tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
+                                                static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0,
+                                                bar);
+                                }
+                            }
+                        }
+                        tile_tok += ST;
+                        page_in_seg += ST / P;
+                        if (++slot == NS) {
+                            slot = 0;
+                            parity ^= 1;
+                        }
+                    }
+                }
+                failed = __shfl_sync(0xffffffffu, failed, 0);
+                if (failed) {
+                    aborted = true;
+                    stage_counter += failed - 1;
+                } else {
+                    stage_counter += seg_tiles;
+                }
+            }
+        }
+        // done with the task's descriptor and page ids
+        __syncwarp();
+        if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+    }
+    // Abort path only: copies already issued may still be landing; wait (bounded) for each ring slot's
+    // last issued phase before the CTA may retire.
+    if (*abort_flag) {
+        for (uint32_t back = 0; back < uint32_t(NS) && back < stage_counter; ++back) {
+            const uint32_t c = stage_counter - 1 - back;
+            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                if (mbar_try_wait(full_bar + 8 * (c % NS), (c / NS) & 1)) break;
+            }
+        }
+    }
+}
+
 template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF>
 __global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, PS, HALF>::kThreads, 1)
 sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
@@ -493,7 +806,6 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     constexpr int DK = D / 16;       // QK k-steps
     constexpr int DN = D / 8;        // O n-tiles
     constexpr int NROW = HALF ? 1 : 2;  // fragment rows (g, g + 8) that can be valid
-    constexpr int NH = G::kColumnHalves;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -589,277 +901,27 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     const uint32_t task_step = balanced ? 1u : gridDim.x;
     const uint32_t task_limit = balanced ? task_range[1] : total_tasks;
 
+    ProducerContext producer{};
+    producer.ring = ring;
+    producer.q_ring = q_ring;
+    producer.pid_smem = pid_smem;
+    producer.task_ring = task_ring;
+    producer.full_bar = full_bar;
+    producer.empty_bar = empty_bar;
+    producer.task_full_bar = task_full_bar;
+    producer.task_empty_bar = task_empty_bar;
+    producer.stream_full_bar = stream_full_bar;
+    producer.abort_flag = abort_flag;
+    producer.task_base = task_base;
+    producer.task_step = task_step;
+    producer.task_limit = task_limit;
+    producer.balanced = balanced;
+    producer.allow_carry = true;
+    producer.lane = lane;
     if (warp == NCW + 1) {
-        // ------------------------------ task warp ---------------------------------------------
-        // Decodes this CTA's tasks (32 at a time, one per lane) and publishes them one task ahead of the
-        // stream warp: descriptor, per-token visibility rows and Q rows for the consumers, the page ids of the
-        // task's first segment for the stream warp. Everything here has global-memory latency in it; keeping it
-        // off the stream warp is what lets that warp issue K/V copies without a pause at task boundaries.
-        uint32_t pushed = 0;  // task-ring pushes so far
-
-        // Order in which this CTA visits its contiguous run [task_base, task_limit) of template-major tasks: cell by
-        // cell (cell = KV head x Q-head range), and within a cell template after template. Neighbours in this order
-        // are consecutive KV slices of the same Q rows, so the consumers can carry their running state from one
-        // task into the next instead of merging and publishing at every slice boundary.
-        const uint32_t cells = p.num_kv_heads * p.head_ranges;
-        const bool by_cell = balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) == 0;
-        const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
-        const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
-        auto visit_to_task = [&](uint64_t visit) -> uint64_t {
-            if (!by_cell) return task_base + visit * task_step;
-            if (visit >= task_limit - task_base) return task_limit;
-            uint32_t before = 0;
-            for (uint32_t c = 0; c < cells; ++c) {
-                const uint32_t first_row = c >= run_c0 ? run_r0 : run_r0 + 1;
-                const uint32_t end_row = c < run_c1 ? run_r1 + 1 : run_r1;  // one past the cell's last row
-                const uint32_t count = end_row > first_row ? end_row - first_row : 0;
-                if (visit < before + count) return uint64_t(first_row + (uint32_t(visit) - before)) * cells + c;
-                before += count;
-            }
-            return task_limit;
-        };
-        // Lane l decodes this CTA's visit number first_index + l.
-        auto decode_batch = [&](uint32_t first_index) {
-            return decode_task(p, visit_to_task(uint64_t(first_index) + lane), task_limit);
-        };
-        uint32_t carry_in = 0;
-
-        // Two batches of 32 decoded tasks live in registers.
-        TaskInfo batch_cur = decode_batch(0);
-        TaskInfo batch_next = decode_batch(32);
-        TaskInfo cur = shfl_task(batch_cur, 0);
-        bool aborted = false;
-        for (uint32_t index = 0;; ++index) {
-            if (visit_to_task(index) >= task_limit) break;
-            // next task's descriptor: from the current batch, or lane 0 of the next one
-            const uint32_t next_lane = (index + 1) & 31;
-            const TaskInfo nxt = next_lane == 0 ? shfl_task(batch_next, 0) : shfl_task(batch_cur, next_lane);
-
-            uint32_t tile_begin = 0, num_tiles = 0;
-            if (cur.active && cur.kv_end > cur.kv_begin) {
-                tile_begin = cur.kv_begin / ST * ST;
-                num_tiles = (cur.kv_end - tile_begin + ST - 1) / ST;
-            }
-            // the next task continues this one: same Q rows, same request, its KV range starts where this one ends
-            const uint32_t carry_out =
-                (by_cell && p.direct == 0 && p.cu == nullptr && cur.active && nxt.active && nxt.tok_begin == cur.tok_begin &&
-                 nxt.num_toks == cur.num_toks && nxt.head_begin == cur.head_begin && nxt.num_heads == cur.num_heads &&
-                 nxt.req_slot == cur.req_slot && nxt.kv_begin == cur.kv_end && cur.kv_end > cur.kv_begin &&
-                 nxt.kv_end > nxt.kv_begin)
-                    ? 1u
-                    : 0u;
-            if (cur.active && !aborted) {
-                const uint32_t slot = pushed % TQ;
-                const uint32_t phase = (pushed / TQ) & 1;
-                // the slot is free once the consumers AND the stream warp are done with the task it held
-                if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) aborted = true;
-                if (!aborted) {
-                    TaskSlot* ts = task_ring + slot;
-                    const uint32_t first_page = tile_begin / P;
-                    const uint32_t num_pages = num_tiles ? (cur.kv_end + P - 1) / P - first_page : 0;
-                    if (lane == 0) {
-                        ts->tmpl = cur.tmpl;
-                        ts->head_begin = cur.head_begin;
-                        ts->num_heads = cur.num_heads;
-                        ts->tok_begin = cur.tok_begin;
-                        ts->num_toks = cur.num_toks;
-                        ts->kv_begin = cur.kv_begin;
-                        ts->kv_end = cur.kv_end;
-                        ts->tile_begin = tile_begin;
-                        ts->num_tiles = num_tiles;
-                        ts->done = 0;
-                        ts->group = cur.group;
-                        ts->part_begin = cur.part_begin;
-                        ts->part_count = cur.part_count;
-                        ts->carry = carry_in | (carry_out << 1);
-                        ts->kv_head = cur.kv_head;
-                        ts->req_slot = cur.req_slot;
-                    }
-                    // page ids of the first segment (the stream warp stages later segments of a very long task itself)
-                    {
-                        const uint64_t base =
-                            (uint64_t(cur.req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
-                        const uint32_t count = min(num_pages, uint32_t(kMaxPidsPerSegment));
-                        for (uint32_t i = lane; i < count; i += 32) {
-                            const uint32_t dst = smem_addr(pid_smem + slot * kMaxPidsPerSegment + i);
-                            const uint32_t* src = p.page_ids + base + first_page + i;
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-                        }
-                        asm volatile("cp.async.commit_group;" ::: "memory");
-                    }
-                    if (p.visible != nullptr) {
-                        for (uint32_t i = lane; i < 2 * cur.num_toks; i += 32) {
-                            const uint32_t dst = smem_addr(&ts->visible[i]);
-                            const uint32_t* src = p.visible + uint64_t(cur.tok_begin) * 2 + i;
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-                        }
-                    }
-                    if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-                    const uint32_t q_boxes = (p.debug & 4) ? 0u : cur.num_toks * NH;
-                    if (lane == 0) {
-                        mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
-                    }
-                    __syncwarp();
-                    for (uint32_t b = lane; b < q_boxes; b += 32) {
-                        const uint32_t tok = b / NH;
-                        const uint32_t half = b % NH;
-                        const uint32_t dst = smem_addr(q_ring + slot * G::kQBytes + half * (G::kQRows * 128) +
-                                                       tok * p.heads_per_task * 128);
-                        const uint32_t row = (cur.tok_begin + tok) * p.num_q_heads + cur.head_begin;
-                        tma_load_2d(dst, &q_map, half * 64, static_cast<int32_t>(row), task_full_bar + 8 * slot);
-                    }
-                    // the page ids have landed: hand the task to the stream warp
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(stream_full_bar + 8 * slot);
-                    ++pushed;
-                }
-            }
-            // advance
-            carry_in = carry_out;
-            cur = nxt;
-            if (next_lane == 0) {
-                batch_cur = batch_next;
-                batch_next = decode_batch(index + 1 + 32);
-            }
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        // ---- tell the consumers and the stream warp there is nothing more
-        if (!aborted) {
-            const uint32_t slot = pushed % TQ;
-            const uint32_t phase = (pushed / TQ) & 1;
-            if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
-                if (lane == 0) {
-                    task_ring[slot].done = 1;
-                    mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
-                    mbar_arrive(stream_full_bar + 8 * slot);
-                }
-                if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-            }
-        }
-        // Abort path only: Q copies already issued may still be landing; wait (bounded) for them.
-        if (*abort_flag) {
-            for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
-                const uint32_t c = pushed - 1 - back;
-                for (uint32_t i = 0; i < kWaitLimit; ++i) {
-                    if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
-                }
-            }
-        }
+        run_task_warp<G, P>(p, q_map, producer);
     } else if (warp == NCW) {
-        // ------------------------------ stream warp -------------------------------------------
-        // Issues the K/V copies of one published task after the other into the stage ring. The per-stage loop runs
-        // in lane 0 alone, with running slot / phase / token counters and 32-bit row arithmetic: this loop is the
-        // one instruction stream that has to keep the copy engine fed, and it reads shared memory only.
-        uint32_t stage_counter = 0;
-        bool aborted = false;
-        const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
-        for (uint32_t taken = 0; !aborted; ++taken) {
-            const uint32_t tslot = taken % TQ;
-            if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
-            const TaskSlot* ts = task_ring + tslot;
-            if (ts->done) break;
-            const uint32_t tile_begin = ts->tile_begin, num_tiles = ts->num_tiles, kv_end = ts->kv_end;
-            const uint32_t head_row = ts->kv_head * P;
-            if (num_tiles > 0) {
-                constexpr uint32_t kTilesPerSegment = uint32_t(kMaxPidsPerSegment) * P / ST;
-                const uint32_t first_page = tile_begin / P;
-                const uint32_t num_pages = (kv_end + P - 1) / P - first_page;
-                const uint32_t* pids = pid_smem + tslot * kMaxPidsPerSegment;
-                for (uint32_t seg_tile = 0; seg_tile < num_tiles && !aborted; seg_tile += kTilesPerSegment) {
-                    if (seg_tile > 0) {
-                        // a task longer than one segment: restage the next run of page ids (whole warp)
-                        const uint32_t seg_first = first_page + seg_tile * (ST / P);
-                        const uint32_t count = min(first_page + num_pages - seg_first, uint32_t(kMaxPidsPerSegment));
-                        const uint64_t base =
-                            (uint64_t(ts->req_slot) * p.num_gqa_layers + p.layer_index) * p.pages_per_request_layer;
-                        __syncwarp();
-                        for (uint32_t i = lane; i < count; i += 32) {
-                            const uint32_t dst = smem_addr(pid_smem + tslot * kMaxPidsPerSegment + i);
-                            const uint32_t* src = p.page_ids + base + seg_first + i;
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-                        }
-                        asm volatile("cp.async.commit_group;" ::: "memory");
-                        asm volatile("cp.async.wait_group 0;" ::: "memory");
-                        __syncwarp();
-                    }
-                    const uint32_t seg_tiles = min(num_tiles - seg_tile, kTilesPerSegment);
-                    uint32_t failed = 0;
-                    if (lane == 0) {
-                        uint32_t slot = stage_counter % NS;
-                        uint32_t parity = ((stage_counter / NS) & 1) ^ 1;
-                        uint32_t tile_tok = tile_begin + seg_tile * ST;
-                        uint32_t page_in_seg = 0;
-                        for (uint32_t tile = 0; tile < seg_tiles; ++tile) {
-                            const uint32_t bar = full_bar + 8 * slot;
-                            if (!mbar_wait(empty_bar + 8 * slot, parity, abort_flag, p.status)) {
-                                failed = tile + 1;
-                                break;
-                            }
-                            const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
-                            if (tile_tok + ST <= kv_end && !(p.debug & 8)) {
-                                mbar_arrive_expect_tx(bar, G::kStageBytes);
-#pragma unroll
-                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                                    const uint32_t tok_in_page = (b * G::kBoxRows) % P;
-                                    const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
-                                    if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
-                                    tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
-                                                static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar);
-                                }
-                            } else {
-                                // the task's last stage (or the measurement mode without copies): only boxes that hold
-                                // a token below kv_end are fetched
-                                uint32_t boxes_needed = 0;
-#pragma unroll
-                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                                    if (tile_tok + b * G::kBoxRows < kv_end) ++boxes_needed;
-                                }
-                                if (p.debug & 8) boxes_needed = 0;
-                                mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
-#pragma unroll
-                                for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                                    if (uint32_t(b) < boxes_needed) {
-                                        const uint32_t tok_in_page = (b * G::kBoxRows) % P;
-                                        const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
-                                        if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
-                                        tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
-                                                    static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0,
-                                                    bar);
-                                    }
-                                }
-                            }
-                            tile_tok += ST;
-                            page_in_seg += ST / P;
-                            if (++slot == NS) {
-                                slot = 0;
-                                parity ^= 1;
-                            }
-                        }
-                    }
-                    failed = __shfl_sync(0xffffffffu, failed, 0);
-                    if (failed) {
-                        aborted = true;
-                        stage_counter += failed - 1;
-                    } else {
-                        stage_counter += seg_tiles;
-                    }
-                }
-            }
-            // done with the task's descriptor and page ids
-            __syncwarp();
-            if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
-        }
-        // Abort path only: copies already issued may still be landing; wait (bounded) for each ring slot's
-        // last issued phase before the CTA may retire.
-        if (*abort_flag) {
-            for (uint32_t back = 0; back < uint32_t(NS) && back < stage_counter; ++back) {
-                const uint32_t c = stage_counter - 1 - back;
-                for (uint32_t i = 0; i < kWaitLimit; ++i) {
-                    if (mbar_try_wait(full_bar + 8 * (c % NS), (c / NS) & 1)) break;
-                }
-            }
-        }
+        run_stream_warp<G, P>(p, kv_map, producer);
     } else {
         // ------------------------------ consumer warps ----------------------------------------
         const int mt = warp % MT;           // row tile
