@@ -14,7 +14,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libkhcuda_gqa.so"
 SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "kv_page_write.cu"]
-HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "sdpa_map.cuh", "../../include/kh_gqa.h"]
+HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "sdpa_map.cuh", "sdpa_tc.cuh", "../../include/kh_gqa.h"]
 
 
 def nvcc_path() -> str:

@@ -451,11 +451,19 @@ Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* request
     } else {
         const uint32_t head_groups = c.num_kv_heads * div_ceil(ratio, variant.max_q_heads);
         unsigned __int128 work = 0;
+        uint64_t tiles_total = 0;
         for (uint32_t r = 0; r < num_requests; ++r) {
             const uint32_t tiles = div_ceil(requests[r].num_q_tokens, variant.max_q_tokens);
+            tiles_total += tiles;
             work += (unsigned __int128)tiles * (requests[r].num_history_tokens + requests[r].num_q_tokens);
         }
-        slice = decode_slice(end, work * head_groups, 256, 2048, (unsigned __int128)sm_count * kTasksPerSm);
+        if (sliced_q && tiles_total * head_groups >= uint64_t(sm_count) * kTasksPerSm) {
+            // enough (Q tile, head group) tasks to fill every SM several times over without cutting the KV range:
+            // one task per tile writes the output directly, no partials and no reduce (chunked prefill)
+            slice = end;
+        } else {
+            slice = decode_slice(end, work * head_groups, 256, 2048, (unsigned __int128)sm_count * kTasksPerSm);
+        }
     }
     const bool direct = sliced_q && slice == end;
     return Route{variant, slice, direct};

@@ -16,6 +16,7 @@
 #include "cuda_objects.h"
 #include "host_sdpa.h"
 #include "sdpa_map.cuh"
+#include "sdpa_tc.cuh"
 
 namespace kh {
 
@@ -170,29 +171,42 @@ static MapInstance make_instance() {
 // take one page each, two warps per SM sub-partition so that one warp's softmax overlaps the other's
 // MMAs. head_dim 256: a stage is 16 KV tokens (one page) and a thread carries a 16 x 256 f32 accumulator
 // (128 registers), so 4 consumer warps run with up to 255 registers each.
+// Tasks of more than 64 rows (prefill and long verify tiles) at head_dim 128 run on tcgen05 with tensor-memory
+// accumulators; KH_GQA_NO_TCGEN05 selects the warp-level instance instead (comparison runs).
 template <typename T, int D, int P>
-static MapInstance pick_rows(uint32_t rows) {
+static MapInstance make_tc_instance() {
+    using G = TcGeometry<D, P>;
+    return MapInstance{sdpa_tc_kernel<T, D, P>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows, G::kStages};
+}
+
+template <typename T, int D, int P>
+static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     constexpr int PS = 1;
     if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();
     if (rows <= 16) return make_instance<T, D, P, 1, 4, PS, false>();
     if (rows <= 32) return make_instance<T, D, P, 2, 2, PS, false>();
     if (rows <= 64) return make_instance<T, D, P, 4, 1, PS, false>();
+    if constexpr (D == 128 && P == 16) {
+        static const bool warp_level = std::getenv("KH_GQA_NO_TCGEN05") != nullptr;
+        if (tensor_memory && !warp_level) return make_tc_instance<T, D, P>();
+    }
     return make_instance<T, D, P, 8, 1, 1, false>();
 }
 
 template <typename T>
-static MapInstance pick_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+static MapInstance pick_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows, bool tensor_memory) {
     KH_REQUIRE(tokens_per_page == 16, "this build instantiates 16-token pages only (got %u)", tokens_per_page);
-    if (head_dim == 128) return pick_rows<T, 128, 16>(rows);
+    if (head_dim == 128) return pick_rows<T, 128, 16>(rows, tensor_memory);
     KH_REQUIRE(head_dim == 256, "this build instantiates head_dim 128 and 256 only (got %u)", head_dim);
-    return pick_rows<T, 256, 16>(rows);
+    return pick_rows<T, 256, 16>(rows, tensor_memory);
 }
 
-static MapInstance pick_instance(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+static MapInstance pick_instance(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows,
+                                 bool tensor_memory) {
     KH_REQUIRE(rows >= 1 && rows <= 128, "a Map task holds at most 128 (Q token, Q head) rows (got %u)", rows);
-    if (dtype == KH_DTYPE_BFLOAT16) return pick_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows);
+    if (dtype == KH_DTYPE_BFLOAT16) return pick_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows, tensor_memory);
     KH_REQUIRE(dtype == KH_DTYPE_FLOAT16, "Q/output dtype must be Bfloat16 or Float16 on this backend");
-    return pick_geometry<__half>(head_dim, tokens_per_page, rows);
+    return pick_geometry<__half>(head_dim, tokens_per_page, rows, tensor_memory);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -230,6 +244,7 @@ struct ComputeCommon {
     kh_page_table_layout layout;
     kh_execution_variant variant;
     MapInstance instance;
+    MapInstance fused_instance;
     std::vector<PoolMap> pool_maps;
     std::vector<PoolMap> q_maps;
 
@@ -308,9 +323,14 @@ static void init_common(ComputeCommon& c, kh_device* device, kh_dtype dtype, kh_
     c.layout = layout;
     c.variant = variant;
     c.tokens_per_page = page_bytes / (2 * num_kv_heads * head_dim * dtype_size(kv_dtype));
-    c.instance = pick_instance(dtype, head_dim, c.tokens_per_page, variant.max_q_tokens * variant.max_q_heads);
+    const uint32_t rows = variant.max_q_tokens * variant.max_q_heads;
+    c.instance = pick_instance(dtype, head_dim, c.tokens_per_page, rows, true);
+    // the one-launch map + reduce form counts arrivals inside the warp-level kernel
+    c.fused_instance = pick_instance(dtype, head_dim, c.tokens_per_page, rows, false);
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.instance.kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, c.instance.smem_bytes));
+    KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.fused_instance.kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, c.fused_instance.smem_bytes));
 }
 
 static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buffer_ref q, kh_buffer_ref kv_pages,
@@ -342,7 +362,8 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     const uint64_t tasks = uint64_t(num_templates) * c.num_kv_heads * p.head_ranges;
     KH_REQUIRE(tasks <= 0xffffffffull, "GQA SDPA map task count must fit u32");
     const uint32_t grid = static_cast<uint32_t>(std::min<uint64_t>(tasks, uint64_t(c.device->sm_count)));
-    c.instance.kernel<<<grid, c.instance.threads, c.instance.smem_bytes, stream->stream>>>(map, qmap, p);
+    const MapInstance& instance = p.cu != nullptr ? c.fused_instance : c.instance;
+    instance.kernel<<<grid, instance.threads, instance.smem_bytes, stream->stream>>>(map, qmap, p);
     KH_CUDA(cudaGetLastError());
 }
 

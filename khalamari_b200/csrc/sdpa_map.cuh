@@ -477,6 +477,57 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
     return r;
 }
 
+// Which tasks a CTA runs. Tasks are numbered template-major. With few enough templates every CTA scans them all
+// (12 bytes each) and takes one CONTIGUOUS run of tasks whose cost - KV tokens plus a fixed per-task term - is its
+// 1/gridDim share of the total: task k belongs to the CTA c with
+// c * W / grid <= cost of tasks [0, k) < (c + 1) * W / grid. No CTA carries more than its share plus one task,
+// where dealing tasks round-robin leaves the CTAs that drew the long slices several percent behind. Contiguous
+// tasks are also neighbours in the page table. Returns false above the template limit (tasks are then dealt
+// round-robin). Called by every thread of the CTA; `scan` is shared scratch of `threads` u64 that nothing else
+// uses until the call returns, `task_range` two shared words that receive [begin, end).
+__device__ __forceinline__ bool balanced_task_range(const MapParams& p, uint64_t* scan, uint32_t* task_range,
+                                                    uint32_t threads) {
+    if (p.num_templates > kBalanceMaxTemplates) return false;
+    const uint32_t cells = p.num_kv_heads * p.head_ranges;
+    const uint32_t chunk = (p.num_templates + threads - 1) / threads;
+    const uint32_t first = min(threadIdx.x * chunk, p.num_templates);
+    const uint32_t last = min(first + chunk, p.num_templates);
+    auto cost_of = [&](uint32_t t) -> uint64_t {
+        const uint32_t kv_begin = p.templates[t * 3 + 1];
+        const uint32_t kv_end = p.templates[t * 3 + 2];
+        if (p.templates[t * 3] == 0xffffffffu || kv_end <= kv_begin) return 1;
+        return uint64_t(kv_end - kv_begin) + kTaskOverheadTokens;
+    };
+    uint64_t local = 0;
+    for (uint32_t t = first; t < last; ++t) local += cost_of(t);
+    scan[threadIdx.x] = local;
+    if (threadIdx.x == 0) {
+        task_range[0] = 0;
+        task_range[1] = 0;
+    }
+    __syncthreads();
+    uint64_t before = 0, total = 0;
+    for (uint32_t i = 0; i < threads; ++i) {
+        const uint64_t v = scan[i];
+        if (i < threadIdx.x) before += v;
+        total += v;
+    }
+    const uint64_t whole = total * cells;
+    const uint64_t lo = whole / gridDim.x * blockIdx.x + whole % gridDim.x * blockIdx.x / gridDim.x;
+    const uint64_t hi = whole / gridDim.x * (blockIdx.x + 1) + whole % gridDim.x * (blockIdx.x + 1) / gridDim.x;
+    // first task whose preceding cost reaches x: inside the template whose cost interval (S, E] holds x
+    uint64_t start = before * cells;
+    for (uint32_t t = first; t < last; ++t) {
+        const uint64_t c = cost_of(t);
+        const uint64_t end = start + c * cells;
+        if (lo > start && lo <= end) task_range[0] = t * cells + uint32_t((lo - start + c - 1) / c);
+        if (hi > start && hi <= end) task_range[1] = t * cells + uint32_t((hi - start + c - 1) / c);
+        start = end;
+    }
+    __syncthreads();  // the scan scratch is read for the last time before this barrier
+    return true;
+}
+
 // What the producer-side warps of a kernel instance need: where the rings and barriers live, and which tasks this
 // CTA runs. Built once per thread after the prologue.
 struct ProducerContext {
@@ -849,54 +900,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
 
     const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
 
-    // ---- which tasks this CTA runs. Tasks are numbered template-major. With few enough templates every CTA
-    // scans them all (12 bytes each) and takes one CONTIGUOUS run of tasks whose cost - KV tokens plus a fixed
-    // per-task term - is its 1/gridDim share of the total: task k belongs to the CTA c with
-    // c * W / grid <= cost of tasks [0, k) < (c + 1) * W / grid. No CTA carries more than its share plus one
-    // task, where dealing tasks round-robin leaves the CTAs that drew the long slices several percent behind.
-    // Contiguous tasks are also neighbours in the page table. Above the limit tasks are dealt round-robin.
     uint32_t* task_range = const_cast<uint32_t*>(last_flag) + 1;  // [begin, end) of this CTA's run
-    const bool balanced = p.num_templates <= kBalanceMaxTemplates;
-    if (balanced) {
-        const uint32_t cells = p.num_kv_heads * p.head_ranges;
-        uint64_t* scan = reinterpret_cast<uint64_t*>(ring);  // the ring is idle until the producer starts
-        const uint32_t chunk = (p.num_templates + G::kThreads - 1) / G::kThreads;
-        const uint32_t first = min(threadIdx.x * chunk, p.num_templates);
-        const uint32_t last = min(first + chunk, p.num_templates);
-        auto cost_of = [&](uint32_t t) -> uint64_t {
-            const uint32_t kv_begin = p.templates[t * 3 + 1];
-            const uint32_t kv_end = p.templates[t * 3 + 2];
-            if (p.templates[t * 3] == 0xffffffffu || kv_end <= kv_begin) return 1;
-            return uint64_t(kv_end - kv_begin) + kTaskOverheadTokens;
-        };
-        uint64_t local = 0;
-        for (uint32_t t = first; t < last; ++t) local += cost_of(t);
-        scan[threadIdx.x] = local;
-        if (threadIdx.x == 0) {
-            task_range[0] = 0;
-            task_range[1] = 0;
-        }
-        __syncthreads();
-        uint64_t before = 0, total = 0;
-        for (uint32_t i = 0; i < uint32_t(G::kThreads); ++i) {
-            const uint64_t v = scan[i];
-            if (i < threadIdx.x) before += v;
-            total += v;
-        }
-        const uint64_t whole = total * cells;
-        const uint64_t lo = whole / gridDim.x * blockIdx.x + whole % gridDim.x * blockIdx.x / gridDim.x;
-        const uint64_t hi = whole / gridDim.x * (blockIdx.x + 1) + whole % gridDim.x * (blockIdx.x + 1) / gridDim.x;
-        // first task whose preceding cost reaches x: inside the template whose cost interval (S, E] holds x
-        uint64_t start = before * cells;
-        for (uint32_t t = first; t < last; ++t) {
-            const uint64_t c = cost_of(t);
-            const uint64_t end = start + c * cells;
-            if (lo > start && lo <= end) task_range[0] = t * cells + uint32_t((lo - start + c - 1) / c);
-            if (hi > start && hi <= end) task_range[1] = t * cells + uint32_t((hi - start + c - 1) / c);
-            start = end;
-        }
-        __syncthreads();  // also: the scan scratch (the ring) is read for the last time before this barrier
-    }
+    const bool balanced = balanced_task_range(p, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
     const uint32_t task_base = balanced ? task_range[0] : blockIdx.x;
     const uint32_t task_step = balanced ? 1u : gridDim.x;
     const uint32_t task_limit = balanced ? task_range[1] : total_tasks;

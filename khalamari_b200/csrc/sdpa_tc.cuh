@@ -1,0 +1,494 @@
+// SlicedQ map / direct kernel for tasks of up to 128 (Q token, Q head) rows on the 5th-generation tensor
+// cores: tcgen05.mma with the accumulators in tensor memory. Same task ABI, rings, task warp and stream warp as
+// sdpa_map_kernel (sdpa_map.cuh); only the consumers differ.
+//
+//   S = Q K^T   tcgen05.mma kind::f16, M = 128 rows, N = 16 KV tokens (one page), K = 16 head-dim elements per
+//               instruction: A = the Q tile and B = the K rows of the page, both K-major with the 128-byte
+//               swizzle exactly as the TMA copies leave them in shared memory. A stage of 32 tokens is two pages.
+//   P           four softmax warps, one thread per row: tcgen05.ld brings the thread its row's 32 scores, so the
+//               row maximum and sum need no shuffles. P goes back to tensor memory as packed 16-bit pairs
+//               (rounded part and rounding remainder, as in the warp-level kernel).
+//   O += P V    A = P from tensor memory, B = the V rows of the page in shared memory, MN-major (V is stored
+//               [token][head dim], the head dim being the contiguous N dimension), N = 128.
+// The running maximum is updated lazily: O (in tensor memory) is rescaled only when a row's maximum grows by more
+// than 2^8, so the common stage costs one tensor-memory load and two stores per thread.
+//
+// Warps: 0-3 softmax and epilogue, 4 MMA issue (one thread), 5 stream warp (K/V copies), 6 task warp.
+// Every wait is bounded (mbar_wait); tensor memory is allocated once and freed on every exit path.
+#pragma once
+
+#include "sdpa_map.cuh"
+
+namespace kh {
+
+template <int D, int P>
+struct TcGeometry {
+    static_assert(D == 128 && P == 16, "the tensor-memory instance is built for head_dim 128 and 16-token pages");
+    static constexpr int kStageTokens = 32;
+    static constexpr int kBoxRows = 16;
+    static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;
+    static constexpr int kColumnHalves = D / 64;
+    static constexpr int kBoxBytes = kBoxRows * 128;
+    static constexpr int kPlaneBoxBytes = kColumnHalves * kBoxBytes;
+    static constexpr int kCopyBytes = 2 * kPlaneBoxBytes;
+    static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;
+    static constexpr int kQRows = 128;
+    static constexpr int kQBytes = kQRows * D * 2;
+    static constexpr int kTaskSlots = 2;
+    static constexpr int kSoftmaxWarps = 4;
+    static constexpr int kThreads = (kSoftmaxWarps + 3) * 32;
+    static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
+    static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
+    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kPidBytes + kTaskBytes + 1024;
+    static constexpr int kSmemLimit = 227 * 1024 - 1024;
+    static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+    static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
+    static constexpr uint32_t kTmemColumns = 512;  // O 128 | S 2 x 32 | P 2 x (16 rounded + 16 remainder) | Q 2 x 64
+    static_assert(kStages >= 4, "shared memory ring too small");
+};
+
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    // start address, leading-dimension and stride-dimension byte offsets in 16-byte units, descriptor version 1,
+    // 128-byte swizzle
+    return uint64_t((addr >> 4) & 0x3fffu) | (uint64_t((leading_bytes >> 4) & 0x3fffu) << 16) |
+           (uint64_t((stride_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// Arrives on `bar` once every tcgen05 operation this thread issued before has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <typename T>
+__device__ __forceinline__ constexpr uint32_t umma_format();
+template <>
+__device__ __forceinline__ constexpr uint32_t umma_format<__half>() { return 0u; }
+template <>
+__device__ __forceinline__ constexpr uint32_t umma_format<__nv_bfloat16>() { return 1u; }
+
+template <typename T, int D, int P>
+__global__ void __launch_bounds__(TcGeometry<D, P>::kThreads, 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
+    using G = TcGeometry<D, P>;
+    constexpr int ST = G::kStageTokens;
+    constexpr int NS = G::kStages;
+    constexpr int TQ = G::kTaskSlots;
+    constexpr int NSW = G::kSoftmaxWarps;
+    constexpr float kRescaleLog2 = 8.0f;  // O is rescaled only when a row maximum grows by more than 2^8
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    uint8_t* q_ring = ring + NS * G::kStageBytes;
+    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(q_ring + TQ * G::kQBytes);
+    TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
+    constexpr int kNumBars = 2 * NS + 3 * TQ + 12;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
+    uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 1;
+    uint32_t* tmem_slot = task_range + 2;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t full_bar = smem_addr(bars);
+    const uint32_t empty_bar = smem_addr(bars + NS);
+    const uint32_t task_full_bar = smem_addr(bars + 2 * NS);
+    const uint32_t task_empty_bar = smem_addr(bars + 2 * NS + TQ);
+    const uint32_t stream_full_bar = smem_addr(bars + 2 * NS + 2 * TQ);
+    const uint32_t s_full_bar = smem_addr(bars + 2 * NS + 3 * TQ);       // [2] scores of a stage are in tensor memory
+    const uint32_t s_free_bar = smem_addr(bars + 2 * NS + 3 * TQ + 2);   // [2] the softmax warps have read them
+    const uint32_t p_full_bar = smem_addr(bars + 2 * NS + 3 * TQ + 4);   // [2] probabilities of a stage are stored
+    const uint32_t pv_done_bar = smem_addr(bars + 2 * NS + 3 * TQ + 6);  // [2] the stage's P V products completed
+    const uint32_t o_free_bar = smem_addr(bars + 2 * NS + 3 * TQ + 8);   // the epilogue has read O
+    const uint32_t drain_bar = smem_addr(bars + 2 * NS + 3 * TQ + 9);    // every issued tcgen05 operation completed
+    const uint32_t q_ready_bar = smem_addr(bars + 2 * NS + 3 * TQ + 10); // [2] a task's Q tile is in tensor memory
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);  // one tcgen05.commit per stage
+        }
+        for (int s = 0; s < TQ; ++s) {
+            mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
+            mbar_init(task_empty_bar + 8 * s, NSW + 1);  // softmax warps and the stream warp
+            mbar_init(q_ready_bar + 8 * s, NSW);
+            mbar_init(stream_full_bar + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(s_full_bar + 8 * s, 1);
+            mbar_init(s_free_bar + 8 * s, NSW);
+            mbar_init(p_full_bar + 8 * s, NSW);
+            mbar_init(pv_done_bar + 8 * s, 1);
+        }
+        mbar_init(o_free_bar, NSW);
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < TQ * G::kQBytes / 16; i += G::kThreads) {
+        reinterpret_cast<uint4*>(q_ring)[i] = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
+                     "r"(G::kTmemColumns)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base;
+    const uint32_t tmem_s = tmem_base + 128;  // + 32 * buffer + 16 * page
+    const uint32_t tmem_p = tmem_base + 192;  // + 32 * buffer (+ 16 for the remainder) + 8 * page
+    const uint32_t tmem_q = tmem_base + 256;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
+
+    const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
+    const bool balanced = balanced_task_range(p, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+
+    ProducerContext producer{};
+    producer.ring = ring;
+    producer.q_ring = q_ring;
+    producer.pid_smem = pid_smem;
+    producer.task_ring = task_ring;
+    producer.full_bar = full_bar;
+    producer.empty_bar = empty_bar;
+    producer.task_full_bar = task_full_bar;
+    producer.task_empty_bar = task_empty_bar;
+    producer.stream_full_bar = stream_full_bar;
+    producer.abort_flag = abort_flag;
+    producer.task_base = balanced ? task_range[0] : blockIdx.x;
+    producer.task_step = balanced ? 1u : gridDim.x;
+    producer.task_limit = balanced ? task_range[1] : total_tasks;
+    producer.balanced = balanced;
+    producer.allow_carry = false;  // the running state lives in tensor memory and is published per task
+    producer.lane = lane;
+
+    if (warp == NSW + 2) {
+        run_task_warp<G, P>(p, q_map, producer);
+    } else if (warp == NSW + 1) {
+        run_stream_warp<G, P>(p, kv_map, producer);
+    } else if (warp == NSW) {
+        // ------------------------------ MMA issue (one thread) ---------------------------------
+        if (lane == 0) {
+            constexpr uint32_t kFormat = umma_format<T>();
+            // D f32; A, B 16-bit; M = 128. QK: N = 16, both operands K-major. PV: N = D, B (V) MN-major.
+            const uint32_t idesc_qk = (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t idesc_pv =
+                (1u << 4) | (kFormat << 7) | (kFormat << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t ring_addr = smem_addr(ring);
+            uint32_t stage_base = 0;  // stages of earlier tasks
+            uint32_t pv_tasks = 0;    // tasks so far that issued P V products (their epilogues release O)
+            bool ok = true;
+            for (uint32_t taken = 0; ok; ++taken) {
+                const uint32_t tslot = taken % TQ;
+                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                const TaskSlot* ts = task_ring + tslot;
+                if (ts->done) break;
+                const uint32_t num_tiles = ts->num_tiles;
+                if (!mbar_wait(q_ready_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                const uint32_t q_tmem = tmem_q + 64 * tslot;
+                auto issue_qk = [&](uint32_t i) -> bool {
+                    const uint32_t g = stage_base + i;
+                    const uint32_t slot = g % NS, sb = g & 1;
+                    if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p.status)) return false;
+                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p.status)) return false;
+                    tmem_fence_after();
+                    const uint32_t stage_addr = ring_addr + slot * G::kStageBytes;
+#pragma unroll
+                    for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+#pragma unroll
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            // A = the Q tile in tensor memory (read once per task from shared memory, not once per
+                            // page: the 4 KB A operand from shared memory made every N = 16 instruction as long as
+                            // an N = 128 one)
+                            const uint64_t k = umma_smem_desc(
+                                stage_addr + b * G::kCopyBytes + (kk / 4) * G::kBoxBytes + (kk % 4) * 32, 16, 1024);
+                            umma_ts(tmem_s + 32 * sb + 16 * b, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(s_full_bar + 8 * sb);
+                    return true;
+                };
+                if (num_tiles > 0) {
+                    ok = issue_qk(0);
+                    for (uint32_t i = 0; i < num_tiles && ok; ++i) {
+                        if (i + 1 < num_tiles) ok = issue_qk(i + 1);
+                        if (!ok) break;
+                        const uint32_t g = stage_base + i;
+                        const uint32_t slot = g % NS, pb = g & 1;
+                        if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                        if (i == 0 && pv_tasks > 0) {
+                            // this task's first product overwrites O: the previous task's epilogue must have read it
+                            if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                        }
+                        tmem_fence_after();
+                        const uint32_t v_addr = ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes;
+#pragma unroll
+                        for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                            const uint64_t v = umma_smem_desc(v_addr + b * G::kCopyBytes, G::kBoxBytes, 1024);
+                            umma_ts(tmem_o, tmem_p + 32 * pb + 8 * b, v, idesc_pv, (i == 0 && b == 0) ? 0u : 1u);
+                            umma_ts(tmem_o, tmem_p + 32 * pb + 16 + 8 * b, v, idesc_pv, 1u);
+                        }
+                        umma_commit(empty_bar + 8 * slot);     // K and V of the stage are consumed
+                        umma_commit(pv_done_bar + 8 * pb);
+                    }
+                    ++pv_tasks;
+                }
+                stage_base += num_tiles;
+            }
+            // nothing issued here may still be running when tensor memory is freed (bounded, also on the abort path)
+            umma_commit(drain_bar);
+            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                if (mbar_try_wait(drain_bar, 0)) break;
+            }
+        }
+    } else {
+        // ------------------------------ softmax and epilogue warps -----------------------------
+        const uint32_t row = uint32_t(warp) * 32 + lane;          // row of the 128-row tile this thread owns
+        const uint32_t lane_base = (uint32_t(warp) * 32) << 16;   // this warp's quarter of the tensor-memory lanes
+        uint32_t stage_base = 0;
+        for (uint32_t popped = 0;; ++popped) {
+            const uint32_t tslot = popped % TQ;
+            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p.status)) break;
+            const TaskSlot* ts = task_ring + tslot;
+            if (ts->done) break;
+            const uint32_t t_tmpl = ts->tmpl, t_head_begin = ts->head_begin, t_num_heads = ts->num_heads;
+            const uint32_t t_tok_begin = ts->tok_begin, t_num_toks = ts->num_toks;
+            const uint32_t t_kv_begin = ts->kv_begin, t_kv_end = ts->kv_end;
+            const uint32_t t_tile_begin = ts->tile_begin, t_num_tiles = ts->num_tiles;
+            const uint32_t row_tok = row / p.heads_per_task;
+            const uint32_t row_head = row % p.heads_per_task;
+            const bool valid = row_tok < t_num_toks && row_head < t_num_heads;
+            uint32_t lo = 0, hi = 0;
+            if (valid) {
+                uint32_t vb = 0, ve = 0xffffffffu;
+                if (p.visible != nullptr) {
+                    vb = ts->visible[row_tok * 2];
+                    ve = ts->visible[row_tok * 2 + 1];
+                }
+                lo = max(vb, t_kv_begin);
+                hi = min(ve, t_kv_end);
+                if (hi < lo) hi = lo;
+            }
+            // ---- the task's Q tile goes to tensor memory once: this thread's row, un-swizzled, as 16-bit pairs
+            {
+                const uint8_t* q_row = q_ring + tslot * G::kQBytes + row * 128;
+#pragma unroll
+                for (int h = 0; h < D / 64; ++h) {
+                    uint32_t q[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(q_row + h * (G::kQRows * 128) + ((c ^ (row & 7)) << 4));
+                        q[4 * c] = v.x;
+                        q[4 * c + 1] = v.y;
+                        q[4 * c + 2] = v.z;
+                        q[4 * c + 3] = v.w;
+                    }
+                    tmem_st32(tmem_q + 64 * tslot + 32 * h + lane_base, q);
+                }
+                tmem_st_wait();
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_ready_bar + 8 * tslot);
+            }
+            float m_used = -INFINITY;  // raw dot-product domain; the maximum the probabilities are relative to
+            float l_run = 0.0f;
+            bool failed = false;
+            for (uint32_t i = 0; i < t_num_tiles; ++i) {
+                const uint32_t g = stage_base + i;
+                const uint32_t sb = g & 1;
+                if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                tmem_fence_after();
+                uint32_t sraw[32];
+                tmem_ld32(sraw, tmem_s + 32 * sb + lane_base);
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free_bar + 8 * sb);
+                const uint32_t tile_tok = t_tile_begin + i * ST;
+                float s[32];
+                float tile_max = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const uint32_t tok = tile_tok + j;
+                    s[j] = (tok >= lo && tok < hi) ? __uint_as_float(sraw[j]) : -INFINITY;
+                    tile_max = fmaxf(tile_max, s[j]);
+                }
+                // lazy maximum: move it (and rescale l and O) only when the tile exceeds it by more than 2^8
+                const bool grow = tile_max > -INFINITY &&
+                                  (m_used == -INFINITY || (tile_max - m_used) * p.scale_log2e > kRescaleLog2);
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = (grow && m_used != -INFINITY) ? fast_exp2((m_used - tile_max) * p.scale_log2e) : 1.0f;
+                    if (grow) {
+                        l_run *= alpha;
+                        m_used = tile_max;
+                    }
+                    if (i > 0) {
+                        // O holds this task's earlier stages: wait for the previous stage's products, then scale
+                        const uint32_t gp = g - 1;
+                        if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                        tmem_fence_after();
+#pragma unroll
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            uint32_t o[32];
+                            tmem_ld32(o, tmem_o + c0 + lane_base);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                            tmem_st32(tmem_o + c0 + lane_base, o);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                const float shift = m_used == -INFINITY ? 0.0f : -m_used * p.scale_log2e;
+                uint32_t packed[32];  // [0,16) rounded pairs, [16,32) rounding remainders
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float p0 = fast_exp2(fmaf(s[2 * j], p.scale_log2e, shift));
+                    const float p1 = fast_exp2(fmaf(s[2 * j + 1], p.scale_log2e, shift));
+                    l_run += p0 + p1;
+                    packed[j] = pack2<T>(p0, p1);
+                    const float2 r = unpack2<T>(packed[j]);
+                    packed[16 + j] = pack2<T>(p0 - r.x, p1 - r.y);
+                }
+                // the buffer is free once the products of two stages ago have completed
+                if (g >= 2) {
+                    const uint32_t gp = g - 2;
+                    if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                }
+                tmem_fence_after();
+                tmem_st32(tmem_p + 32 * sb + lane_base, packed);
+                tmem_st_wait();
+                if (tile_tok + ST > t_kv_end) {
+                    // V rows of tokens at or past kv_end may never have been loaded: clear them so that a zero
+                    // probability times stale bits cannot produce NaN (generic-proxy writes, then a proxy fence
+                    // before the tensor core reads them)
+                    const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0;
+                    uint8_t* stage = ring + (g % NS) * G::kStageBytes;
+                    for (uint32_t idx = first_bad * (D / 8) + row; idx < uint32_t(ST) * (D / 8); idx += NSW * 32) {
+                        const uint32_t r = idx / (D / 8);
+                        const uint32_t c = idx % (D / 8);
+                        uint8_t* dst = stage + (r / G::kBoxRows) * G::kCopyBytes + G::kPlaneBoxBytes + (c / 8) * G::kBoxBytes +
+                                       (r % G::kBoxRows) * 128 + (c % 8) * 16;
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full_bar + 8 * sb);
+            }
+            if (failed) break;
+            stage_base += t_num_tiles;
+
+            // ---- epilogue: normalise and publish the task's rows
+            const bool write_final = p.direct != 0;
+            const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            const uint32_t head = t_head_begin + row_head;
+            const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
+            if (t_num_tiles > 0) {
+                const uint32_t gl = stage_base - 1;
+                if (!mbar_wait(pv_done_bar + 8 * (gl & 1), (gl >> 1) & 1, abort_flag, p.status)) break;
+                tmem_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(o, tmem_o + c0 + lane_base);
+                    if (valid) {
+                        if (write_final) {
+                            T* dst = reinterpret_cast<T*>(p.out) +
+                                     (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + c0;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                v.x = pack2<T>(__uint_as_float(o[j]) * inv_l, __uint_as_float(o[j + 1]) * inv_l);
+                                v.y = pack2<T>(__uint_as_float(o[j + 2]) * inv_l, __uint_as_float(o[j + 3]) * inv_l);
+                                v.z = pack2<T>(__uint_as_float(o[j + 4]) * inv_l, __uint_as_float(o[j + 5]) * inv_l);
+                                v.w = pack2<T>(__uint_as_float(o[j + 6]) * inv_l, __uint_as_float(o[j + 7]) * inv_l);
+                                *reinterpret_cast<uint4*>(dst + j) = v;
+                            }
+                        } else {
+                            float* dst = p.partial_out + index * D + c0;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                *reinterpret_cast<float4*>(dst + j) =
+                                    make_float4(__uint_as_float(o[j]) * inv_l, __uint_as_float(o[j + 1]) * inv_l,
+                                                __uint_as_float(o[j + 2]) * inv_l, __uint_as_float(o[j + 3]) * inv_l);
+                            }
+                        }
+                    }
+                }
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_free_bar);
+            } else if (valid) {
+                if (write_final) {
+                    T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D;
+                    for (int j = 0; j < D; j += 8) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
+                } else {
+                    float* dst = p.partial_out + index * D;
+                    for (int j = 0; j < D; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+            if (valid && !write_final) {
+                p.partial_sum[index] = l_run;
+                // the maximum is a raw dot product; publish the natural-log-domain logit (dot * scale)
+                p.partial_max[index] = l_run > 0.0f ? m_used * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+        }
+    }
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(G::kTmemColumns) : "memory");
+    }
+}
+
+}  // namespace kh

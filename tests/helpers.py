@@ -191,10 +191,10 @@ class DeviceCase:
             assert not counters.any(), "arrival counters must be left zero"
         self.attention.fused = False
         if len(outputs) == 2:
-            # same partials, same merge formula; a one-partial range is written straight from registers in the
-            # one-launch form, which may differ from (sum * v) / sum by one rounding of the output type
-            assert np.allclose(outputs[0], outputs[1], rtol=2.0 ** -7, atol=1e-6), \
-                "one-launch and two-launch results differ"
+            # Same inputs, two kernels (the one-launch form always runs the warp-level instance; a one-partial
+            # range is written straight from registers there): they agree to the rounding of the output type,
+            # checked with the contract's bound
+            assert_within_contract(outputs[0], outputs[1], "one-launch against two-launch")
         return outputs[0]
 
     def read_output(self) -> np.ndarray:
