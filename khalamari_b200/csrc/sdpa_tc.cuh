@@ -24,7 +24,7 @@ namespace kh {
 template <int D, int P>
 struct TcGeometry {
     static_assert(D == 128 && P == 16, "the tensor-memory instance is built for head_dim 128 and 16-token pages");
-    static constexpr int kStageTokens = 32;
+    static constexpr int kStageTokens = 64;  // four pages: Q K^T runs with N = 32 (row group g of every page)
     static constexpr int kBoxRows = 16;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;
     static constexpr int kColumnHalves = D / 64;
@@ -44,8 +44,8 @@ struct TcGeometry {
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
     static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
-    static constexpr uint32_t kTmemColumns = 512;  // O 128 | S 2 x 32 | P 2 x (16 rounded + 16 remainder) | Q 2 x 64
-    static_assert(kStages >= 4, "shared memory ring too small");
+    static constexpr uint32_t kTmemColumns = 512;  // O 128 | S 2 x 64 | P 2 x (32 rounded + 32 remainder) | Q 2 x 64
+    static_assert(kStages >= 3, "shared memory ring too small");
 };
 
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
@@ -185,9 +185,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     tmem_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base;
-    const uint32_t tmem_s = tmem_base + 128;  // + 32 * buffer + 16 * page
-    const uint32_t tmem_p = tmem_base + 192;  // + 32 * buffer (+ 16 for the remainder) + 8 * page
-    const uint32_t tmem_q = tmem_base + 256;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
+    // Column c of a stage's scores is KV token tile_tok + 16 * page + 8 * g + r with g = c / 32, page = (c % 32) / 8,
+    // r = c % 8: one Q K^T instruction covers row group g (8 token rows) of all four pages, whose 8-row groups lie
+    // one page copy apart in shared memory (a uniform stride, which is what the operand descriptor can express).
+    const uint32_t tmem_s = tmem_base + 128;  // + 64 * buffer + 32 * g
+    const uint32_t tmem_p = tmem_base + 256;  // + 64 * buffer (+ 32 for the remainder) + 8 * (16-token chunk)
+    const uint32_t tmem_q = tmem_base + 384;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
 
     const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
     const bool balanced = balanced_task_range(p, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
@@ -218,8 +221,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // ------------------------------ MMA issue (one thread) ---------------------------------
         if (lane == 0) {
             constexpr uint32_t kFormat = umma_format<T>();
-            // D f32; A, B 16-bit; M = 128. QK: N = 16, both operands K-major. PV: N = D, B (V) MN-major.
-            const uint32_t idesc_qk = (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            // D f32; A, B 16-bit; M = 128. QK: N = 32, both operands K-major. PV: N = D, B (V) MN-major.
+            const uint32_t idesc_qk = (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t idesc_pv =
                 (1u << 4) | (kFormat << 7) | (kFormat << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t ring_addr = smem_addr(ring);
@@ -242,15 +245,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     tmem_fence_after();
                     const uint32_t stage_addr = ring_addr + slot * G::kStageBytes;
 #pragma unroll
-                    for (int b = 0; b < G::kBoxesPerPlane; ++b) {
+                    for (int gr = 0; gr < 2; ++gr) {
 #pragma unroll
                         for (int kk = 0; kk < D / 16; ++kk) {
                             // A = the Q tile in tensor memory (read once per task from shared memory, not once per
-                            // page: the 4 KB A operand from shared memory made every N = 16 instruction as long as
-                            // an N = 128 one)
+                            // instruction). B = K rows 8 * gr .. 8 * gr + 7 of the stage's four pages.
                             const uint64_t k = umma_smem_desc(
-                                stage_addr + b * G::kCopyBytes + (kk / 4) * G::kBoxBytes + (kk % 4) * 32, 16, 1024);
-                            umma_ts(tmem_s + 32 * sb + 16 * b, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
+                                stage_addr + (kk / 4) * G::kBoxBytes + gr * 1024 + (kk % 4) * 32, 16, G::kCopyBytes);
+                            umma_ts(tmem_s + 64 * sb + 32 * gr, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
                         }
                     }
                     umma_commit(s_full_bar + 8 * sb);
@@ -271,10 +273,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         tmem_fence_after();
                         const uint32_t v_addr = ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes;
 #pragma unroll
-                        for (int b = 0; b < G::kBoxesPerPlane; ++b) {
-                            const uint64_t v = umma_smem_desc(v_addr + b * G::kCopyBytes, G::kBoxBytes, 1024);
-                            umma_ts(tmem_o, tmem_p + 32 * pb + 8 * b, v, idesc_pv, (i == 0 && b == 0) ? 0u : 1u);
-                            umma_ts(tmem_o, tmem_p + 32 * pb + 16 + 8 * b, v, idesc_pv, 1u);
+                        for (int j = 0; j < ST / 16; ++j) {
+                            // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
+                            const uint64_t v = umma_smem_desc(v_addr + (2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024,
+                                                              G::kBoxBytes, G::kCopyBytes);
+                            umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
+                            umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
                         }
                         umma_commit(empty_bar + 8 * slot);     // K and V of the stage are consumed
                         umma_commit(pv_done_bar + 8 * pb);
@@ -346,19 +350,38 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t sb = g & 1;
                 if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
                 tmem_fence_after();
-                uint32_t sraw[32];
-                tmem_ld32(sraw, tmem_s + 32 * sb + lane_base);
+                uint32_t sraw[ST];
+                {
+                    uint32_t lo32[32], hi32[32];
+                    tmem_ld32(lo32, tmem_s + 64 * sb + lane_base);
+                    tmem_ld32(hi32, tmem_s + 64 * sb + 32 + lane_base);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        sraw[j] = lo32[j];
+                        sraw[32 + j] = hi32[j];
+                    }
+                }
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_free_bar + 8 * sb);
                 const uint32_t tile_tok = t_tile_begin + i * ST;
-                float s[32];
+                float s[ST];
                 float tile_max = -INFINITY;
+                // most stages of a long context lie wholly inside every row's visible range: no masking then
+                const bool cut = tile_tok < lo || tile_tok + ST > hi;
+                if (__any_sync(0xffffffffu, cut)) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const uint32_t tok = tile_tok + j;
-                    s[j] = (tok >= lo && tok < hi) ? __uint_as_float(sraw[j]) : -INFINITY;
-                    tile_max = fmaxf(tile_max, s[j]);
+                    for (int j = 0; j < ST; ++j) {
+                        const uint32_t tok = tile_tok + ((j % 32) / 8) * 16 + (j / 32) * 8 + (j % 8);
+                        s[j] = (tok >= lo && tok < hi) ? __uint_as_float(sraw[j]) : -INFINITY;
+                        tile_max = fmaxf(tile_max, s[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < ST; ++j) {
+                        s[j] = __uint_as_float(sraw[j]);
+                        tile_max = fmaxf(tile_max, s[j]);
+                    }
                 }
                 // lazy maximum: move it (and rescale l and O) only when the tile exceeds it by more than 2^8
                 const bool grow = tile_max > -INFINITY &&
@@ -386,15 +409,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     }
                 }
                 const float shift = m_used == -INFINITY ? 0.0f : -m_used * p.scale_log2e;
-                uint32_t packed[32];  // [0,16) rounded pairs, [16,32) rounding remainders
+                uint32_t packed_hi[32], packed_lo[32];  // rounded pairs and their rounding remainders
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < ST / 2; ++j) {
                     const float p0 = fast_exp2(fmaf(s[2 * j], p.scale_log2e, shift));
                     const float p1 = fast_exp2(fmaf(s[2 * j + 1], p.scale_log2e, shift));
                     l_run += p0 + p1;
-                    packed[j] = pack2<T>(p0, p1);
-                    const float2 r = unpack2<T>(packed[j]);
-                    packed[16 + j] = pack2<T>(p0 - r.x, p1 - r.y);
+                    packed_hi[j] = pack2<T>(p0, p1);
+                    const float2 r = unpack2<T>(packed_hi[j]);
+                    packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
                 }
                 // the buffer is free once the products of two stages ago have completed
                 if (g >= 2) {
@@ -402,7 +425,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
                 }
                 tmem_fence_after();
-                tmem_st32(tmem_p + 32 * sb + lane_base, packed);
+                tmem_st32(tmem_p + 64 * sb + lane_base, packed_hi);
+                tmem_st32(tmem_p + 64 * sb + 32 + lane_base, packed_lo);
                 tmem_st_wait();
                 if (tile_tok + ST > t_kv_end) {
                     // V rows of tokens at or past kv_end may never have been loaded: clear them so that a zero
