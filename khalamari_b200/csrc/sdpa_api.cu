@@ -43,6 +43,7 @@ struct ReduceParams {
     uint32_t fixed_partials;
     uint64_t stat_stride;      // floats between consecutive partials of a row; 0: dense [partial][Hq][maxq]
     uint64_t out_stride;       // same for the partial outputs; 0: dense [partial][Hq][maxq][D]
+    uint32_t heads_per_block;  // > 1 (one-token ranges only): a block serves this many consecutive heads
 };
 
 template <typename T>
@@ -72,9 +73,35 @@ template <typename T>
 __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const ReduceParams p) {
     __shared__ float4 shared_acc[kReduceMaxThreads];
     __shared__ float2 shared_stat[kReduceMaxThreads];
-    const uint32_t head = blockIdx.x;
     const uint32_t range = blockIdx.y;
     if (range >= p.num_active_ranges) return;
+    if (p.heads_per_block > 1) {
+        // decode shape: one token per range, few partials per row. A thread owns four output columns of one
+        // head; no shared memory, no second wave of blocks.
+        const uint32_t D = p.head_dim;
+        const uint32_t slots = D / 4;
+        const uint32_t head = blockIdx.x * p.heads_per_block + threadIdx.x / slots;
+        const uint32_t d = (threadIdx.x % slots) * 4;
+        if (head >= p.num_q_heads || threadIdx.x / slots >= p.heads_per_block) return;
+        const uint32_t tok = p.q_ranges != nullptr ? p.q_ranges[range * 2] : range;
+        if (tok >= p.num_active_tokens) return;
+        const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
+        const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
+        const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads);
+        const uint64_t out_stride = p.out_stride != 0 ? p.out_stride : stride * D;
+        const uint64_t first_index = uint64_t(first) * p.num_q_heads + head;
+        float merged_sum, merged_max;
+        const float4 acc = merge_partials_vec(p.partial_sum, p.partial_max, p.partial_out, first_index, stride, out_stride,
+                                              last - first, D, d, &merged_sum, &merged_max);
+        const uint64_t out_row = uint64_t(tok) * p.num_q_heads + head;
+        store4<T>(reinterpret_cast<T*>(p.out) + out_row * D + d, acc);
+        if (p.out_sum != nullptr && d == 0) {
+            p.out_sum[out_row] = merged_sum;
+            p.out_max[out_row] = merged_max;
+        }
+        return;
+    }
+    const uint32_t head = blockIdx.x;
     uint32_t tok_begin = range, tok_end = range + 1;
     if (p.q_ranges != nullptr) {
         tok_begin = p.q_ranges[range * 2];
@@ -369,10 +396,17 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
 
 template <typename T>
 static void launch_reduce_typed(const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {
+    ReduceParams params = p;
     dim3 grid(p.num_q_heads, num_ranges, 1);
     // a fixed, long partial list per row (the cross-slice and cross-GPU merges) gets the widest block
-    const uint32_t threads = (p.cu == nullptr && p.fixed_partials > 32) ? kReduceMaxThreads : 128;
-    sdpa_reduce_kernel<T><<<grid, threads, 0, stream>>>(p);
+    uint32_t threads = (p.cu == nullptr && p.fixed_partials > 32) ? kReduceMaxThreads : 128;
+    params.heads_per_block = 1;
+    const uint32_t slots = p.head_dim / 4;
+    if (p.max_q_tokens == 1 && threads == 128 && slots <= 64 && 128 % slots == 0) {
+        params.heads_per_block = 128 / slots;
+        grid.x = (p.num_q_heads + params.heads_per_block - 1) / params.heads_per_block;
+    }
+    sdpa_reduce_kernel<T><<<grid, threads, 0, stream>>>(params);
 }
 
 static void launch_reduce(kh_dtype dtype, const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {

@@ -250,21 +250,30 @@ __device__ __forceinline__ void merge_partials_accumulate(MergeState& state, con
     float run_max = state.max, run_sum = state.sum;
     float4 acc = state.acc;
     for (uint32_t base = 0; base < count; base += 8) {
+        // statistics of eight partials first, then the output rows of those that carry weight (a task that handed
+        // its running state on publishes an empty partial, so most rows of a long list are never read)
         float mx[8], sm[8];
-        float4 v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const bool valid = base + j < count;
             const uint64_t index = first_index + uint64_t(base + j) * index_stride;
-            const uint64_t out_index = first_index * head_dim + uint64_t(base + j) * out_stride + d;
             mx[j] = valid ? __ldcg(partial_max + index) : -INFINITY;
             sm[j] = valid ? __ldcg(partial_sum + index) : 0.0f;
-            v[j] = valid ? __ldcg(reinterpret_cast<const float4*>(partial_out + out_index))
-                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
         float new_max = run_max;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) new_max = fmaxf(new_max, mx[j]);
+        for (int j = 0; j < 8; ++j) {
+            if (sm[j] != 0.0f && isfinite(mx[j])) new_max = fmaxf(new_max, mx[j]);
+        }
+        float weight[8];
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            weight[j] = (sm[j] != 0.0f && isfinite(mx[j])) ? expf(mx[j] - new_max) * sm[j] : 0.0f;
+            const uint64_t out_index = first_index * head_dim + uint64_t(base + j) * out_stride + d;
+            v[j] = weight[j] != 0.0f ? __ldcg(reinterpret_cast<const float4*>(partial_out + out_index))
+                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
         const float keep = run_max == -INFINITY ? 0.0f : expf(run_max - new_max);
         acc.x *= keep;
         acc.y *= keep;
@@ -273,14 +282,11 @@ __device__ __forceinline__ void merge_partials_accumulate(MergeState& state, con
         run_sum *= keep;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float weight = (sm[j] != 0.0f && isfinite(mx[j])) ? expf(mx[j] - new_max) * sm[j] : 0.0f;
-            if (weight != 0.0f) {  // an empty partial's output row is never used, whatever its bits
-                acc.x += weight * v[j].x;
-                acc.y += weight * v[j].y;
-                acc.z += weight * v[j].z;
-                acc.w += weight * v[j].w;
-            }
-            run_sum += weight;
+            acc.x += weight[j] * v[j].x;
+            acc.y += weight[j] * v[j].y;
+            acc.z += weight[j] * v[j].z;
+            acc.w += weight[j] * v[j].w;
+            run_sum += weight[j];
         }
         run_max = new_max;
     }
