@@ -13,7 +13,8 @@
 // The running maximum is updated lazily: O (in tensor memory) is rescaled only when a row's maximum grows by more
 // than 2^8, so the common stage costs one tensor-memory load and two stores per thread.
 //
-// Warps: 0-3 softmax and epilogue, 4 MMA issue (one thread), 5 stream warp (K/V copies), 6 task warp.
+// Warps: 0-7 softmax and epilogue (two groups of four), 8 Q K^T issue (one thread), 9 stream warp (K/V copies),
+// 10 task warp, 11 P V issue (one thread).
 // Every wait is bounded (mbar_wait); tensor memory is allocated once and freed on every exit path.
 #pragma once
 
@@ -35,11 +36,11 @@ struct TcGeometry {
     static constexpr int kQRows = 128;
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;
-    static constexpr int kSoftmaxWarps = 4;
-    static constexpr int kThreads = (kSoftmaxWarps + 3) * 32;
+    static constexpr int kSoftmaxWarps = 8;  // two groups of four; group w takes the stages of parity w
+    static constexpr int kThreads = (kSoftmaxWarps + 4) * 32;  // + Q K^T issue, stream, task, P V issue
     static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
-    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kPidBytes + kTaskBytes + 1024;
+    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kPidBytes + kTaskBytes + 3072;  // barriers, row maxima and sums
     static constexpr int kSmemLimit = 227 * 1024 - 1024;
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
     static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
@@ -128,10 +129,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     uint32_t* pid_smem = reinterpret_cast<uint32_t*>(q_ring + TQ * G::kQBytes);
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
-    constexpr int kNumBars = 2 * NS + 3 * TQ + 12;
+    constexpr int kNumBars = 2 * NS + 3 * TQ + 17;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
     uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 1;
     uint32_t* tmem_slot = task_range + 2;
+    volatile float* row_max = reinterpret_cast<volatile float*>(tmem_slot + 1);  // [128] maximum per row of the tile
+    volatile float* row_sum = row_max + 128;                                     // [2][128] each group's row sum
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -145,8 +148,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t p_full_bar = smem_addr(bars + 2 * NS + 3 * TQ + 4);   // [2] probabilities of a stage are stored
     const uint32_t pv_done_bar = smem_addr(bars + 2 * NS + 3 * TQ + 6);  // [2] the stage's P V products completed
     const uint32_t o_free_bar = smem_addr(bars + 2 * NS + 3 * TQ + 8);   // the epilogue has read O
-    const uint32_t drain_bar = smem_addr(bars + 2 * NS + 3 * TQ + 9);    // every issued tcgen05 operation completed
-    const uint32_t q_ready_bar = smem_addr(bars + 2 * NS + 3 * TQ + 10); // [2] a task's Q tile is in tensor memory
+    const uint32_t drain_bar = smem_addr(bars + 2 * NS + 3 * TQ + 15);   // [2] every tcgen05 operation of an issuing thread completed
+    const uint32_t q_ready_bar = smem_addr(bars + 2 * NS + 3 * TQ + 9);  // [2] a task's Q tile is in tensor memory
+    const uint32_t decided_bar = smem_addr(bars + 2 * NS + 3 * TQ + 11); // [2] a group fixed the row maxima of its stage
+    const uint32_t epilogue_bar = smem_addr(bars + 2 * NS + 3 * TQ + 13); // [2] task-end hand-offs between the groups
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -155,18 +160,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         }
         for (int s = 0; s < TQ; ++s) {
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
-            mbar_init(task_empty_bar + 8 * s, NSW + 1);  // softmax warps and the stream warp
+            mbar_init(task_empty_bar + 8 * s, NSW + 3);  // softmax warps, the stream warp, the two issuing threads
             mbar_init(q_ready_bar + 8 * s, NSW);
             mbar_init(stream_full_bar + 8 * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(s_full_bar + 8 * s, 1);
-            mbar_init(s_free_bar + 8 * s, NSW);
-            mbar_init(p_full_bar + 8 * s, NSW);
+            mbar_init(s_free_bar + 8 * s, 4);   // the four warps of the group that owns the buffer
+            mbar_init(p_full_bar + 8 * s, 4);
             mbar_init(pv_done_bar + 8 * s, 1);
+            mbar_init(decided_bar + 8 * s, 4);
+            mbar_init(epilogue_bar + 8 * s, NSW);
         }
         mbar_init(o_free_bar, NSW);
         mbar_init(drain_bar, 1);
+        mbar_init(drain_bar + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -218,16 +226,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     } else if (warp == NSW + 1) {
         run_stream_warp<G, P>(p, kv_map, producer);
     } else if (warp == NSW) {
-        // ------------------------------ MMA issue (one thread) ---------------------------------
+        // ------------------------------ Q K^T issue (one thread) -------------------------------
+        // tcgen05.mma is issued by single threads. Two of them share the work - this one the score products, the
+        // next warp's the P V products - because one thread's issue rate (descriptor arithmetic, waits, about a
+        // hundred cycles per instruction) was what bounded the kernel. Everything the two need from each other
+        // goes through the softmax warps' barriers, so no ordering between the two instruction streams is assumed.
         if (lane == 0) {
             constexpr uint32_t kFormat = umma_format<T>();
-            // D f32; A, B 16-bit; M = 128. QK: N = 32, both operands K-major. PV: N = D, B (V) MN-major.
+            // D f32; A, B 16-bit; M = 128, N = 32, both operands K-major
             const uint32_t idesc_qk = (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
-            const uint32_t idesc_pv =
-                (1u << 4) | (kFormat << 7) | (kFormat << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((128u >> 4) << 24);
+            // descriptor of a K operand at byte address 0 (stride between 8-row groups: one page copy); shared
+            // memory addresses are below 2^18, so the 14-bit address field is a plain sum
+            const uint64_t k_desc0 = umma_smem_desc(0, 16, G::kCopyBytes);
             const uint32_t ring_addr = smem_addr(ring);
             uint32_t stage_base = 0;  // stages of earlier tasks
-            uint32_t pv_tasks = 0;    // tasks so far that issued P V products (their epilogues release O)
             bool ok = true;
             for (uint32_t taken = 0; ok; ++taken) {
                 const uint32_t tslot = taken % TQ;
@@ -237,55 +249,27 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t num_tiles = ts->num_tiles;
                 if (!mbar_wait(q_ready_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
                 const uint32_t q_tmem = tmem_q + 64 * tslot;
-                auto issue_qk = [&](uint32_t i) -> bool {
+                for (uint32_t i = 0; i < num_tiles; ++i) {
                     const uint32_t g = stage_base + i;
                     const uint32_t slot = g % NS, sb = g & 1;
-                    if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p.status)) return false;
-                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p.status)) return false;
+                    if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p.status)) { ok = false; break; }
+                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
                     tmem_fence_after();
-                    const uint32_t stage_addr = ring_addr + slot * G::kStageBytes;
+                    const uint64_t k_desc = k_desc0 + uint64_t((ring_addr + slot * G::kStageBytes) >> 4);
 #pragma unroll
                     for (int gr = 0; gr < 2; ++gr) {
 #pragma unroll
                         for (int kk = 0; kk < D / 16; ++kk) {
                             // A = the Q tile in tensor memory (read once per task from shared memory, not once per
                             // instruction). B = K rows 8 * gr .. 8 * gr + 7 of the stage's four pages.
-                            const uint64_t k = umma_smem_desc(
-                                stage_addr + (kk / 4) * G::kBoxBytes + gr * 1024 + (kk % 4) * 32, 16, G::kCopyBytes);
+                            const uint64_t k = k_desc + uint64_t(((kk / 4) * G::kBoxBytes + gr * 1024 + (kk % 4) * 32) >> 4);
                             umma_ts(tmem_s + 64 * sb + 32 * gr, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
                         }
                     }
                     umma_commit(s_full_bar + 8 * sb);
-                    return true;
-                };
-                if (num_tiles > 0) {
-                    ok = issue_qk(0);
-                    for (uint32_t i = 0; i < num_tiles && ok; ++i) {
-                        if (i + 1 < num_tiles) ok = issue_qk(i + 1);
-                        if (!ok) break;
-                        const uint32_t g = stage_base + i;
-                        const uint32_t slot = g % NS, pb = g & 1;
-                        if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
-                        if (i == 0 && pv_tasks > 0) {
-                            // this task's first product overwrites O: the previous task's epilogue must have read it
-                            if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p.status)) { ok = false; break; }
-                        }
-                        tmem_fence_after();
-                        const uint32_t v_addr = ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes;
-#pragma unroll
-                        for (int j = 0; j < ST / 16; ++j) {
-                            // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
-                            const uint64_t v = umma_smem_desc(v_addr + (2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024,
-                                                              G::kBoxBytes, G::kCopyBytes);
-                            umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
-                            umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
-                        }
-                        umma_commit(empty_bar + 8 * slot);     // K and V of the stage are consumed
-                        umma_commit(pv_done_bar + 8 * pb);
-                    }
-                    ++pv_tasks;
                 }
                 stage_base += num_tiles;
+                if (ok) mbar_arrive(task_empty_bar + 8 * tslot);  // done with the task's descriptor
             }
             // nothing issued here may still be running when tensor memory is freed (bounded, also on the abort path)
             umma_commit(drain_bar);
@@ -293,10 +277,67 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 if (mbar_try_wait(drain_bar, 0)) break;
             }
         }
+    } else if (warp == NSW + 3) {
+        // ------------------------------ P V issue (one thread) ---------------------------------
+        if (lane == 0) {
+            constexpr uint32_t kFormat = umma_format<T>();
+            // D f32; A (P, tensor memory) and B 16-bit; M = 128, N = D; B (V) MN-major
+            const uint32_t idesc_pv =
+                (1u << 4) | (kFormat << 7) | (kFormat << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((128u >> 4) << 24);
+            const uint64_t v_desc0 = umma_smem_desc(0, G::kBoxBytes, G::kCopyBytes);
+            const uint32_t ring_addr = smem_addr(ring);
+            uint32_t stage_base = 0;
+            uint32_t pv_tasks = 0;  // tasks so far that issued P V products (their epilogues release O)
+            bool ok = true;
+            for (uint32_t taken = 0; ok; ++taken) {
+                const uint32_t tslot = taken % TQ;
+                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                const TaskSlot* ts = task_ring + tslot;
+                if (ts->done) break;
+                const uint32_t num_tiles = ts->num_tiles;
+                for (uint32_t i = 0; i < num_tiles; ++i) {
+                    const uint32_t g = stage_base + i;
+                    const uint32_t slot = g % NS, pb = g & 1;
+                    if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    if (i == 0 && pv_tasks > 0) {
+                        // this task's first product overwrites O: the previous task's epilogue must have read it
+                        if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    }
+                    tmem_fence_after();
+                    const uint64_t v_desc = v_desc0 + uint64_t((ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes) >> 4);
+#pragma unroll
+                    for (int j = 0; j < ST / 16; ++j) {
+                        // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
+                        const uint64_t v = v_desc + uint64_t(((2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024) >> 4);
+                        umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
+                        if (!(p.debug & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
+                    }
+                    umma_commit(empty_bar + 8 * slot);  // K and V of the stage are consumed (its Q K^T completed
+                                                        // before the probabilities could be computed)
+                    umma_commit(pv_done_bar + 8 * pb);
+                }
+                if (num_tiles > 0) ++pv_tasks;
+                stage_base += num_tiles;
+                if (ok) mbar_arrive(task_empty_bar + 8 * tslot);  // done with the task's descriptor
+            }
+            umma_commit(drain_bar + 8);
+            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                if (mbar_try_wait(drain_bar + 8, 0)) break;
+            }
+        }
     } else {
         // ------------------------------ softmax and epilogue warps -----------------------------
-        const uint32_t row = uint32_t(warp) * 32 + lane;          // row of the 128-row tile this thread owns
-        const uint32_t lane_base = (uint32_t(warp) * 32) << 16;   // this warp's quarter of the tensor-memory lanes
+        // Two groups of four warps; both cover the tile's 128 rows (a warp reaches the tensor-memory lanes of
+        // quadrant warp % 4) and take alternate stages: group w handles the stages whose running number has
+        // parity w, with score buffer w and probability buffer w. Per row, the maximum the probabilities are
+        // relative to lives in shared memory; the decision about it (cheap: tile maximum, compare, the rare
+        // rescale of O) is made stage after stage in order - a group waits for the other group's decision on
+        // the previous stage - while the expensive part (exponentials, rounding, stores) of consecutive stages
+        // overlaps. Each group keeps its own row sum, relative to the maximum it last saw.
+        const uint32_t wg = uint32_t(warp) / 4;
+        const uint32_t quad = uint32_t(warp) % 4;
+        const uint32_t row = quad * 32 + lane;           // row of the 128-row tile this thread owns
+        const uint32_t lane_base = (quad * 32) << 16;    // this warp's quarter of the tensor-memory lanes
         uint32_t stage_base = 0;
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
@@ -321,33 +362,33 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 hi = min(ve, t_kv_end);
                 if (hi < lo) hi = lo;
             }
-            // ---- the task's Q tile goes to tensor memory once: this thread's row, un-swizzled, as 16-bit pairs
+            // ---- the task's Q tile goes to tensor memory once: this thread's row, un-swizzled, as 16-bit pairs;
+            // each group copies one 64-column half
             {
                 const uint8_t* q_row = q_ring + tslot * G::kQBytes + row * 128;
+                const uint32_t h = wg;
+                uint32_t q[32];
 #pragma unroll
-                for (int h = 0; h < D / 64; ++h) {
-                    uint32_t q[32];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(q_row + h * (G::kQRows * 128) + ((c ^ (row & 7)) << 4));
-                        q[4 * c] = v.x;
-                        q[4 * c + 1] = v.y;
-                        q[4 * c + 2] = v.z;
-                        q[4 * c + 3] = v.w;
-                    }
-                    tmem_st32(tmem_q + 64 * tslot + 32 * h + lane_base, q);
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + h * (G::kQRows * 128) + ((c ^ (row & 7)) << 4));
+                    q[4 * c] = v.x;
+                    q[4 * c + 1] = v.y;
+                    q[4 * c + 2] = v.z;
+                    q[4 * c + 3] = v.w;
                 }
+                tmem_st32(tmem_q + 64 * tslot + 32 * h + lane_base, q);
                 tmem_st_wait();
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(q_ready_bar + 8 * tslot);
             }
-            float m_used = -INFINITY;  // raw dot-product domain; the maximum the probabilities are relative to
+            float m_ref = -INFINITY;  // raw dot-product domain: the maximum this group's l_run is relative to
             float l_run = 0.0f;
             bool failed = false;
             for (uint32_t i = 0; i < t_num_tiles; ++i) {
                 const uint32_t g = stage_base + i;
-                const uint32_t sb = g & 1;
+                if ((g & 1) != wg) continue;
+                const uint32_t sb = wg;
                 if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
                 tmem_fence_after();
                 uint32_t sraw[ST];
@@ -383,14 +424,26 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         tile_max = fmaxf(tile_max, s[j]);
                     }
                 }
+                // ---- the decision about the row maximum, in stage order
+                float m_prev = -INFINITY;
+                if (i > 0) {
+                    const uint32_t gp = g - 1;  // handled by the other group
+                    if (!mbar_wait(decided_bar + 8 * (wg ^ 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                    m_prev = row_max[row];
+                }
+                if (m_ref != m_prev) {
+                    // the other group moved the maximum since this group last added to its sum
+                    if (m_ref != -INFINITY) l_run *= fast_exp2((m_ref - m_prev) * p.scale_log2e);
+                    m_ref = m_prev;
+                }
                 // lazy maximum: move it (and rescale l and O) only when the tile exceeds it by more than 2^8
                 const bool grow = tile_max > -INFINITY &&
-                                  (m_used == -INFINITY || (tile_max - m_used) * p.scale_log2e > kRescaleLog2);
+                                  (m_prev == -INFINITY || (tile_max - m_prev) * p.scale_log2e > kRescaleLog2);
                 if (__any_sync(0xffffffffu, grow)) {
-                    const float alpha = (grow && m_used != -INFINITY) ? fast_exp2((m_used - tile_max) * p.scale_log2e) : 1.0f;
+                    const float alpha = (grow && m_prev != -INFINITY) ? fast_exp2((m_prev - tile_max) * p.scale_log2e) : 1.0f;
                     if (grow) {
                         l_run *= alpha;
-                        m_used = tile_max;
+                        m_ref = tile_max;
                     }
                     if (i > 0) {
                         // O holds this task's earlier stages: wait for the previous stage's products, then scale
@@ -406,8 +459,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                             tmem_st32(tmem_o + c0 + lane_base, o);
                         }
                         tmem_st_wait();
+                        tmem_fence_before();
                     }
                 }
+                row_max[row] = m_ref;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(decided_bar + 8 * wg);
+                const float m_used = m_ref;
                 const float shift = m_used == -INFINITY ? 0.0f : -m_used * p.scale_log2e;
                 uint32_t packed_hi[32], packed_lo[32];  // rounded pairs and their rounding remainders
 #pragma unroll
@@ -419,7 +477,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     const float2 r = unpack2<T>(packed_hi[j]);
                     packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
                 }
-                // the buffer is free once the products of two stages ago have completed
+                // the buffer is free once the products of this group's previous stage have completed
                 if (g >= 2) {
                     const uint32_t gp = g - 2;
                     if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
@@ -434,7 +492,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     // before the tensor core reads them)
                     const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0;
                     uint8_t* stage = ring + (g % NS) * G::kStageBytes;
-                    for (uint32_t idx = first_bad * (D / 8) + row; idx < uint32_t(ST) * (D / 8); idx += NSW * 32) {
+                    for (uint32_t idx = first_bad * (D / 8) + row; idx < uint32_t(ST) * (D / 8); idx += 128) {
                         const uint32_t r = idx / (D / 8);
                         const uint32_t c = idx % (D / 8);
                         uint8_t* dst = stage + (r / G::kBoxRows) * G::kCopyBytes + G::kPlaneBoxBytes + (c / 8) * G::kBoxBytes +
@@ -450,9 +508,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             if (failed) break;
             stage_base += t_num_tiles;
 
-            // ---- epilogue: normalise and publish the task's rows
+            // ---- epilogue: both groups bring their row sums to the final maximum and add them, then each
+            // publishes 64 of the row's columns
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epilogue_bar);      // every decision of the task has been made
+            if (!mbar_wait(epilogue_bar, popped & 1, abort_flag, p.status)) break;
+            const float m_fin = t_num_tiles > 0 ? row_max[row] : -INFINITY;
+            if (m_ref != m_fin && m_ref != -INFINITY) l_run *= fast_exp2((m_ref - m_fin) * p.scale_log2e);
+            row_sum[wg * 128 + row] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epilogue_bar + 8);  // every group's sum is written
+            if (!mbar_wait(epilogue_bar + 8, popped & 1, abort_flag, p.status)) break;
+            const float l_tot = row_sum[row] + row_sum[128 + row];
             const bool write_final = p.direct != 0;
-            const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            const float inv_l = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
             const uint32_t head = t_head_begin + row_head;
             const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
             if (t_num_tiles > 0) {
@@ -460,13 +529,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 if (!mbar_wait(pv_done_bar + 8 * (gl & 1), (gl >> 1) & 1, abort_flag, p.status)) break;
                 tmem_fence_after();
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = 0; c0 < D / 2; c0 += 32) {
+                    const int col = int(wg) * (D / 2) + c0;
                     uint32_t o[32];
-                    tmem_ld32(o, tmem_o + c0 + lane_base);
+                    tmem_ld32(o, tmem_o + col + lane_base);
                     if (valid) {
                         if (write_final) {
                             T* dst = reinterpret_cast<T*>(p.out) +
-                                     (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + c0;
+                                     (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + col;
 #pragma unroll
                             for (int j = 0; j < 32; j += 8) {
                                 uint4 v;
@@ -477,7 +547,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                                 *reinterpret_cast<uint4*>(dst + j) = v;
                             }
                         } else {
-                            float* dst = p.partial_out + index * D + c0;
+                            float* dst = p.partial_out + index * D + col;
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 *reinterpret_cast<float4*>(dst + j) =
@@ -491,18 +561,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(o_free_bar);
             } else if (valid) {
+                const int col = int(wg) * (D / 2);
                 if (write_final) {
-                    T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D;
-                    for (int j = 0; j < D; j += 8) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
+                    T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + col;
+                    for (int j = 0; j < D / 2; j += 8) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
                 } else {
-                    float* dst = p.partial_out + index * D;
-                    for (int j = 0; j < D; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    float* dst = p.partial_out + index * D + col;
+                    for (int j = 0; j < D / 2; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
             }
-            if (valid && !write_final) {
-                p.partial_sum[index] = l_run;
+            if (valid && !write_final && wg == 0) {
+                p.partial_sum[index] = l_tot;
                 // the maximum is a raw dot product; publish the natural-log-domain logit (dot * scale)
-                p.partial_max[index] = l_run > 0.0f ? m_used * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
+                p.partial_max[index] = l_tot > 0.0f ? m_fin * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
