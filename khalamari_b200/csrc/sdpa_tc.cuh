@@ -89,8 +89,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+
+// Results of tmem_ld32 may be used only after this.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -396,6 +398,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     uint32_t lo32[32], hi32[32];
                     tmem_ld32(lo32, tmem_s + 64 * sb + lane_base);
                     tmem_ld32(hi32, tmem_s + 64 * sb + 32 + lane_base);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         sraw[j] = lo32[j];
@@ -454,6 +457,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         for (int c0 = 0; c0 < D; c0 += 32) {
                             uint32_t o[32];
                             tmem_ld32(o, tmem_o + c0 + lane_base);
+                            tmem_ld_wait();
 #pragma unroll
                             for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
                             tmem_st32(tmem_o + c0 + lane_base, o);
@@ -533,6 +537,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     const int col = int(wg) * (D / 2) + c0;
                     uint32_t o[32];
                     tmem_ld32(o, tmem_o + col + lane_base);
+                    tmem_ld_wait();
                     if (valid) {
                         if (write_final) {
                             T* dst = reinterpret_cast<T*>(p.out) +
