@@ -91,6 +91,15 @@ KH_API kh_status kh_buffer_zero(kh_device* device, kh_buffer_ref buffer, uint64_
 /* Stream::new (BM/metal/stream/mod.rs); kh_stream_wrap adopts an existing cudaStream_t. */
 KH_API kh_status kh_stream_create(kh_device* device, kh_stream** out);
 KH_API kh_status kh_stream_wrap(kh_device* device, void* cuda_stream, kh_stream** out);
+/* Replay counts, the analogue of ReplayU32::Parameter (BM/metal/stream/replay.rs; bound in
+ * sliced_kv.rs:571-582, sliced_q.rs:565-582, kv-side contract in docs/executor_gqa.md:476-532). While a buffer is
+ * bound to the stream, every SlicedKv / SlicedQ map, direct and reduce launch recorded on it sizes its grid from
+ * the num_active_* arguments of the call - pass the recorded capacities (`num_total_*`) - and READS the counts it
+ * works with from `active_counts` when the kernel runs: four u32 {num_active_tokens, num_active_q_token_tiles,
+ * num_active_kv_splits, 0}, each clamped to the capacity passed at the call. A launch captured into a CUDA graph
+ * can therefore be replayed for a new batch after the metadata arrays and these four words have been rewritten
+ * (on the same stream, before the graph launch). Bind a null buffer to return to by-value counts. */
+KH_API kh_status kh_stream_bind_active_counts(kh_stream* stream, kh_buffer_ref active_counts);
 KH_API kh_status kh_stream_destroy(kh_stream* stream);
 /* ReplaySubmission::wait (BM/metal/stream/submission.rs:88). */
 KH_API kh_status kh_stream_synchronize(kh_stream* stream);

@@ -192,6 +192,7 @@ PROTOTYPES = {
     "kh_buffer_zero": [_vp, BufferRef, C.c_uint64, C.c_uint64],
     "kh_stream_create": [_vp, P(_vp)],
     "kh_stream_wrap": [_vp, _vp, P(_vp)],
+    "kh_stream_bind_active_counts": [_vp, BufferRef],
     "kh_stream_destroy": [_vp],
     "kh_stream_synchronize": [_vp],
     "kh_stream_write": [_vp, BufferRef, C.c_uint64, _vp, C.c_uint64],

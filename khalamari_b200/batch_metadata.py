@@ -36,6 +36,11 @@ class GQAMetadataBuffers:
         for pinned in self._host.values():
             pinned.array[:] = 0
         self._dev = {name: Buffer.new_zeroed(device, count * 4) for name, count in counts.items()}
+        # replay counts {num_active_tokens, num_active_q_token_tiles, num_active_kv_splits, 0}: the device words a
+        # recorded (graph-captured) launch reads its active counts from (Stream.bind_active_counts)
+        self._host_counts = PinnedArray(4, np.uint32)
+        self._host_counts.array[:] = 0
+        self._active_counts = Buffer.new_zeroed(device, 16)
         self._replay_shape = None
         self._variant = None
 
@@ -76,6 +81,11 @@ class GQAMetadataBuffers:
                 self._dev[name].write(0, self._host[name].array[:count])
             else:
                 stream.write(self._dev[name], 0, self._host[name].ptr, count * 4)
+        self._host_counts.array[:] = (shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates, 0)
+        if stream is None:
+            self._active_counts.write(0, self._host_counts.array)
+        else:
+            stream.write(self._active_counts, 0, self._host_counts.ptr, 16)
         self._replay_shape = shape
         self._variant = variant
         return shape
@@ -105,6 +115,9 @@ class GQAMetadataBuffers:
 
     def cu_sdpa_partial_outputs(self) -> Buffer:
         return self._dev["cu_sdpa_partial_outputs"]
+
+    def active_counts(self) -> Buffer:
+        return self._active_counts
 
     def host_image(self, name: str) -> np.ndarray:
         return self._host[name].array

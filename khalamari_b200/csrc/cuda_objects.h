@@ -16,6 +16,7 @@ struct kh_stream {
     kh_device* device;
     cudaStream_t stream;
     bool owned;
+    kh_buffer_ref active_counts;  // bound by kh_stream_bind_active_counts: launches read their counts from it
 };
 
 namespace kh {

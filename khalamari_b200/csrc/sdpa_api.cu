@@ -44,6 +44,8 @@ struct ReduceParams {
     uint64_t stat_stride;      // floats between consecutive partials of a row; 0: dense [partial][Hq][maxq]
     uint64_t out_stride;       // same for the partial outputs; 0: dense [partial][Hq][maxq][D]
     uint32_t heads_per_block;  // > 1 (one-token ranges only): a block serves this many consecutive heads
+    const uint32_t* active;    // replay: device words {tokens, Q-token tiles, templates}; the counts above bound them
+    uint32_t active_range_word; // which of the words counts this launch's ranges (0: tokens, 1: Q-token tiles)
 };
 
 template <typename T>
@@ -74,7 +76,12 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
     __shared__ float4 shared_acc[kReduceMaxThreads];
     __shared__ float2 shared_stat[kReduceMaxThreads];
     const uint32_t range = blockIdx.y;
-    if (range >= p.num_active_ranges) return;
+    uint32_t num_active_ranges = p.num_active_ranges, num_active_tokens = p.num_active_tokens;
+    if (p.active != nullptr) {
+        num_active_ranges = min(p.active[p.active_range_word], num_active_ranges);
+        num_active_tokens = min(p.active[0], num_active_tokens);
+    }
+    if (range >= num_active_ranges) return;
     if (p.heads_per_block > 1) {
         // decode shape: one token per range, few partials per row. A thread owns four output columns of one
         // head; no shared memory, no second wave of blocks.
@@ -84,7 +91,7 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
         const uint32_t d = (threadIdx.x % slots) * 4;
         if (head >= p.num_q_heads || threadIdx.x / slots >= p.heads_per_block) return;
         const uint32_t tok = p.q_ranges != nullptr ? p.q_ranges[range * 2] : range;
-        if (tok >= p.num_active_tokens) return;
+        if (tok >= num_active_tokens) return;
         const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
         const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
         const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads);
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
         tok_begin = p.q_ranges[range * 2];
         tok_end = p.q_ranges[range * 2 + 1];
     }
-    if (tok_begin >= p.num_active_tokens || tok_end > p.num_active_tokens || tok_end <= tok_begin) return;
+    if (tok_begin >= num_active_tokens || tok_end > num_active_tokens || tok_end <= tok_begin) return;
     const uint32_t num_toks = min(tok_end - tok_begin, p.max_q_tokens);
     const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
     const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
@@ -368,6 +375,7 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     const CUtensorMap& qmap = c.q_map(q);
     p.status = c.device->status;
     p.num_templates = num_templates;
+    p.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
     p.num_q_heads = c.num_q_heads;
     p.num_kv_heads = c.num_kv_heads;
     p.group = c.num_q_heads / c.num_kv_heads;
@@ -661,6 +669,19 @@ kh_status kh_stream_wrap(kh_device* device, void* cuda_stream, kh_stream** out) 
         stream->owned = false;
         stream->stream = static_cast<cudaStream_t>(cuda_stream);
         *out = stream.release();
+        return KH_OK;
+    });
+}
+
+kh_status kh_stream_bind_active_counts(kh_stream* stream, kh_buffer_ref active_counts) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(stream != nullptr, "null argument");
+        if (active_counts.ptr != nullptr) {
+            KH_REQUIRE(active_counts.bytes >= 16, "active_counts holds %llu bytes but 16 are required",
+                       (unsigned long long)active_counts.bytes);
+            KH_REQUIRE((reinterpret_cast<uintptr_t>(active_counts.ptr) & 3) == 0, "active_counts must be 4-byte aligned");
+        }
+        stream->active_counts = active_counts;
         return KH_OK;
     });
 }
@@ -966,6 +987,8 @@ kh_status kh_sliced_kv_reduce(kh_sliced_kv* compute, kh_stream* stream, const kh
         p.max_q_tokens = 1;
         p.num_active_ranges = num_active_tokens;
         p.num_active_tokens = num_active_tokens;
+        p.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
+        p.active_range_word = 0;
         launch_reduce(compute->config.dtype, p, num_active_tokens, stream->stream);
         return KH_OK;
     });
@@ -1173,6 +1196,8 @@ kh_status kh_sliced_q_reduce(kh_sliced_q* compute, kh_stream* stream, const kh_s
         p.max_q_tokens = compute->common.variant.max_q_tokens;
         p.num_active_ranges = num_active_q_token_tiles;
         p.num_active_tokens = s.num_total_tokens;
+        p.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
+        p.active_range_word = 1;
         launch_reduce(compute->config.dtype, p, num_active_q_token_tiles, stream->stream);
         return KH_OK;
     });
@@ -1366,6 +1391,8 @@ kh_status kh_sliced_kv_attend_static(kh_sliced_kv* compute, kh_stream* stream,
         r.max_q_tokens = 1;
         r.num_active_ranges = num_active_tokens;
         r.num_active_tokens = num_active_tokens;
+        r.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
+        r.active_range_word = 0;
         launch_reduce(config.dtype, r, num_active_tokens, stream->stream);
         return KH_OK;
     });

@@ -64,6 +64,10 @@ struct MapParams {
     uint32_t direct;                  // 1: write final output, 0: write partials
     const uint32_t* cu;               // fused reduce: [ranges + 1] first partial (= template) of every Q range; null: off
     uint32_t* arrivals;               // fused reduce: one zeroed counter per (Q range, KV head, head range)
+    // Replay: when set, the active counts {tokens, Q-token tiles, map task templates} are read from this device
+    // word triple when the kernel runs (a captured launch replays with new counts); num_active_tokens,
+    // num_active_q_tiles and num_templates are then the recorded capacities and only bound the values read.
+    const uint32_t* active;
     // Measurement aid (KH_GQA_DEBUG, 0 in normal use; outputs are meaningless when set). Bits: 1 consumers release
     // every stage without computing; 2 skip the task-end merge and publish; 4 skip the Q copies; 8 issue no K/V
     // copies (consumers run on stale shared memory); 16 / 32 / 64 skip QK / softmax / PV; 128 never run the
@@ -418,6 +422,21 @@ struct MapGeometry {
     static_assert(sizeof(TaskSlot) % 8 == 0, "task slots must keep the barriers 8-byte aligned");
 };
 
+// Counts a launch works with: its by-value arguments, or the device words a replayed launch reads them from.
+struct ActiveCounts {
+    uint32_t tokens, q_tiles, templates;
+};
+
+__device__ __forceinline__ ActiveCounts resolve_active(const MapParams& p) {
+    ActiveCounts a{p.num_active_tokens, p.num_active_q_tiles, p.num_templates};
+    if (p.active != nullptr) {
+        a.tokens = min(p.active[0], a.tokens);
+        a.q_tiles = min(p.active[1], a.q_tiles);
+        a.templates = min(p.active[2], a.templates);
+    }
+    return a;
+}
+
 // Per-lane decoded task (producer registers).
 struct TaskInfo {
     uint32_t tmpl, head_begin, num_heads, tok_begin, num_toks, kv_begin, kv_end, req_slot, kv_head, active;
@@ -427,7 +446,8 @@ struct TaskInfo {
 // Decodes flat task index -> template, KV head, head range, and applies the reference kernels'
 // early-return rules for padded and inactive templates (gqa_sdpa_sliced_kv_map.metal:56-58,
 // gqa_sdpa_sliced_q_map.metal:56-67).
-__device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint64_t task, uint32_t total_tasks) {
+__device__ __forceinline__ TaskInfo decode_task(const MapParams& p, const ActiveCounts& a, uint64_t task,
+                                                uint32_t total_tasks) {
     TaskInfo t;
     t.tmpl = t.head_begin = t.num_heads = t.tok_begin = t.num_toks = t.kv_begin = t.kv_end = t.req_slot = t.kv_head = 0;
     t.active = 0;
@@ -442,14 +462,14 @@ __device__ __forceinline__ TaskInfo decode_task(const MapParams& p, uint64_t tas
     t.num_heads = min(p.heads_per_task, p.group - range * p.heads_per_task);
     const uint32_t q_range = p.templates[t.tmpl * 3];
     if (p.q_ranges == nullptr) {
-        if (q_range >= p.num_active_tokens) return t;
+        if (q_range >= a.tokens) return t;
         t.tok_begin = q_range;
         t.num_toks = 1;
     } else {
-        if (q_range >= p.num_active_q_tiles) return t;
+        if (q_range >= a.q_tiles) return t;
         const uint32_t begin = p.q_ranges[q_range * 2];
         const uint32_t end = p.q_ranges[q_range * 2 + 1];
-        if (begin >= p.num_active_tokens || end > p.num_active_tokens || end <= begin) return t;
+        if (begin >= a.tokens || end > a.tokens || end <= begin) return t;
         t.tok_begin = begin;
         t.num_toks = min(min(end - begin, p.max_q_tokens), uint32_t(kMaxTaskTokens));
     }
@@ -491,13 +511,13 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
 // tasks are also neighbours in the page table. Returns false above the template limit (tasks are then dealt
 // round-robin). Called by every thread of the CTA; `scan` is shared scratch of `threads` u64 that nothing else
 // uses until the call returns, `task_range` two shared words that receive [begin, end).
-__device__ __forceinline__ bool balanced_task_range(const MapParams& p, uint64_t* scan, uint32_t* task_range,
-                                                    uint32_t threads) {
-    if (p.num_templates > kBalanceMaxTemplates) return false;
+__device__ __forceinline__ bool balanced_task_range(const MapParams& p, uint32_t num_templates, uint64_t* scan,
+                                                    uint32_t* task_range, uint32_t threads) {
+    if (num_templates > kBalanceMaxTemplates) return false;
     const uint32_t cells = p.num_kv_heads * p.head_ranges;
-    const uint32_t chunk = (p.num_templates + threads - 1) / threads;
-    const uint32_t first = min(threadIdx.x * chunk, p.num_templates);
-    const uint32_t last = min(first + chunk, p.num_templates);
+    const uint32_t chunk = (num_templates + threads - 1) / threads;
+    const uint32_t first = min(threadIdx.x * chunk, num_templates);
+    const uint32_t last = min(first + chunk, num_templates);
     auto cost_of = [&](uint32_t t) -> uint64_t {
         const uint32_t kv_begin = p.templates[t * 3 + 1];
         const uint32_t kv_end = p.templates[t * 3 + 2];
@@ -546,6 +566,7 @@ struct ProducerContext {
     uint32_t task_base, task_step, task_limit;
     bool balanced;             // the CTA owns one contiguous run of tasks
     bool allow_carry;          // consumers can continue a running state across tasks
+    ActiveCounts active;
     int lane;
 };
 
@@ -592,7 +613,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     };
     // Lane l decodes this CTA's visit number first_index + l.
     auto decode_batch = [&](uint32_t first_index) {
-        return decode_task(p, visit_to_task(uint64_t(first_index) + lane), task_limit);
+        return decode_task(p, c.active, visit_to_task(uint64_t(first_index) + lane), task_limit);
     };
     uint32_t carry_in = 0;
 
@@ -904,10 +925,12 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
-    const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
+    const ActiveCounts active = resolve_active(p);
+    const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
 
     uint32_t* task_range = const_cast<uint32_t*>(last_flag) + 1;  // [begin, end) of this CTA's run
-    const bool balanced = balanced_task_range(p, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+    const bool balanced =
+        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
     const uint32_t task_base = balanced ? task_range[0] : blockIdx.x;
     const uint32_t task_step = balanced ? 1u : gridDim.x;
     const uint32_t task_limit = balanced ? task_range[1] : total_tasks;
@@ -928,6 +951,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     producer.task_limit = task_limit;
     producer.balanced = balanced;
     producer.allow_carry = true;
+    producer.active = active;
     producer.lane = lane;
     if (warp == NCW + 1) {
         run_task_warp<G, P>(p, q_map, producer);

@@ -202,8 +202,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t tmem_p = tmem_base + 256;  // + 64 * buffer (+ 32 for the remainder) + 8 * (16-token chunk)
     const uint32_t tmem_q = tmem_base + 384;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
 
-    const uint32_t total_tasks = p.num_templates * p.num_kv_heads * p.head_ranges;
-    const bool balanced = balanced_task_range(p, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+    const ActiveCounts active = resolve_active(p);
+    const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
+    const bool balanced =
+        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
 
     ProducerContext producer{};
     producer.ring = ring;
@@ -221,6 +223,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     producer.task_limit = balanced ? task_range[1] : total_tasks;
     producer.balanced = balanced;
     producer.allow_carry = false;  // the running state lives in tensor memory and is published per task
+    producer.active = active;
     producer.lane = lane;
 
     if (warp == NSW + 2) {

@@ -138,6 +138,11 @@ class Stream:
     def read(self, buffer: Buffer, byte_offset: int, host_ptr: int, num_bytes: int) -> None:
         abi.call("kh_stream_read", self.handle, buffer.ref, int(byte_offset), C.c_void_p(host_ptr), int(num_bytes))
 
+    def bind_active_counts(self, counts: "Buffer | None") -> None:
+        """While bound, SDPA launches recorded on this stream read their active counts from ``counts`` when they
+        run (four u32: tokens, Q-token tiles, map task templates, 0); ``None`` returns to by-value counts."""
+        abi.call("kh_stream_bind_active_counts", self.handle, counts.ref if counts is not None else abi.BufferRef())
+
     def destroy(self) -> None:
         if self.handle:
             abi.call("kh_stream_destroy", self.handle)

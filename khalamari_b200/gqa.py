@@ -115,12 +115,28 @@ class GQAAttention:
         return self._computes[key]
 
     # -- GQA::record_sdpa (backend.rs:438-542) -----------------------------------------------------
+    def record_replay(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer, output: Buffer,
+                      gqa_layer_index: int = 0) -> int:
+        """``record_sdpa`` in the form a replay program records it (EM/replay.rs:21-74): grids sized by the
+        recorded capacities (``num_total_*``), active counts read on the device from the metadata's count words.
+        Capture this call into a CUDA graph; ``prepare`` on the same stream then retargets every later launch of
+        the graph, as long as the batch stays in the same replay bucket (same ``GQAReplayShape`` totals)."""
+        stream.bind_active_counts(self.metadata.active_counts())
+        try:
+            return self.record_sdpa(stream, q, kv_pages, page_ids, output, gqa_layer_index, capacities=True)
+        finally:
+            stream.bind_active_counts(None)
+
     def record_sdpa(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer, output: Buffer,
-                    gqa_layer_index: int = 0, after_map=None) -> int:
+                    gqa_layer_index: int = 0, after_map=None, capacities: bool = False) -> int:
         """Enqueues the selected branch on ``stream`` and returns how many kernels it launched. ``after_map``,
         when given, is called between the map and the reduce launch (a timing hook: record an event there)."""
         meta = self.metadata
         shape = meta.replay_shape()
+        if capacities:
+            shape = GQAReplayShape(shape.num_total_tokens, shape.num_total_tokens, shape.num_total_q_token_tiles,
+                                   shape.num_total_q_token_tiles, shape.num_total_sdpa_map_task_templates,
+                                   shape.num_total_sdpa_map_task_templates, shape.reduce_sdpa_partial_outputs)
         execution = meta.variant()
         if execution.kind == sdpa.MapKernelKind.SlicedKv:
             compute = self._sliced_kv(shape, execution)
