@@ -1,6 +1,6 @@
 """Builds ``libkhcuda_gqa.so`` in-tree with nvcc for sm_100a.
 
-The Rust ``inference-backend-cuda`` crate sketched in INTEGRATION.md runs the same nvcc command from its
+A Rust ``inference-backend-cuda`` crate that binds the library would run the same nvcc command from its
 ``build.rs``; this module is what the Python harness and the tests use.
 """
 from __future__ import annotations

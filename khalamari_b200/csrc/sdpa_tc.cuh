@@ -105,6 +105,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <typename T>
@@ -396,23 +404,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t sb = wg;
                 if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
                 tmem_fence_after();
+                // the row's 64 scores, kept as bit patterns in one register array (register pressure decides the
+                // speed of this loop: twelve warps leave 170 registers per thread)
                 uint32_t sraw[ST];
-                {
-                    uint32_t lo32[32], hi32[32];
-                    tmem_ld32(lo32, tmem_s + 64 * sb + lane_base);
-                    tmem_ld32(hi32, tmem_s + 64 * sb + 32 + lane_base);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        sraw[j] = lo32[j];
-                        sraw[32 + j] = hi32[j];
-                    }
-                }
+                tmem_ld32(*reinterpret_cast<uint32_t(*)[32]>(&sraw[0]), tmem_s + 64 * sb + lane_base);
+                tmem_ld32(*reinterpret_cast<uint32_t(*)[32]>(&sraw[32]), tmem_s + 64 * sb + 32 + lane_base);
+                tmem_ld_wait();
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_free_bar + 8 * sb);
                 const uint32_t tile_tok = t_tile_begin + i * ST;
-                float s[ST];
                 float tile_max = -INFINITY;
                 // most stages of a long context lie wholly inside every row's visible range: no masking then
                 const bool cut = tile_tok < lo || tile_tok + ST > hi;
@@ -420,15 +421,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < ST; ++j) {
                         const uint32_t tok = tile_tok + ((j % 32) / 8) * 16 + (j / 32) * 8 + (j % 8);
-                        s[j] = (tok >= lo && tok < hi) ? __uint_as_float(sraw[j]) : -INFINITY;
-                        tile_max = fmaxf(tile_max, s[j]);
+                        if (!(tok >= lo && tok < hi)) sraw[j] = 0xff800000u;  // -inf
+                        tile_max = fmaxf(tile_max, __uint_as_float(sraw[j]));
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < ST; ++j) {
-                        s[j] = __uint_as_float(sraw[j]);
-                        tile_max = fmaxf(tile_max, s[j]);
-                    }
+                    for (int j = 0; j < ST; ++j) tile_max = fmaxf(tile_max, __uint_as_float(sraw[j]));
                 }
                 // ---- the decision about the row maximum, in stage order
                 float m_prev = -INFINITY;
@@ -474,24 +472,28 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 if (lane == 0) mbar_arrive(decided_bar + 8 * wg);
                 const float m_used = m_ref;
                 const float shift = m_used == -INFINITY ? 0.0f : -m_used * p.scale_log2e;
-                uint32_t packed_hi[32], packed_lo[32];  // rounded pairs and their rounding remainders
-#pragma unroll
-                for (int j = 0; j < ST / 2; ++j) {
-                    const float p0 = fast_exp2(fmaf(s[2 * j], p.scale_log2e, shift));
-                    const float p1 = fast_exp2(fmaf(s[2 * j + 1], p.scale_log2e, shift));
-                    l_run += p0 + p1;
-                    packed_hi[j] = pack2<T>(p0, p1);
-                    const float2 r = unpack2<T>(packed_hi[j]);
-                    packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
-                }
-                // the buffer is free once the products of this group's previous stage have completed
+                // the probability buffer is free once the products of this group's previous stage have completed
                 if (g >= 2) {
                     const uint32_t gp = g - 2;
                     if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
                 }
                 tmem_fence_after();
-                tmem_st32(tmem_p + 64 * sb + lane_base, packed_hi);
-                tmem_st32(tmem_p + 64 * sb + 32 + lane_base, packed_lo);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t packed_hi[16], packed_lo[16];  // rounded pairs and their rounding remainders
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int c = 32 * half + 2 * j;
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c]), p.scale_log2e, shift));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c + 1]), p.scale_log2e, shift));
+                        l_run += p0 + p1;
+                        packed_hi[j] = pack2<T>(p0, p1);
+                        const float2 r = unpack2<T>(packed_hi[j]);
+                        packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
+                    }
+                    tmem_st16(tmem_p + 64 * sb + 16 * half + lane_base, packed_hi);
+                    tmem_st16(tmem_p + 64 * sb + 32 + 16 * half + lane_base, packed_lo);
+                }
                 tmem_st_wait();
                 if (tile_tok + ST > t_kv_end) {
                     // V rows of tokens at or past kv_end may never have been loaded: clear them so that a zero
