@@ -762,8 +762,10 @@ kh_status kh_selector_create_for_lookup(const kh_sdpa_config* config, uint32_t m
                        layout->num_page_ids_per_block > 0,
                    "GQA page-table layout dimensions must be positive");
         KH_REQUIRE(max_tokens > 0, "GQA lookup requires tokens");
-        if (c.io_dtype != KH_DTYPE_BFLOAT16 || !sliced_q_profile(c.head_dim, c.tokens_per_page) ||
-            group_size(c) > 32) {
+        // The reference's route table is written for BF16 (its only tensor-tile type); FP16 Q / output, which
+        // this backend also takes, follows the same routes.
+        const bool tile_type = c.io_dtype == KH_DTYPE_BFLOAT16 || c.io_dtype == KH_DTYPE_FLOAT16;
+        if (!tile_type || !sliced_q_profile(c.head_dim, c.tokens_per_page) || group_size(c) > 32) {
             auto variants = registry_variants(c);
             const uint64_t partials = mul_u64(max_tokens, registry_max_q_tokens(variants),
                                               "GQA partial-state-group capacity");

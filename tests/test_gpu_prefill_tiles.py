@@ -32,8 +32,7 @@ def test_policy_routes_prefill_chunks_to_128_row_tiles(device, dtype_name):
     run = DeviceCase(device, case, max_tokens=128)
     out = run.run(fused=False)
     variant = run.attention.metadata.variant()
-    if dtype_name == "bf16":  # fp16 batches keep the reference's route (one Q token per task)
-        assert variant.thread_block.max_q_tokens * variant.thread_block.max_q_heads == 128
+    assert variant.thread_block.max_q_tokens * variant.thread_block.max_q_heads == 128
     assert_within_contract(out, case.oracle_output(), f"prefill tiles {dtype_name}")
 
 
