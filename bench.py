@@ -1,15 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the paged GQA split-KV decode attention path.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c2|c3|c1]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c2|c3|c1|c4|c5p]
 
-One step = one attention call (split-KV map tasks and the LSE merge, one kernel launch) over one batch of
-synthetic paged decode requests.
+One step = one attention call (the split-KV map kernel and the LSE reduce kernel) over one batch of synthetic
+paged decode requests.
 Default workload: batch 64, q_len 1, Hq 64 / Hkv 8 / head_dim 128, bf16, context lengths uniform in
 [1024, 8192] (seed 1), 16-token pages in a 40,000-page pool with random block tables, split-KV partitions
 of 512 tokens. Metric: KV-read GB/s = algorithmic KV bytes (every visible K and V row once) / time.
 With N > 1 every rank runs its own batch of independent requests (no collective on the data path; weak
 scaling) and the value is the sum of all ranks' KV bytes over the slowest rank's time.
+Other workloads are exploration cases: c3 speculative verify, c1 the small fp16 case, c4 one long sequence
+whose pages are split over the ranks (one all-gather per step; strong scaling), c5p chunked prefill (TFLOP/s).
 """
 from __future__ import annotations
 
@@ -349,7 +351,9 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": spec["label"], "batch_per_gpu": len(contexts), "q_len": q_len,
                        "kv_tokens_per_gpu": int(sum(contexts)), "map_tasks": shape.num_sdpa_map_task_templates * spec["hkv"],
-                       "l2": "inputs (KV pages read per step) larger than L2; no flush", "parallelism": f"dp{world} by request"},
+                       "l2": "inputs (KV pages read per step) larger than L2; no flush" if kv_bytes > 126e6
+                       else "KV pages read per step fit L2: not an HBM measurement",
+                       "parallelism": f"dp{world} by request"},
             "tokens_per_s": round(total_tokens / (ms_per_step * 1e-3), 1),
             "tflops": round(attention_flops(spec, contexts) / (ms_per_step * 1e-3) / 1e12, 2),
             "hbm_frac": round(value / world / peak, 4),
