@@ -423,7 +423,10 @@ Route lookup_route_reference(const kh_sdpa_config& c, const kh_request_shape* re
 //    ring busy) and never above 2048 (bounds the per-task tail).
 Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* requests, uint32_t num_requests,
                         uint32_t sm_count) {
+    // measured: decode (one Q token per task) runs best with about 4 tasks per SM (2,048-token slices on the decode
+    // bench and on 1M tokens); Q-tile tasks, fewer and costlier, balance better with about 8
     constexpr uint32_t kTasksPerSm = 8;
+    constexpr uint32_t kDecodeTasksPerSm = 4;
     uint32_t max_q = 0, end = 0;
     unsigned __int128 visible = 0;
     for (uint32_t r = 0; r < num_requests; ++r) {
@@ -462,7 +465,8 @@ Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* request
             // one task per tile writes the output directly, no partials and no reduce (chunked prefill)
             slice = end;
         } else {
-            slice = decode_slice(end, work * head_groups, 256, 2048, (unsigned __int128)sm_count * kTasksPerSm);
+            slice = decode_slice(end, work * head_groups, 256, 2048,
+                                 (unsigned __int128)sm_count * (sliced_q ? kTasksPerSm : kDecodeTasksPerSm));
         }
     }
     const bool direct = sliced_q && slice == end;

@@ -412,10 +412,10 @@ def test_b200_policy_sizes_slices_for_148_sms():
     config = Config(Dtype.Bfloat16, 64, 8, 128, 16)
     sel = Selector.for_lookup(config, 64, GQAPageTableLayout(64, 1, 512, 1)).set_policy(SelectorPolicy.B200, 148)
     policy = GQAReplayBucketPolicy(64, sel.limits().max_map_task_templates)
-    # 64 x 4608 tokens x 8 KV heads over 148 SMs x 8 tasks -> 1024-token slices
+    # 64 x 4608 tokens x 8 KV heads over 148 SMs x 4 tasks -> 2048-token slices (the upper clamp)
     result = sel.select([RequestShape(4607, 1)] * 64, policy, 64)
     sizes = {len(m.request_local_kv_token_indices) for m in result.map_task_templates()}
-    assert max(sizes) == 1024
+    assert max(sizes) == 2048
     # a single short request cannot fill the machine: the floor of 256 tokens applies
     result = sel.select([RequestShape(2047, 1)], policy, 64)
     assert {len(m.request_local_kv_token_indices) for m in result.map_task_templates()} == {256}
