@@ -32,15 +32,31 @@ class GQAMetadataBuffers:
             "q_token_ranges": max_tokens * 2, "sdpa_map_task_templates": max_map_task_templates * 3,
             "cu_sdpa_partial_outputs": max_tokens + 1,
         }
-        self._host = {name: PinnedArray(count, np.uint32) for name, count in counts.items()}
-        for pinned in self._host.values():
-            pinned.array[:] = 0
-        self._dev = {name: Buffer.new_zeroed(device, count * 4) for name, count in counts.items()}
+        # One page-locked host block and one device block hold all arrays (each on a 256-byte boundary) and the four
+        # replay-count words, so that ``update`` is one fill and ONE stream-ordered copy; the arrays handed to the
+        # kernels are views into the device block.
+        self._offsets = {}
+        cursor = 256  # the first 256 bytes hold the replay-count words
+        self._counts_offset = 0
+        # the template array (the only large one) goes last, so that the copy can stop after the templates in use
+        order = [name for name in counts if name != "sdpa_map_task_templates"] + ["sdpa_map_task_templates"]
+        for name in order:
+            count = counts[name]
+            self._offsets[name] = (cursor, count)
+            cursor += -(-count * 4 // 256) * 256
+        self._block_bytes = cursor
+        self._host_block = PinnedArray(cursor // 4, np.uint32)
+        self._host_block.array[:] = 0
+        self._dev_block = Buffer.new_zeroed(device, cursor)
+        self._host = {name: self._host_block.array[off // 4: off // 4 + count] for name, (off, count) in self._offsets.items()}
+        self._host_ptr = {name: self._host_block.ptr + off for name, (off, _) in self._offsets.items()}
+        self._dev = {name: Buffer.wrap(device, self._dev_block.ref.ptr + off, count * 4)
+                     for name, (off, count) in self._offsets.items()}
         # replay counts {num_active_tokens, num_active_q_token_tiles, num_active_kv_splits, 0}: the device words a
         # recorded (graph-captured) launch reads its active counts from (Stream.bind_active_counts)
-        self._host_counts = PinnedArray(4, np.uint32)
-        self._host_counts.array[:] = 0
-        self._active_counts = Buffer.new_zeroed(device, 16)
+        self._host_counts = self._host_block.array[self._counts_offset // 4: self._counts_offset // 4 + 4]
+        self._active_counts = Buffer.wrap(device, self._dev_block.ref.ptr + self._counts_offset, 16)
+        self._uploaded_bytes = 0
         self._replay_shape = None
         self._variant = None
 
@@ -61,42 +77,26 @@ class GQAMetadataBuffers:
             raise abi.InvalidArgument(1, "GQA metadata update needs one slot and index per request and n+1 offsets")
         u32p = C.POINTER(C.c_uint32)
         arrays = abi.MetadataArraysC(
-            *[C.cast(self._host[name].ptr, u32p) for name, _ in _FIELDS], self._max_tokens, self._max_maps)
+            *[C.cast(self._host_ptr[name], u32p) for name, _ in _FIELDS], self._max_tokens, self._max_maps)
         shape_c = abi.ReplayShapeC()
         abi.call("kh_metadata_update", C.byref(arrays), rs.ctypes.data_as(u32p), ti.ctypes.data_as(u32p),
                  cu.ctypes.data_as(u32p), rs.size, selection.handle, C.byref(shape_c))
         shape = GQAReplayShape.from_c(shape_c)
         variant = selection.variant()
-        written = {
-            "req_slots": shape.num_tokens, "flat_token_indices": shape.num_tokens,
-            "visible_kv_token_ranges": shape.num_tokens * 2,
-            "q_token_ranges": 0 if variant.kind == MapKernelKind.SlicedKv else shape.num_q_token_tiles * 2,
-            "sdpa_map_task_templates": shape.num_total_sdpa_map_task_templates * 3,
-            "cu_sdpa_partial_outputs": shape.num_q_token_tiles + 1,
-        }
-        for name, count in written.items():
-            if count == 0:
-                continue
-            if stream is None:
-                self._dev[name].write(0, self._host[name].array[:count])
-            else:
-                stream.write(self._dev[name], 0, self._host[name].ptr, count * 4)
-        self._host_counts.array[:] = (shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates, 0)
+        self._host_counts[:] = (shape.num_tokens, shape.num_q_token_tiles, shape.num_sdpa_map_task_templates, 0)
+        used = self._offsets["sdpa_map_task_templates"][0] + shape.num_total_sdpa_map_task_templates * 12
+        self._uploaded_bytes = used
         if stream is None:
-            self._active_counts.write(0, self._host_counts.array)
+            self._dev_block.write(0, self._host_block.array[:used // 4])
         else:
-            stream.write(self._active_counts, 0, self._host_counts.ptr, 16)
+            stream.write(self._dev_block, 0, self._host_block.ptr, used)
         self._replay_shape = shape
         self._variant = variant
         return shape
 
     def upload_bytes(self) -> int:
-        """Bytes the last ``update`` copied to the device."""
-        shape, variant = self.replay_shape(), self.variant()
-        words = shape.num_tokens * 4 + shape.num_total_sdpa_map_task_templates * 3 + shape.num_q_token_tiles + 1
-        if variant.kind != MapKernelKind.SlicedKv:
-            words += shape.num_q_token_tiles * 2
-        return words * 4
+        """Bytes the last ``update`` copied to the device (the block up to the last template in use)."""
+        return self._uploaded_bytes
 
     def req_slots(self) -> Buffer:
         return self._dev["req_slots"]
@@ -120,7 +120,7 @@ class GQAMetadataBuffers:
         return self._active_counts
 
     def host_image(self, name: str) -> np.ndarray:
-        return self._host[name].array
+        return self._host[name]
 
     def replay_shape(self) -> GQAReplayShape:
         if self._replay_shape is None:

@@ -189,8 +189,8 @@ class GQAAttention:
         (kernel launches, host->device bytes, device->host bytes). The caller synchronises ``stream``."""
         num_tokens = int(cu_tokens[-1])
         row = self.core.num_q_heads * self.core.head_dim * self.io_dtype.item_size()
+        stream.write(q_dev, 0, q_host.ptr, num_tokens * row)  # first: the copy runs while the host plans the batch
         self.prepare(req_slots, token_indices, cu_tokens, num_tokens, stream, selection)
-        stream.write(q_dev, 0, q_host.ptr, num_tokens * row)
         launches = self.record_sdpa(stream, q_dev, kv_pages, page_ids, out_dev, gqa_layer_index)
         stream.read(out_dev, 0, out_host.ptr, num_tokens * row)
         return launches, num_tokens * row + self.metadata.upload_bytes(), num_tokens * row
