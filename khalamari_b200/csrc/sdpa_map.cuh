@@ -141,11 +141,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// K/V pages are read once per launch and never again: the copy carries an evict-first L2 policy so that the
+// stream does not push the partials, the block table and the batch metadata out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2,
-                                            int32_t c3, uint32_t bar) {
+                                            int32_t c3, uint32_t bar, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
         : "memory");
 }
 
@@ -760,6 +769,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
     uint32_t stage_counter = 0;
     bool aborted = false;
     const uint32_t rows_per_page = 2 * p.num_kv_heads * P;
+    const uint64_t kv_policy = l2_evict_first_policy();
     for (uint32_t taken = 0; !aborted; ++taken) {
         const uint32_t tslot = taken % TQ;
         if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
@@ -811,7 +821,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
                                 const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
                                 if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
                                 tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
-                                            static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar);
+                                            static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar, kv_policy);
                             }
                         } else {
                             // the task's last stage (or the measurement mode without copies): only boxes that hold
@@ -831,7 +841,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
                                     if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
                                     tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
                                                 static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0,
-                                                bar);
+                                                bar, kv_policy);
                                 }
                             }
                         }
