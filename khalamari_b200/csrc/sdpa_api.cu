@@ -227,12 +227,18 @@ static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     return make_instance<T, D, P, 8, 1, 1, false>();
 }
 
+template <typename T, int D>
+static MapInstance pick_page(uint32_t tokens_per_page, uint32_t rows, bool tensor_memory) {
+    if (tokens_per_page == 16) return pick_rows<T, D, 16>(rows, tensor_memory);
+    KH_REQUIRE(tokens_per_page == 8, "this build instantiates 8- and 16-token pages (got %u)", tokens_per_page);
+    return pick_rows<T, D, 8>(rows, tensor_memory);
+}
+
 template <typename T>
 static MapInstance pick_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows, bool tensor_memory) {
-    KH_REQUIRE(tokens_per_page == 16, "this build instantiates 16-token pages only (got %u)", tokens_per_page);
-    if (head_dim == 128) return pick_rows<T, 128, 16>(rows, tensor_memory);
+    if (head_dim == 128) return pick_page<T, 128>(tokens_per_page, rows, tensor_memory);
     KH_REQUIRE(head_dim == 256, "this build instantiates head_dim 128 and 256 only (got %u)", head_dim);
-    return pick_rows<T, 256, 16>(rows, tensor_memory);
+    return pick_page<T, 256>(tokens_per_page, rows, tensor_memory);
 }
 
 static MapInstance pick_instance(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows,
