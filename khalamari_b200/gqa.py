@@ -79,7 +79,9 @@ class GQAAttention:
         if num_tokens <= 0:
             raise abi.InvalidArgument(1, "GQA replay requires active tokens")
         if num_total_tokens is None:
-            num_total_tokens = num_tokens
+            # the executor records token capacities in replay buckets; a Q-tile capacity (bucketed by the selector)
+            # can never exceed it
+            num_total_tokens = self.policy.q_token_ranges.capacity(num_tokens)
         if selection is None:
             shapes = RequestShape.from_batch(list(token_indices), list(cu_tokens))
             selection = self.selector.select(shapes, self.policy, num_total_tokens)
@@ -89,7 +91,7 @@ class GQAAttention:
     def select_partitioned(self, variant, kv_slice, direct_output, token_indices, cu_tokens,
                            num_total_tokens=None) -> Selection:
         shapes = RequestShape.from_batch(list(token_indices), list(cu_tokens))
-        total = int(cu_tokens[-1]) if num_total_tokens is None else num_total_tokens
+        total = self.policy.q_token_ranges.capacity(int(cu_tokens[-1])) if num_total_tokens is None else num_total_tokens
         return self.selector.select_partitioned(variant, kv_slice, direct_output, shapes, self.policy, total)
 
     def _sliced_kv(self, shape: GQAReplayShape, execution):

@@ -160,17 +160,22 @@ class DeviceCase:
         self.layout = GQAPageTableLayout(case.layout.num_req_slots, case.layout.num_gqa_layers,
                                          case.layout.num_blocks, case.layout.num_page_ids_per_block)
         self.stream = Stream(device)
-        self.q = Buffer.from_slice(device, case.q_bits)
         self.kv_pages = Buffer.from_slice(device, case.pool)
         self.page_ids = Buffer.from_slice(device, case.page_ids)
         row = case.num_q_heads * case.head_dim
         self.canary = 0x4228 if case.dtype_name == "bf16" else 0x5140  # 42.0
-        self.out_rows = case.num_tokens + 2
-        self.output = Buffer.from_slice(device, np.full(self.out_rows * row, self.canary, dtype=np.uint16))
         self.attention = GQAAttention(
             device, GQACore(case.head_dim, case.num_q_heads, case.num_kv_heads, case.scale), self.dtype,
             case.page_bytes, self.layout, max_tokens or max(case.num_tokens, 1),
             policy if policy is not None else SelectorPolicy.B200, selector)
+        # Q and output are sized for the recorded token capacity (the replay bucket of the batch), as the executor
+        # sizes them; rows past the active tokens hold NaN bits (Q) and a canary (output)
+        capacity = self.attention.policy.q_token_ranges.capacity(max(case.num_tokens, 1))
+        q_rows = np.full(capacity * row, nan_bits(case.dtype_name), dtype=np.uint16)
+        q_rows[:case.num_tokens * row] = np.ascontiguousarray(case.q_bits).reshape(-1)
+        self.q = Buffer.from_slice(device, q_rows)
+        self.out_rows = capacity + 2
+        self.output = Buffer.from_slice(device, np.full(self.out_rows * row, self.canary, dtype=np.uint16))
 
     def run(self, selection=None, fused: bool | None = None) -> np.ndarray:
         """Runs the batch through map + reduce in one launch and, unless ``fused`` pins one form, also through the
