@@ -218,6 +218,9 @@ static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     constexpr int PS = 1;
     if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();
     if (rows <= 16) return make_instance<T, D, P, 1, 4, PS, false>();
+    // 17-24 rows (verify of four tokens with a group of six heads): three half tiles; the same tensor-core work as
+    // two full tiles, spread over six warps instead of four
+    if (rows <= 24) return make_instance<T, D, P, 3, 2, PS, true>();
     if (rows <= 32) return make_instance<T, D, P, 2, 2, PS, false>();
     if (rows <= 64) return make_instance<T, D, P, 4, 1, PS, false>();
     if constexpr (D == 128 && P == 16) {

@@ -403,7 +403,8 @@ struct MapGeometry {
     static constexpr int kMergeParts = KVW * PS;                     // (m, l, O) states merged per row tile
     static constexpr int kConsumerWarps = MT * KVW * PS;
     static constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + stream warp + task warp
-    static constexpr int kQRows = MT * 16;
+    static constexpr int kTileRows = HALF ? 8 : 16;  // valid rows of a row tile
+    static constexpr int kQRows = MT * kTileRows;  // Q rows of a task in shared memory (per 64-column half)
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;  // the producer publishes at most one task ahead of the consumers
     static constexpr int kFragRegs = HALF ? D / 4 : D / 2;        // O accumulator registers a warp parks
@@ -423,7 +424,6 @@ struct MapGeometry {
     static_assert(kStages >= 2 && kStages >= KVW, "shared memory ring too small");
     static_assert(D % 64 == 0 && (P == 8 || P == 16 || P == 32), "unsupported page geometry");
     static_assert((KVW & (KVW - 1)) == 0, "KV warps must be a power of two");
-    static_assert(!HALF || MT == 1, "half-tile mode needs a single row tile");
     static_assert((D / 8) % kMergeParts == 0, "output n-tiles must split evenly across the merging warps");
     static_assert(kWarpTokens % 16 == 0, "a warp handles whole 16-token MMA k-tiles");
     static_assert(PS == 1 || PS == 2, "a stage is split between at most two warps");
@@ -1013,7 +1013,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             uint32_t lo[NROW], hi[NROW];
 #pragma unroll
             for (int i = 0; i < NROW; ++i) {
-                const uint32_t row = mt * 16 + g + 8 * i;
+                const uint32_t row = mt * G::kTileRows + g + 8 * i;
                 const uint32_t row_tok = row / p.heads_per_task;
                 const uint32_t row_head = row % p.heads_per_task;
                 // rows that hold no (token, head) of this task are never published; leaving them unmasked keeps
@@ -1041,7 +1041,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 m_run[0] = m_run[1] = -INFINITY;
                 l_run[0] = l_run[1] = 0.0f;
             }
-            const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * 16 * 128;
+            const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes) + mt * G::kTileRows * 128;
             uint32_t q_addr[4];
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) q_addr[c4] = q_tile + v_row * 128 + (((2 * c4) ^ v_xor) << 4);
@@ -1253,7 +1253,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 if (part == 0 && tq == 0) {
 #pragma unroll
                     for (int i = 0; i < NROW; ++i) {
-                        const uint32_t row = mt * 16 + g + 8 * i;
+                        const uint32_t row = mt * G::kTileRows + g + 8 * i;
                         const uint32_t row_tok = row / p.heads_per_task;
                         const uint32_t row_head = row % p.heads_per_task;
                         if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
@@ -1364,7 +1364,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             constexpr int NTILES_PER_THREAD = DN / KP;
 #pragma unroll
             for (int i = 0; i < NROW; ++i) {
-                const uint32_t row = mt * 16 + g + 8 * i;
+                const uint32_t row = mt * G::kTileRows + g + 8 * i;
                 const uint32_t row_tok = row / p.heads_per_task;
                 const uint32_t row_head = row % p.heads_per_task;
                 if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
