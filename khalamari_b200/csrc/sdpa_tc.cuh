@@ -2,16 +2,18 @@
 // cores: tcgen05.mma with the accumulators in tensor memory. Same task ABI, rings, task warp and stream warp as
 // sdpa_map_kernel (sdpa_map.cuh); only the consumers differ.
 //
-//   S = Q K^T   tcgen05.mma kind::f16, M = 128 rows, N = 16 KV tokens (one page), K = 16 head-dim elements per
-//               instruction: A = the Q tile and B = the K rows of the page, both K-major with the 128-byte
-//               swizzle exactly as the TMA copies leave them in shared memory. A stage of 32 tokens is two pages.
-//   P           four softmax warps, one thread per row: tcgen05.ld brings the thread its row's 32 scores, so the
-//               row maximum and sum need no shuffles. P goes back to tensor memory as packed 16-bit pairs
-//               (rounded part and rounding remainder, as in the warp-level kernel).
-//   O += P V    A = P from tensor memory, B = the V rows of the page in shared memory, MN-major (V is stored
-//               [token][head dim], the head dim being the contiguous N dimension), N = 128.
+//   S = Q K^T   tcgen05.mma kind::f16, M = 128 rows, N = 32 KV tokens, K = 16 head-dim elements per instruction.
+//               A = the Q tile in tensor memory (copied there once per task). B = K rows in shared memory, K-major
+//               with the 128-byte swizzle exactly as the TMA copies leave them; one instruction takes row group g
+//               (8 token rows) of each of the stage's four pages, the only uniform stride 16-token pages offer.
+//   P           eight softmax warps in two groups that take alternate stages, one thread per row: tcgen05.ld brings
+//               the thread its row's 64 scores, so the row maximum and sum need no shuffles. P goes back to
+//               tensor memory as packed 16-bit pairs (rounded part and rounding remainder, as in the warp-level
+//               kernel).
+//   O += P V    A = P from tensor memory, B = the V rows in shared memory, MN-major (V is stored
+//               [token][head dim], the head dim being the contiguous N dimension), N = 128, K = 16.
 // The running maximum is updated lazily: O (in tensor memory) is rescaled only when a row's maximum grows by more
-// than 2^8, so the common stage costs one tensor-memory load and two stores per thread.
+// than 2^8, so the common stage costs two tensor-memory loads and four stores per thread.
 //
 // Warps: 0-7 softmax and epilogue (two groups of four), 8 Q K^T issue (one thread), 9 stream warp (K/V copies),
 // 10 task warp, 11 P V issue (one thread).
