@@ -63,7 +63,8 @@ MAP_TRAFFIC_PER_KV_BYTE = 317.27 / 309.67
 def traffic_estimate(spec, kv_bytes):
     """Bytes one map-kernel launch moves to and from DRAM, scaled from the profiler capture; only for the decode
     workload that was captured (None elsewhere)."""
-    if spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512:
+    if (spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512
+            and spec.get("kv_elem", 2) == 2):
         return int(kv_bytes * MAP_TRAFFIC_PER_KV_BYTE)
     return None
 
@@ -186,11 +187,13 @@ def build_device_case(device, spec, contexts, torch, seed):
     pool_pages = spec["pool_pages"] or (sum(pages_per_req) + 16)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
-    pool = torch.empty(pool_pages * page_elems, dtype=dt, device="cuda")
+    fp8 = spec.get("kv_elem", 2) == 1  # pages of FP8 E4M3FN codes (the reference's cache format)
+    pool = torch.empty(pool_pages * page_elems, dtype=torch.uint8 if fp8 else dt, device="cuda")
     chunk = 1 << 26
     for begin in range(0, pool.numel(), chunk):
         end = min(begin + chunk, pool.numel())
-        pool[begin:end] = torch.randn(end - begin, generator=gen, device="cuda", dtype=torch.float32).to(dt)
+        values = torch.randn(end - begin, generator=gen, device="cuda", dtype=torch.float32)
+        pool[begin:end] = values.to(torch.float8_e4m3fn).view(torch.uint8) if fp8 else values.to(dt)
     num_blocks = max(pages_per_req)
     rng = np.random.default_rng(seed)
     perm = rng.permutation(pool_pages).astype(np.uint32)
@@ -236,6 +239,10 @@ def run_ours(args):
     if args.uniform_context:
         spec["contexts"] = [args.uniform_context] * spec["batch"]
         spec["label"] += f" [uniform context {args.uniform_context}]"
+    if args.kv_dtype == "fp8":
+        spec["kv_elem"] = 1
+        spec["label"] += " [K/V pages of FP8 E4M3FN]"
+    kv_elem = spec.get("kv_elem", 2)
     contexts = contexts_for(spec, rank)
     q_len = spec["q_len"]
     device = Device(local)
@@ -246,8 +253,8 @@ def run_ours(args):
     layout = GQAPageTableLayout(len(contexts), 1, case["num_blocks"], 1)
     scale = 1.0 / float(np.sqrt(spec["d"]))
     attention = GQAAttention(device, GQACore(spec["d"], spec["hq"], spec["hkv"], scale), io_dtype,
-                             2 * spec["hkv"] * PAGE * spec["d"] * 2, layout, len(contexts) * q_len,
-                             SelectorPolicy.B200)
+                             2 * spec["hkv"] * PAGE * spec["d"] * kv_elem, layout, len(contexts) * q_len,
+                             SelectorPolicy.B200, kv_dtype=Dtype.Fp8E4M3FN if kv_elem == 1 else None)
     req_slots = list(range(len(contexts)))
     token_indices = [c - q_len for c in contexts]
     cu_tokens = [i * q_len for i in range(len(contexts) + 1)]
@@ -258,7 +265,7 @@ def run_ours(args):
     attention.fused = args.fused
     attention.prepare(req_slots, token_indices, cu_tokens, selection=selection)
     shape = attention.metadata.replay_shape()
-    kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * 2  # q_len new tokens are already in the cache
+    kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * kv_elem  # q_len new tokens are already in the cache
 
     def step(after_map=None):
         return attention.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0, after_map)
@@ -592,6 +599,8 @@ def main():
     parser.add_argument("--fused", action="store_true",
                         help="map and reduce in one launch (last-arriver merge) instead of the reference's two")
     parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")
+    parser.add_argument("--kv-dtype", default="io", choices=["io", "fp8"],
+                        help="element type of the K/V pages: the Q/output type (default) or FP8 E4M3FN")
     parser.add_argument("--context", type=int, default=0, help="workload c4: tokens of the one sequence")
     args = parser.parse_args()
     if args.impl == "reference":

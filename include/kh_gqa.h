@@ -317,7 +317,10 @@ KH_API kh_status kh_metadata_update(const kh_metadata_arrays* arrays, const uint
 /* ---- SlicedKv compute: BM/components/gqa/sdpa/sliced_kv.rs ---------------------------------- */
 /* sliced_kv::Config (sliced_kv.rs:90-98) plus the KV-cache element type, which the reference
  * fixes at one byte (sliced_kv.rs:113-125) and this library makes a parameter. tokens per page =
- * page_bytes / (2 * num_kv_heads * head_dim * sizeof(kv_dtype)). */
+ * page_bytes / (2 * num_kv_heads * head_dim * sizeof(kv_dtype)).
+ * kv_dtype = KH_DTYPE_FP8_E4M3FN: the reference's cache format; codes are decoded on load exactly as
+ * metal/gqa_fp8.metal:1-25 does (16-token pages, head_dim 128 or 256). kv_dtype = dtype: the pages hold
+ * Q/output-type elements. */
 typedef struct kh_sliced_kv_config {
     uint32_t num_q_heads;
     uint32_t num_kv_heads;
@@ -443,7 +446,8 @@ KH_API kh_status kh_sliced_kv_static_bytes_needed(const kh_sliced_kv_config* con
                                                   uint64_t* out);
 
 /* ---- SlicedQ compute: BM/components/gqa/sdpa/sliced_q.rs ------------------------------------ */
-/* sliced_q::Config (sliced_q.rs:145-153) plus kv_dtype. */
+/* sliced_q::Config (sliced_q.rs:145-153) plus kv_dtype (as in kh_sliced_kv_config; the reference fixes one
+ * byte per element, sliced_q.rs:202). */
 typedef struct kh_sliced_q_config {
     uint32_t num_q_heads;
     uint32_t num_kv_heads;

@@ -13,8 +13,8 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libkhcuda_gqa.so"
-SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "kv_page_write.cu"]
-HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "sdpa_map.cuh", "sdpa_tc.cuh", "../../include/kh_gqa.h"]
+SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu"]
+HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "map_instance.h", "sdpa_map.cuh", "sdpa_tc.cuh", "../../include/kh_gqa.h"]
 
 
 def nvcc_path() -> str:
@@ -38,7 +38,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     tmp = LIBRARY.with_suffix(f".so.tmp{os.getpid()}")
     cmd = [
         nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-shared", "-cudart", "static",
+        "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-shared", "-t", "4", "-cudart", "static",
         "-o", str(tmp),
     ] + [str(CSRC / name) for name in SOURCES]
     if verbose:

@@ -15,6 +15,7 @@
 #include "common.h"
 #include "cuda_objects.h"
 #include "host_sdpa.h"
+#include "map_instance.h"
 #include "sdpa_map.cuh"
 #include "sdpa_tc.cuh"
 
@@ -180,17 +181,6 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
 // ---------------------------------------------------------------------------------------------
 // Kernel instance table
 // ---------------------------------------------------------------------------------------------
-using MapKernel = void (*)(const CUtensorMap, const CUtensorMap, const MapParams);
-
-struct MapInstance {
-    MapKernel kernel;
-    int threads;
-    int smem_bytes;
-    int stage_tokens;
-    int box_rows;
-    int stages;
-};
-
 template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF>
 static MapInstance make_instance() {
     using G = MapGeometry<D, P, MT, KVW, PS, HALF>;
@@ -282,6 +272,7 @@ struct PoolMap {
 struct ComputeCommon {
     kh_device* device;
     kh_dtype dtype;
+    kh_dtype kv_dtype;
     uint32_t num_q_heads, num_kv_heads, head_dim, tokens_per_page, page_bytes;
     float scale;
     kh_page_table_layout layout;
@@ -335,12 +326,17 @@ struct ComputeCommon {
         // through their K-plane index only, so the row extent stops one plane short of the pool's end and a
         // page id beyond the pool falls outside it (the copy then writes zeros).
         const uint64_t plane_rows = uint64_t(num_kv_heads) * tokens_per_page;
-        const cuuint64_t dims[4] = {64, rows - plane_rows, head_dim / 64, 2};
-        const cuuint64_t strides[3] = {uint64_t(head_dim) * 2, 128, plane_rows * head_dim * 2};
-        const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(instance.box_rows), head_dim / 64, 2};
+        // FP8 pages: the same four dimensions in bytes, a 128-byte line holding 128 elements.
+        const bool fp8 = kv_dtype == KH_DTYPE_FP8_E4M3FN;
+        const uint32_t line = fp8 ? 128 : 64;  // elements of a 128-byte line
+        const uint64_t elem = fp8 ? 1 : 2;
+        const cuuint64_t dims[4] = {line, rows - plane_rows, head_dim / line, 2};
+        const cuuint64_t strides[3] = {uint64_t(head_dim) * elem, 128, plane_rows * head_dim * elem};
+        const cuuint32_t box[4] = {line, static_cast<cuuint32_t>(instance.box_rows), head_dim / line, 2};
         const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
-        const CUtensorMapDataType type =
-            dtype == KH_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const CUtensorMapDataType type = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                             : dtype == KH_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         const CUresult rc = encode_tiled_fn()(&entry.map, type, 4, pages.ptr, dims, strides, box, elem_strides,
                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -355,9 +351,11 @@ static void init_common(ComputeCommon& c, kh_device* device, kh_dtype dtype, kh_
                         uint32_t num_kv_heads, uint32_t head_dim, float scale, uint32_t page_bytes,
                         const kh_page_table_layout& layout, const kh_execution_variant& variant) {
     use_device(device);
-    KH_REQUIRE(kv_dtype == dtype, "this build reads K/V pages in the Q/output element type (kv_dtype must equal dtype)");
+    const bool fp8 = kv_dtype == KH_DTYPE_FP8_E4M3FN;
+    KH_REQUIRE(kv_dtype == dtype || fp8, "K/V pages hold the Q/output element type or FP8 E4M3FN");
     c.device = device;
     c.dtype = dtype;
+    c.kv_dtype = kv_dtype;
     c.num_q_heads = num_q_heads;
     c.num_kv_heads = num_kv_heads;
     c.head_dim = head_dim;
@@ -367,9 +365,10 @@ static void init_common(ComputeCommon& c, kh_device* device, kh_dtype dtype, kh_
     c.variant = variant;
     c.tokens_per_page = page_bytes / (2 * num_kv_heads * head_dim * dtype_size(kv_dtype));
     const uint32_t rows = variant.max_q_tokens * variant.max_q_heads;
-    c.instance = pick_instance(dtype, head_dim, c.tokens_per_page, rows, true);
+    c.instance = fp8 ? pick_instance_fp8(dtype, head_dim, c.tokens_per_page, rows)
+                     : pick_instance(dtype, head_dim, c.tokens_per_page, rows, true);
     // the one-launch map + reduce form counts arrivals inside the warp-level kernel
-    c.fused_instance = pick_instance(dtype, head_dim, c.tokens_per_page, rows, false);
+    c.fused_instance = fp8 ? c.instance : pick_instance(dtype, head_dim, c.tokens_per_page, rows, false);
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.instance.kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, c.instance.smem_bytes));
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.fused_instance.kernel),

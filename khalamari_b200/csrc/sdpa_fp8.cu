@@ -1,0 +1,47 @@
+// Map / direct kernel instances that read K/V pages of FP8 E4M3FN elements, the reference's cache format
+// (components/gqa/sdpa/sliced_kv.rs:118, sliced_q.rs:202: one byte per stored element; decode on load by
+// metal/gqa_fp8.metal:1-25). The kernel is sdpa_map_kernel with KVB = 1: the stream warp copies raw pages, decode
+// warps expand them into the 16-bit stage ring, and the consumers are the ones of the 16-bit instances.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+#include "map_instance.h"
+
+namespace kh {
+
+template <typename T, int D, int P, int MT, int KVW, bool HALF>
+static MapInstance make_fp8_instance() {
+    using G = MapGeometry<D, P, MT, KVW, 1, HALF, 1>;
+    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, 1, HALF, 1>, G::kThreads, G::kSmemBytes, G::kStageTokens,
+                       G::kBoxRows, G::kRawStages};
+}
+
+// Same consumer shapes by task rows as the 16-bit table; tasks of more than 64 rows stay on the warp-level
+// instance (the tensor-memory kernel reads 16-bit pages only).
+template <typename T, int D, int P>
+static MapInstance pick_fp8_rows(uint32_t rows) {
+    if (rows <= 8) return make_fp8_instance<T, D, P, 1, 4, true>();
+    if (rows <= 16) return make_fp8_instance<T, D, P, 1, 4, false>();
+    if (rows <= 24) return make_fp8_instance<T, D, P, 3, 2, true>();
+    if (rows <= 32) return make_fp8_instance<T, D, P, 2, 2, false>();
+    if (rows <= 64) return make_fp8_instance<T, D, P, 4, 1, false>();
+    return make_fp8_instance<T, D, P, 8, 1, false>();
+}
+
+template <typename T>
+static MapInstance pick_fp8_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+    KH_REQUIRE(tokens_per_page == 16, "FP8 pages: this build instantiates 16-token pages (got %u)", tokens_per_page);
+    if (head_dim == 128) return pick_fp8_rows<T, 128, 16>(rows);
+    KH_REQUIRE(head_dim == 256, "this build instantiates head_dim 128 and 256 only (got %u)", head_dim);
+    return pick_fp8_rows<T, 256, 16>(rows);
+}
+
+MapInstance pick_instance_fp8(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+    KH_REQUIRE(rows >= 1 && rows <= 128, "a Map task holds at most 128 (Q token, Q head) rows (got %u)", rows);
+    if (dtype == KH_DTYPE_BFLOAT16) return pick_fp8_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows);
+    KH_REQUIRE(dtype == KH_DTYPE_FLOAT16, "Q/output dtype must be Bfloat16 or Float16 on this backend");
+    return pick_fp8_geometry<__half>(head_dim, tokens_per_page, rows);
+}
+
+}  // namespace kh

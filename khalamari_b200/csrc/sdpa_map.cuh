@@ -33,6 +33,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <type_traits>
 
 namespace kh {
 
@@ -389,8 +390,12 @@ struct TaskSlot {
 //   KVW: KV warp groups per row tile (a stage goes to one group). PS: warps of a group that split one
 //   stage's tokens between them. HALF: only rows 0-7 of the (single) row tile are ever valid.
 //   Consumer warps = MT * KVW * PS; one extra warp produces.
-template <int D, int P, int MT, int KVW, int PS, bool HALF>
+// KVB: bytes of a stored K/V element. 2: the pages hold the Q/output element type and the consumers read the
+// copied stages directly. 1: the pages hold FP8 E4M3FN (one unit scale); the copies land in a ring of raw
+// stages and decode warps expand them into the 16-bit stage ring the consumers read.
+template <int D, int P, int MT, int KVW, int PS, bool HALF, int KVB = 2>
 struct MapGeometry {
+    static_assert(KVB == 1 || KVB == 2, "K/V elements are stored in one or two bytes");
     static constexpr int kStageTokens = (D == 128) ? 32 : 16;
     static constexpr int kBoxRows = (P < kStageTokens) ? P : kStageTokens;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;  // token boxes per stage
@@ -402,7 +407,10 @@ struct MapGeometry {
     static constexpr int kWarpTokens = kStageTokens / PS;            // KV tokens one warp handles per stage
     static constexpr int kMergeParts = KVW * PS;                     // (m, l, O) states merged per row tile
     static constexpr int kConsumerWarps = MT * KVW * PS;
-    static constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + stream warp + task warp
+    // FP8 pages: the decode work per stage is fixed while the tensor-core work grows with the row tiles, and
+    // head_dim 256 consumers need the registers of a smaller block
+    static constexpr int kDecodeWarps = (KVB == 2) ? 0 : ((MT >= 4 || D == 256) ? 2 : 4);
+    static constexpr int kThreads = (kConsumerWarps + 2 + kDecodeWarps) * 32;  // + stream warp + task warp
     static constexpr int kTileRows = HALF ? 8 : 16;  // valid rows of a row tile
     static constexpr int kQRows = MT * kTileRows;  // Q rows of a task in shared memory (per 64-column half)
     static constexpr int kQBytes = kQRows * D * 2;
@@ -412,16 +420,41 @@ struct MapGeometry {
     static constexpr int kMergeBytes = (kMergeParts == 1) ? 0 : MT * KVW * kMergeSlotFloats * 4;  // one state: no merge
     static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
-    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 512;
+    static constexpr int kFixedBytes =
+        kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + (KVB == 1 ? 1024 : 512);
     static constexpr int kSmemLimit = 227 * 1024 - 1024 /* alignment slack */;
-    static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+    static constexpr int kRawStageBytes = kStageBytes / 2;
+    // FP8 pages: a short 16-bit ring (two slots per KV warp: one being read, one being decoded) and the rest
+    // of shared memory for raw stages, which are what covers the HBM latency
+    static constexpr bool kTwoSlotsPerWarp = (kSmemLimit - kFixedBytes - 2 * KVW * kStageBytes) / kRawStageBytes >= 4;
+    static constexpr int kStagesFit =
+        (KVB == 1) ? (kTwoSlotsPerWarp ? 2 * KVW : KVW) : (kSmemLimit - kFixedBytes) / kStageBytes;
     // A KV warp consumes the stages whose running number is congruent to its index modulo KVW. With the
     // ring depth a multiple of KVW every ring slot is always consumed by the same warp, so a warp can
     // never wait on a slot more than one phase ahead of the slot's barrier (phase parity cannot alias).
     static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
     static constexpr int kStages = kStagesCapped / KVW * KVW;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
+    static constexpr int kRawStagesFit =
+        (KVB == 1) ? (kSmemLimit - kFixedBytes - kStages * kStageBytes) / kRawStageBytes : 0;
+    static constexpr int kRawStages = kRawStagesFit > 24 ? 24 : kRawStagesFit;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kRawStages * kRawStageBytes + kFixedBytes + 1024;
     static_assert(kStages >= 2 && kStages >= KVW, "shared memory ring too small");
+    static_assert(KVB == 2 || kRawStages >= 3, "raw stage ring too small");
+    // What the stream warp sees when the pages hold one-byte elements: the same token boxes at half the bytes
+    // (a 128-byte line holds 128 elements, so head_dim 128 has one column group).
+    struct Raw {
+        static constexpr int kStageTokens = MapGeometry::kStageTokens;
+        static constexpr int kBoxRows = MapGeometry::kBoxRows;
+        static constexpr int kBoxesPerPlane = MapGeometry::kBoxesPerPlane;
+        static constexpr int kColumnGroups = D / 128;
+        static constexpr int kBoxBytes = kBoxRows * 128;
+        static constexpr int kPlaneBoxBytes = kColumnGroups * kBoxBytes;
+        static constexpr int kCopyBytes = 2 * kPlaneBoxBytes;
+        static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;
+        static constexpr int kStages = MapGeometry::kRawStages;
+        static constexpr int kTaskSlots = MapGeometry::kTaskSlots;
+    };
+    static_assert(Raw::kStageBytes == kRawStageBytes, "raw stage geometry");
     static_assert(D % 64 == 0 && (P == 8 || P == 16 || P == 32), "unsupported page geometry");
     static_assert((KVW & (KVW - 1)) == 0, "KV warps must be a power of two");
     static_assert((D / 8) % kMergeParts == 0, "output n-tiles must split evenly across the merging warps");
@@ -878,11 +911,158 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
     }
 }
 
-template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF>
-__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, PS, HALF>::kThreads, 1)
+// ------------------------------ decode warps (FP8 pages) ------------------------------
+// Two FP8 E4M3FN bytes (bits 0-7 and 8-15 of `pair`, already moved to the high byte of each 16-bit lane) to two
+// elements of T, exactly (components/gqa/fp8.rs:46-58, metal/gqa_fp8.metal:1-25): sign and the seven magnitude
+// bits are placed so that the 4-bit exponent sits at the bottom of T's exponent field, then one multiplication
+// by 2^(bias of T - 7) moves the exponent into place. A zero exponent field is a subnormal of T there, which the
+// multiplication normalises, so the FP8 subnormals need no special case; 0x7f / 0xff (NaN) do.
+template <typename T>
+__device__ __forceinline__ uint32_t fp8x2_high_bytes_to_t2(uint32_t high_bytes);
+
+template <>
+__device__ __forceinline__ uint32_t fp8x2_high_bytes_to_t2<__nv_bfloat16>(uint32_t x) {
+    const uint32_t placed = (x & 0x80008000u) | ((x >> 4) & 0x07f007f0u);
+    uint32_t scaled;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(scaled) : "r"(placed), "r"(0x7b807b80u));  // x 2^120, both lanes
+    return scaled;
+}
+
+template <>
+__device__ __forceinline__ uint32_t fp8x2_high_bytes_to_t2<__half>(uint32_t x) {
+    const uint32_t placed = (x & 0x80008000u) | ((x >> 1) & 0x3f803f80u);
+    uint32_t scaled;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(scaled) : "r"(placed), "r"(0x5c005c00u));  // x 2^8, both lanes
+    return scaled;
+}
+
+// Nonzero when one of the four bytes of `word` is the NaN code (0x7f / 0xff).
+__device__ __forceinline__ uint32_t fp8x4_nan_mask(uint32_t word) {
+    return ((word & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u;
+}
+
+// Four FP8 bytes of `word` (element i in bits 8i..8i+7) to four elements of T in two words. PATCH: also give
+// the NaN codes a NaN value (without it they decode to +-480, a value no other code has).
+template <typename T, bool PATCH>
+__device__ __forceinline__ void fp8x4_to_t4(uint32_t word, uint32_t& lo, uint32_t& hi) {
+    lo = fp8x2_high_bytes_to_t2<T>(__byte_perm(word, 0u, 0x1404));
+    hi = fp8x2_high_bytes_to_t2<T>(__byte_perm(word, 0u, 0x3424));
+    if (PATCH && fp8x4_nan_mask(word)) {
+        constexpr uint32_t nan_bits = 0x7fffu;  // all exponent and mantissa bits of a 16-bit element
+        if ((word & 0x0000007fu) == 0x0000007fu) lo |= nan_bits;
+        if ((word & 0x00007f00u) == 0x00007f00u) lo |= nan_bits << 16;
+        if ((word & 0x007f0000u) == 0x007f0000u) hi |= nan_bits;
+        if ((word & 0x7f000000u) == 0x7f000000u) hi |= nan_bits << 16;
+    }
+}
+
+// Expands raw stages into the 16-bit stage ring: 16 raw bytes (16 elements of one K or V row) become two
+// 16-byte chunks. Decode warp w takes the stages whose running number is congruent to w modulo the number of
+// decode warps, so the warps work on different stages and hide one another's latencies.
+// Both rings use the 128-byte swizzle of the copies (chunk c of row r at position c ^ (r & 7) of its 128-byte
+// line); a raw line holds 128 elements, i.e. the 64-element lines of two column halves of the 16-bit stage.
+// Lane mapping, per block of four rows: eight consecutive lanes take the lower four chunks of one row and the
+// upper four of its neighbour (r ^ 1). That makes the eight 16-byte loads of a quarter warp, and each of its two
+// rounds of eight 16-byte stores, cover all 32 banks.
+template <typename T, typename G>
+__device__ __forceinline__ void run_decode_warps(const MapParams& p, const ProducerContext& c, uint8_t* stage_ring,
+                                                 uint32_t stage_full_bar, uint32_t stage_empty_bar, int decode_thread) {
+    using R = typename G::Raw;
+    constexpr int NS = G::kStages;
+    constexpr int NR = R::kStages;
+    constexpr int TQ = G::kTaskSlots;
+    constexpr int DW = G::kDecodeWarps;
+    constexpr int kLines = R::kBoxRows;                                   // 128-byte lines per block
+    constexpr int kBlocks = R::kBoxesPerPlane * 2 * R::kColumnGroups;     // (token box, plane, column group)
+    static_assert(kLines % 4 == 0, "a block is a whole number of four-row groups");
+    volatile uint32_t* const abort_flag = c.abort_flag;
+    const int lane = decode_thread & 31;
+    const uint32_t dw = uint32_t(decode_thread) >> 5;
+    // lane roles within a four-row group
+    const uint32_t sub = (lane >> 2) & 1, cc = lane & 3, pair = lane >> 4, flip = (lane >> 3) & 1;
+    const uint32_t row4 = 2 * pair + sub;             // row within the group
+    const uint32_t upper = sub ^ flip;                // which half of the raw line: raw chunk = 4 * upper + cc
+    const uint32_t raw_lane = row4 * 128 + (((4 * upper + cc) ^ row4) << 4);
+    const uint32_t out_lane = upper * G::kBoxBytes + row4 * 128;
+    const uint32_t even_lane = out_lane + (((2 * cc) ^ row4) << 4);
+    const uint32_t odd_lane = out_lane + (((2 * cc + 1) ^ row4) << 4);
+    uint32_t stage_base = 0;  // running number of the task's first stage
+    for (uint32_t taken = 0;; ++taken) {
+        const uint32_t tslot = taken % TQ;
+        if (!mbar_wait(c.stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) return;
+        const TaskSlot* ts = c.task_ring + tslot;
+        const uint32_t done = ts->done, num_tiles = ts->num_tiles;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.task_empty_bar + 8 * tslot);  // the descriptor has been read
+        if (done) return;
+        uint32_t stage = stage_base + (dw + DW - stage_base % DW) % DW;  // this warp's first stage of the task
+        for (; stage < stage_base + num_tiles; stage += DW) {
+            const uint32_t rslot = stage % NR, sslot = stage % NS;
+            if (!mbar_wait(c.full_bar + 8 * rslot, (stage / NR) & 1, abort_flag, p.status)) return;
+            if (!mbar_wait(stage_empty_bar + 8 * sslot, ((stage / NS) & 1) ^ 1, abort_flag, p.status)) return;
+            const uint32_t raw = smem_addr(c.ring + rslot * R::kStageBytes) + raw_lane;
+            const uint32_t out = smem_addr(stage_ring + sslot * G::kStageBytes);
+            // The common pass has no branches (the loads, conversions and stores of the 16 units interleave
+            // freely) and only notes whether a NaN code went by; a stage that held one is decoded again with
+            // the patching form.
+            uint32_t suspect = 0;
+            auto decode_stage = [&](auto patch) {
+                constexpr bool kPatch = decltype(patch)::value;
+#pragma unroll
+                for (int blk = 0; blk < kBlocks; ++blk) {
+                    constexpr int kGroups = R::kColumnGroups;
+                    const int group = blk % kGroups, plane = (blk / kGroups) & 1, box = blk / (2 * kGroups);
+                    const uint32_t block_out =
+                        out + box * G::kCopyBytes + plane * G::kPlaneBoxBytes + 2 * group * G::kBoxBytes;
+                    // all loads of the block first: they are volatile, as are the stores, and keep their order
+                    uint4 bytes[kLines / 4];
+#pragma unroll
+                    for (int rb = 0; rb < kLines / 4; ++rb) {
+                        // rows 4-7 of an eight-row swizzle period: position bit 2 flips (64 bytes)
+                        const uint32_t period = (rb & 1) * 64;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(bytes[rb].x), "=r"(bytes[rb].y), "=r"(bytes[rb].z), "=r"(bytes[rb].w)
+                                     : "r"((raw ^ period) + blk * kLines * 128 + rb * 512));
+                    }
+#pragma unroll
+                    for (int rb = 0; rb < kLines / 4; ++rb) {
+                        const uint32_t period = (rb & 1) * 64;
+                        if (!kPatch) {
+                            suspect |= fp8x4_nan_mask(bytes[rb].x) | fp8x4_nan_mask(bytes[rb].y) |
+                                       fp8x4_nan_mask(bytes[rb].z) | fp8x4_nan_mask(bytes[rb].w);
+                        }
+                        uint4 first, second;
+                        fp8x4_to_t4<T, kPatch>(bytes[rb].x, first.x, first.y);
+                        fp8x4_to_t4<T, kPatch>(bytes[rb].y, first.z, first.w);
+                        fp8x4_to_t4<T, kPatch>(bytes[rb].z, second.x, second.y);
+                        fp8x4_to_t4<T, kPatch>(bytes[rb].w, second.z, second.w);
+                        const uint32_t rows = block_out + rb * 512;
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rows + (even_lane ^ period)),
+                                     "r"(first.x), "r"(first.y), "r"(first.z), "r"(first.w) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rows + (odd_lane ^ period)),
+                                     "r"(second.x), "r"(second.y), "r"(second.z), "r"(second.w) : "memory");
+                    }
+                }
+            };
+            if (!(p.debug & 4096)) {
+                decode_stage(std::false_type{});
+                if (__any_sync(0xffffffffu, suspect != 0)) decode_stage(std::true_type{});
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(stage_full_bar + 8 * sslot);   // the 16-bit stage is written
+                mbar_arrive(c.empty_bar + 8 * rslot);       // the raw stage has been read
+            }
+        }
+        stage_base += num_tiles;
+    }
+}
+
+template <typename T, int D, int P, int MT, int KVW, int PS, bool HALF, int KVB = 2>
+__global__ void __launch_bounds__(MapGeometry<D, P, MT, KVW, PS, HALF, KVB>::kThreads, 1)
 sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
                 const MapParams p) {
-    using G = MapGeometry<D, P, MT, KVW, PS, HALF>;
+    using G = MapGeometry<D, P, MT, KVW, PS, HALF, KVB>;
     constexpr int ST = G::kStageTokens;
     constexpr int NS = G::kStages;
     constexpr int TQ = G::kTaskSlots;
@@ -898,12 +1078,14 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
-    uint8_t* q_ring = ring + NS * G::kStageBytes;
+    uint8_t* raw_ring = ring + NS * G::kStageBytes;  // FP8 pages only (no bytes otherwise)
+    uint8_t* q_ring = raw_ring + G::kRawStages * G::kRawStageBytes;
     float* merge = reinterpret_cast<float*>(q_ring + TQ * G::kQBytes);
     uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 3 * TQ);
+    constexpr int NR = G::kRawStages;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * NS + 3 * TQ + 2 * NR);
     volatile uint32_t* last_flag = abort_flag + 1;  // fused reduce: "this CTA completed its group"
 
     const int warp = threadIdx.x >> 5;
@@ -913,16 +1095,24 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     const uint32_t task_full_bar = smem_addr(bars + 2 * NS);
     const uint32_t task_empty_bar = smem_addr(bars + 2 * NS + TQ);
     const uint32_t stream_full_bar = smem_addr(bars + 2 * NS + 2 * TQ);
+    const uint32_t raw_full_bar = smem_addr(bars + 2 * NS + 3 * TQ);
+    const uint32_t raw_empty_bar = smem_addr(bars + 2 * NS + 3 * TQ + NR);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
+            // a stage is complete when its copies have landed, or when a decode warp has written it
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, MT * PS);
+        }
+        for (int s = 0; s < NR; ++s) {
+            mbar_init(raw_full_bar + 8 * s, 1);
+            mbar_init(raw_empty_bar + 8 * s, 1);
         }
         for (int s = 0; s < TQ; ++s) {
             // the expect_tx arrival, plus (when per-token visibility rows are staged) 32 lanes' cp.async arrivals
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
-            mbar_init(task_empty_bar + 8 * s, NCW + 1);  // every consumer warp and the stream warp
+            // every consumer warp, the stream warp and the decode warps
+            mbar_init(task_empty_bar + 8 * s, NCW + 1 + G::kDecodeWarps);
             mbar_init(stream_full_bar + 8 * s, 1);
         }
         *abort_flag = 0;
@@ -963,10 +1153,24 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     producer.allow_carry = true;
     producer.active = active;
     producer.lane = lane;
-    if (warp == NCW + 1) {
+    if constexpr (KVB == 1) {
+        // the stream warp fills the raw ring; the decode warps sit between it and the consumers' ring
+        producer.ring = raw_ring;
+        producer.full_bar = raw_full_bar;
+        producer.empty_bar = raw_empty_bar;
+    }
+    if (warp >= NCW + 2) {
+        if constexpr (KVB == 1) {
+            run_decode_warps<T, G>(p, producer, ring, full_bar, empty_bar, int(threadIdx.x) - (NCW + 2) * 32);
+        }
+    } else if (warp == NCW + 1) {
         run_task_warp<G, P>(p, q_map, producer);
     } else if (warp == NCW) {
-        run_stream_warp<G, P>(p, kv_map, producer);
+        if constexpr (KVB == 1) {
+            run_stream_warp<typename G::Raw, P>(p, kv_map, producer);
+        } else {
+            run_stream_warp<G, P>(p, kv_map, producer);
+        }
     } else {
         // ------------------------------ consumer warps ----------------------------------------
         const int mt = warp % MT;           // row tile

@@ -40,14 +40,18 @@ class GQACore:
 class GQAAttention:
     def __init__(self, device: Device, core: GQACore, io_dtype: Dtype, page_bytes: int,
                  page_table_layout: GQAPageTableLayout, max_tokens: int,
-                 policy: SelectorPolicy = SelectorPolicy.B200, selector: Selector | None = None):
+                 policy: SelectorPolicy = SelectorPolicy.B200, selector: Selector | None = None,
+                 kv_dtype: Dtype | None = None):
+        """``kv_dtype``: element type of the K/V pages; ``io_dtype`` (default) or ``Dtype.Fp8E4M3FN``, the
+        reference's cache format (decoded on load, components/gqa/sdpa/sliced_kv.rs:118)."""
         core.validate()
         self.device = device
         self.core = core
         self.io_dtype = io_dtype
+        self.kv_dtype = io_dtype if kv_dtype is None else kv_dtype
         self.page_bytes = page_bytes
         self.layout = page_table_layout
-        elem = io_dtype.item_size()
+        elem = self.kv_dtype.item_size()
         self.tokens_per_page = page_bytes // (2 * core.num_kv_heads * core.head_dim * elem)
         self.sdpa_config = sdpa.Config(io_dtype, core.num_q_heads, core.num_kv_heads, core.head_dim,
                                        self.tokens_per_page)
@@ -98,7 +102,7 @@ class GQAAttention:
         key = ("kv", execution, shape.num_total_tokens, shape.num_total_sdpa_map_task_templates)
         if key not in self._computes:
             config = sliced_kv.Config(self.core.num_q_heads, self.core.num_kv_heads, self.core.head_dim,
-                                      self.core.scale, self.page_bytes, self.layout, self.io_dtype)
+                                      self.core.scale, self.page_bytes, self.layout, self.io_dtype, self.kv_dtype)
             self._computes[key] = sliced_kv.Compute(
                 self.device, config, execution,
                 sliced_kv.Shape(shape.num_total_tokens, shape.num_total_sdpa_map_task_templates))
@@ -109,7 +113,7 @@ class GQAAttention:
                shape.num_total_sdpa_map_task_templates)
         if key not in self._computes:
             config = sliced_q.Config(self.core.num_q_heads, self.core.num_kv_heads, self.core.head_dim,
-                                     self.core.scale, self.page_bytes, self.io_dtype, self.layout)
+                                     self.core.scale, self.page_bytes, self.io_dtype, self.layout, self.kv_dtype)
             self._computes[key] = sliced_q.Compute(
                 self.device, config, execution,
                 sliced_q.Shape(shape.num_total_tokens, shape.num_total_q_token_tiles,

@@ -69,10 +69,11 @@ class PagedCase:
     page_ids: np.ndarray         # uint32 flat table
     k_f32: list = field(default_factory=list)   # per request [ctx, Hkv, D]
     v_f32: list = field(default_factory=list)
+    kv_elem_bytes: int = 2       # 1: the pages hold FP8 E4M3FN codes (the reference's cache format)
 
     @property
     def page_bytes(self) -> int:
-        return 2 * self.num_kv_heads * self.tokens_per_page * self.head_dim * 2
+        return 2 * self.num_kv_heads * self.tokens_per_page * self.head_dim * self.kv_elem_bytes
 
     @property
     def num_tokens(self) -> int:
@@ -83,7 +84,7 @@ class PagedCase:
 
     def kv_bytes(self) -> int:
         """Algorithmic KV bytes: every (request, kv head, visible token) K and V row counted once."""
-        return sum(self.contexts()) * 2 * self.num_kv_heads * self.head_dim * 2
+        return sum(self.contexts()) * 2 * self.num_kv_heads * self.head_dim * self.kv_elem_bytes
 
     def oracle_output(self, num_threads: int = 0) -> np.ndarray:
         threads = num_threads or oracle.max_threads()
@@ -94,10 +95,13 @@ class PagedCase:
 def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, head_dim: int, histories, q_lens,
               tokens_per_page: int = 16, num_gqa_layers: int = 1, layer_index: int = 0, num_page_ids_per_block: int = 1,
               pool_pages: int | None = None, extra_slots: int = 0, poison: bool = True, scale: float | None = None,
-              keep_f32: bool = True, q_std: float = 1.0) -> PagedCase:
+              keep_f32: bool = True, q_std: float = 1.0, kv_fp8: bool = False, kv_std: float = 1.0) -> PagedCase:
     """Builds requests with ``histories[r]`` cached tokens and ``q_lens[r]`` new tokens (already in the cache,
     as after the page-write step), a shared pool whose pages are handed out by a seeded permutation, and an
-    unwritten pool filled with NaN bit patterns when ``poison`` (the tail of a last page must not leak)."""
+    unwritten pool filled with NaN bit patterns when ``poison`` (the tail of a last page must not leak).
+    ``kv_fp8``: K and V go through the reference's page-write conversion (rounded to bf16, then to FP8 E4M3FN,
+    components/gqa/fp8.rs:19-44); the pool holds the codes and the oracle sees their decoded values, as in
+    sliced_kv_test.rs:171-182."""
     rng = np.random.default_rng(seed)
     num_reqs = len(histories)
     contexts = [int(h) + int(q) for h, q in zip(histories, q_lens)]
@@ -110,9 +114,13 @@ def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, h
     if pool_pages is None:
         pool_pages = total_pages + 3
     assert pool_pages >= total_pages
-    page_bytes = 2 * num_kv_heads * tokens_per_page * head_dim * 2
-    pool16 = np.full(pool_pages * page_bytes // 2, nan_bits(dtype_name) if poison else 0, dtype=np.uint16)
-    pool = pool16.view(np.uint8)
+    kv_elem = 1 if kv_fp8 else 2
+    page_bytes = 2 * num_kv_heads * tokens_per_page * head_dim * kv_elem
+    if kv_fp8:
+        pool = np.full(pool_pages * page_bytes, 0x7F if poison else 0, dtype=np.uint8)  # 0x7f: the NaN code
+    else:
+        pool16 = np.full(pool_pages * page_bytes // 2, nan_bits(dtype_name) if poison else 0, dtype=np.uint16)
+        pool = pool16.view(np.uint8)
     table = np.zeros(layout.num_page_ids(), dtype=np.uint32)
     # request r lives in slot order shuffled so that slot != request index
     slots = rng.permutation(num_slots)[:num_reqs].astype(np.uint32)
@@ -124,12 +132,16 @@ def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, h
         cursor += pages_needed[r]
         base = ((int(slots[r]) * num_gqa_layers + layer_index) * num_blocks) * num_page_ids_per_block
         table[base:base + ids.size] = ids
-        k = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32)
-        v = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32)
-        k_bits, k_round = round_to(dtype_name, k)
-        v_bits, v_round = round_to(dtype_name, v)
+        k = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
+        v = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
+        if kv_fp8:
+            k_bits, k_round = fp8_codes(k)
+            v_bits, v_round = fp8_codes(v)
+        else:
+            k_bits, k_round = round_to(dtype_name, k)
+            v_bits, v_round = round_to(dtype_name, v)
         oracle.scatter_paged(pool, table, layout, int(slots[r]), layer_index, tokens_per_page, num_kv_heads,
-                             head_dim, 2, 0, k_bits, v_bits)
+                             head_dim, kv_elem, 0, k_bits, v_bits)
         if keep_f32:
             case_k.append(k_round)
             case_v.append(v_round)
@@ -142,7 +154,15 @@ def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, h
         scale = 1.0 / float(np.sqrt(head_dim))
     return PagedCase(dtype_name, num_q_heads, num_kv_heads, head_dim, tokens_per_page, scale, layout, layer_index,
                      slots.tolist(), [int(h) for h in histories], [int(x) for x in q_lens], cu, q_bits, q_round, pool,
-                     table, case_k, case_v)
+                     table, case_k, case_v, kv_elem)
+
+
+def fp8_codes(values: np.ndarray):
+    """Returns (uint8 FP8 E4M3FN codes of the bf16-rounded values, f32 value of those codes)."""
+    bf16_bits, _ = oracle.round_bf16(values)
+    codes = oracle.fp8_from_bf16_bits(bf16_bits.reshape(-1)).reshape(values.shape)
+    decoded = oracle.bf16_bits_to_f32(oracle.fp8_to_bf16_bits(codes.reshape(-1))).reshape(values.shape)
+    return codes, decoded
 
 
 class DeviceCase:
@@ -167,7 +187,8 @@ class DeviceCase:
         self.attention = GQAAttention(
             device, GQACore(case.head_dim, case.num_q_heads, case.num_kv_heads, case.scale), self.dtype,
             case.page_bytes, self.layout, max_tokens or max(case.num_tokens, 1),
-            policy if policy is not None else SelectorPolicy.B200, selector)
+            policy if policy is not None else SelectorPolicy.B200, selector,
+            kv_dtype=Dtype.Fp8E4M3FN if case.kv_elem_bytes == 1 else None)
         # Q and output are sized for the recorded token capacity (the replay bucket of the batch), as the executor
         # sizes them; rows past the active tokens hold NaN bits (Q) and a canary (output)
         capacity = self.attention.policy.q_token_ranges.capacity(max(case.num_tokens, 1))
