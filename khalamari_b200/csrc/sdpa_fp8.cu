@@ -10,17 +10,24 @@
 
 namespace kh {
 
-template <typename T, int D, int P, int MT, int KVW, bool HALF>
+template <typename T, int D, int P, int MT, int KVW, bool HALF, int PS = 1>
 static MapInstance make_fp8_instance() {
-    using G = MapGeometry<D, P, MT, KVW, 1, HALF, 1>;
-    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, 1, HALF, 1>, G::kThreads, G::kSmemBytes, G::kStageTokens,
+    using G = MapGeometry<D, P, MT, KVW, PS, HALF, 1>;
+    return MapInstance{sdpa_map_kernel<T, D, P, MT, KVW, PS, HALF, 1>, G::kThreads, G::kSmemBytes, G::kStageTokens,
                        G::kBoxRows, G::kRawStages};
 }
 
 // Same consumer shapes by task rows as the 16-bit table; tasks of more than 64 rows stay on the warp-level
 // instance (the tensor-memory kernel reads 16-bit pages only).
+// Decode shapes (one row tile) at head_dim 128: two KV warp groups of two warps that split a stage's tokens,
+// instead of four groups of one. The 16-bit ring (two slots per group) then takes 64 KB instead of 128 KB, and
+// the raw ring, whose depth is what covers the HBM latency, twice as many stages.
 template <typename T, int D, int P>
 static MapInstance pick_fp8_rows(uint32_t rows) {
+    if constexpr (D == 128) {
+        if (rows <= 8) return make_fp8_instance<T, D, P, 1, 2, true, 2>();
+        if (rows <= 16) return make_fp8_instance<T, D, P, 1, 2, false, 2>();
+    }
     if (rows <= 8) return make_fp8_instance<T, D, P, 1, 4, true>();
     if (rows <= 16) return make_fp8_instance<T, D, P, 1, 4, false>();
     if (rows <= 24) return make_fp8_instance<T, D, P, 3, 2, true>();

@@ -81,3 +81,22 @@ def test_library_codec_equals_the_oracle_on_every_bf16_value():
         assert ours == theirs or (ours & 0x7F == 0x7F and theirs & 0x7F == 0x7F), hex(bits)
     for bits in range(256):
         assert kv_page_write.fp8_e4m3_to_bf16(bits) == _oracle_decode(bits)
+
+
+def test_fp8_page_pool_fixture_round_trips_through_the_paged_gather():
+    """The FP8 attention fixture (helpers.make_case with kv_fp8): the codes gathered back from the pool decode to
+    the values the oracle is given, and the quality bound of sliced_kv_test.rs:69-114 holds between attention on
+    the decoded values and on the bf16 values they came from (mean abs error <= 0.025 of the output scale)."""
+    from helpers import make_case
+
+    fp8_case = make_case(77, "bf16", 8, 2, 128, [40, 130], [1, 1], kv_fp8=True)
+    for r, slot in enumerate(fp8_case.req_slots):
+        ctx = fp8_case.contexts()[r]
+        k_codes, v_codes = oracle.gather_paged(fp8_case.pool, fp8_case.page_ids, fp8_case.layout, slot, 0,
+                                               fp8_case.tokens_per_page, 2, 128, 1, ctx)
+        k = oracle.bf16_bits_to_f32(oracle.fp8_to_bf16_bits(k_codes.reshape(-1))).reshape(ctx, 2, 128)
+        v = oracle.bf16_bits_to_f32(oracle.fp8_to_bf16_bits(v_codes.reshape(-1))).reshape(ctx, 2, 128)
+        assert np.array_equal(k, fp8_case.k_f32[r]) and np.array_equal(v, fp8_case.v_f32[r])
+    wide_case = make_case(77, "bf16", 8, 2, 128, [40, 130], [1, 1])  # same seed: the same values before rounding
+    fp8_out, wide_out = fp8_case.oracle_output(), wide_case.oracle_output()
+    assert np.mean(np.abs(fp8_out - wide_out)) <= 0.025
