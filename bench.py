@@ -58,14 +58,15 @@ def load_peaks():
 # committed capture of the decode workload at batch 16 (profiles/sdpa_map_kernel_decode_b16_full.md: 317.27 MB over
 # 309.67 MB); traffic grows with the tokens processed, so the ratio carries to the full batch.
 MAP_TRAFFIC_PER_KV_BYTE = 317.27 / 309.67
+MAP_TRAFFIC_PER_FP8_KV_BYTE = 308.63 / 301.35  # profiles/sdpa_map_kernel_fp8_decode_b32_full.md
 
 
 def traffic_estimate(spec, kv_bytes):
-    """Bytes one map-kernel launch moves to and from DRAM, scaled from the profiler capture; only for the decode
+    """Bytes one map-kernel launch moves to and from DRAM, scaled from the profiler captures; only for the decode
     workload that was captured (None elsewhere)."""
-    if (spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512
-            and spec.get("kv_elem", 2) == 2):
-        return int(kv_bytes * MAP_TRAFFIC_PER_KV_BYTE)
+    if spec.get("q_len") == 1 and spec["d"] == 128 and spec["hkv"] == 8 and spec.get("partition") == 512:
+        ratio = MAP_TRAFFIC_PER_KV_BYTE if spec.get("kv_elem", 2) == 2 else MAP_TRAFFIC_PER_FP8_KV_BYTE
+        return int(kv_bytes * ratio)
     return None
 
 
