@@ -55,7 +55,7 @@ def load_peaks():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_map_kernel launch over its algorithmic K/V bytes, from the
-# committed capture of the decode workload at batch 16 (profiles/sdpa_map_kernel_decode_b16_full.md: 317.27 MB over
+# committed capture of the decode workload at batch 16 (profiles/sdpa_map_kernel_decode_b16_full.md: 315.70 MB over
 # 309.67 MB); traffic grows with the tokens processed, so the ratio carries to the full batch.
 MAP_TRAFFIC_PER_KV_BYTE = 315.70 / 309.67
 MAP_TRAFFIC_PER_FP8_KV_BYTE = 308.63 / 301.35  # profiles/sdpa_map_kernel_fp8_decode_b32_full.md
