@@ -10,6 +10,10 @@ Default workload: batch 64, q_len 1, Hq 64 / Hkv 8 / head_dim 128, bf16, context
 of 512 tokens. Metric: KV-read GB/s = algorithmic KV bytes (every visible K and V row once) / time.
 With N > 1 every rank runs its own batch of independent requests (no collective on the data path; weak
 scaling) and the value is the sum of all ranks' KV bytes over the slowest rank's time.
+The line also carries ``parity`` (the bench's own output against the CPU oracle on the same stored inputs) and,
+for the default workload, ``split_kv``: one long sequence of 131,072 / 524,288 / 1,048,576 tokens whose pages are
+split over the same N ranks (local map, one NCCL all-gather of a 16.5 KB record per rank, LSE merge), with the
+step, the local kernels, the exchange and the efficiency against one GPU.
 Other workloads are exploration cases: c3 speculative verify, c1 the small fp16 case, c4 one long sequence
 whose pages are split over the ranks (one all-gather per step; strong scaling), c5p chunked prefill (TFLOP/s).
 """
@@ -44,6 +48,7 @@ WORKLOADS = {
                contexts=[128, 517, 1024, 2048], label="decode B4 Hq16/Hkv2/D256 fp16 ctx {128,517,1024,2048} P16"),
 }
 PAGE = 16
+SPLIT_CONTEXTS = (131072, 524288, 1048576)  # one long sequence split over the ranks (configuration 4)
 
 
 def load_peaks():
@@ -54,11 +59,12 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_map_kernel launch over its algorithmic K/V bytes, from the
-# committed capture of the decode workload at batch 16 (profiles/sdpa_map_kernel_decode_b16_full.md: 315.70 MB over
-# 309.67 MB); traffic grows with the tokens processed, so the ratio carries to the full batch.
+# dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_map_kernel launch over its algorithmic K/V bytes, from
+# profiler captures of the decode workload at a reduced batch (315.70 MB moved for 309.67 MB of 16-bit pages;
+# 308.63 MB for 301.35 MB of FP8 pages); traffic grows with the tokens processed, so the ratio carries to the
+# full batch.
 MAP_TRAFFIC_PER_KV_BYTE = 315.70 / 309.67
-MAP_TRAFFIC_PER_FP8_KV_BYTE = 308.63 / 301.35  # profiles/sdpa_map_kernel_fp8_decode_b32_full.md
+MAP_TRAFFIC_PER_FP8_KV_BYTE = 308.63 / 301.35
 
 
 def traffic_estimate(spec, kv_bytes):
@@ -82,6 +88,16 @@ def contexts_for(spec, rank):
         return list(spec["contexts"])
     rng = np.random.default_rng(spec["seed"] + 1000 * rank)
     return rng.integers(spec["lo"], spec["hi"] + 1, size=spec["batch"]).tolist()
+
+
+def workload_config(spec, contexts, world):
+    """The ``config`` object of the JSON line: the same for this library's arm and the reference arm."""
+    kv_bytes = sum(contexts) * 2 * spec["hkv"] * spec["d"] * spec.get("kv_elem", 2)
+    return {"workload": spec["label"], "batch_per_gpu": len(contexts), "q_len": spec["q_len"],
+            "kv_tokens_per_gpu": int(sum(contexts)),
+            "l2": "inputs (KV pages read per step) larger than L2; no flush" if kv_bytes > 126e6
+            else "KV pages read per step fit L2: not an HBM measurement",
+            "parallelism": f"dp{world} by request"}
 
 
 class ClockSampler:
@@ -203,7 +219,8 @@ def build_device_case(device, spec, contexts, torch, seed):
     for r, n in enumerate(pages_per_req):
         table[r, :n] = perm[cursor:cursor + n]
         cursor += n
-    total_q = len(contexts) * spec["q_len"]
+    q_lens = spec.get("q_lens") or [spec["q_len"]] * len(contexts)
+    total_q = sum(q_lens)
     q = torch.randn(total_q * hq * d, generator=gen, device="cuda", dtype=torch.float32).to(dt)
     out = torch.zeros_like(q)
     wrap = lambda t: Buffer.wrap(device, t.data_ptr(), t.numel() * t.element_size())
@@ -211,23 +228,100 @@ def build_device_case(device, spec, contexts, torch, seed):
                 d_table=Buffer.from_slice(device, table.reshape(-1)), num_blocks=num_blocks)
 
 
-def run_ours(args):
+# ---- parity of the bench's own output against the CPU oracle (rank 0, outside every timed region) ----------
+def _storage_to_f32(bits_u8, spec, fp8):
+    import oracle
+    if fp8:
+        lut = oracle.bf16_bits_to_f32(oracle.fp8_to_bf16_bits(np.arange(256, dtype=np.uint8)))
+        return lut[bits_u8]
+    bits = np.ascontiguousarray(bits_u8).view(np.uint16)
+    if spec["dtype"] == "bf16":
+        return oracle.bf16_bits_to_f32(bits)
+    return bits.view(np.float16).astype(np.float32)
+
+
+def oracle_parity(spec, contexts, q_lens, case, out_f32, sample_tokens=None):
+    """Copies the device-resident Q, page pool and block tables back, gathers every request's K/V rows through the
+    oracle's paged gather (the reference's address function), runs the CPU oracle on those values and compares the
+    output the bench produced. ``sample_tokens``: per request, the new-token indices to check (None: all of them).
+    Returns the ``parity`` object of the JSON line and the seconds the oracle pass took."""
     import torch
+
+    import oracle
+    hq, hkv, d = spec["hq"], spec["hkv"], spec["d"]
+    fp8 = spec.get("kv_elem", 2) == 1
+    elem = 1 if fp8 else 2
+    pool = case["pool"].view(torch.uint8).cpu().numpy()
+    q_all = _storage_to_f32(case["q"].view(torch.uint8).cpu().numpy(), spec, False).reshape(-1, hq, d)
+    layout = oracle.PageTableLayout(len(contexts), 1, case["num_blocks"], 1)
+    table = case["table"].reshape(-1)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int64)
+    q_rows, ks, vs, histories, flat = [], [], [], [], []
+    for r, ctx in enumerate(contexts):
+        tokens = range(q_lens[r]) if sample_tokens is None else sample_tokens[r]
+        if not len(tokens):
+            continue
+        k_u8, v_u8 = oracle.gather_paged(pool, table, layout, r, 0, PAGE, hkv, d, elem, ctx)
+        k = _storage_to_f32(k_u8, spec, fp8).reshape(ctx, hkv, d)
+        v = _storage_to_f32(v_u8, spec, fp8).reshape(ctx, hkv, d)
+        if sample_tokens is None:
+            q_rows.append(q_all[cu[r]:cu[r + 1]])
+            ks.append(k)
+            vs.append(v)
+            histories.append((ctx - q_lens[r], q_lens[r]))
+            flat.extend(range(int(cu[r]), int(cu[r + 1])))
+        else:
+            for t in tokens:
+                visible = ctx - q_lens[r] + t + 1
+                q_rows.append(q_all[cu[r] + t:cu[r] + t + 1])
+                ks.append(k[:visible])
+                vs.append(v[:visible])
+                histories.append((visible - 1, 1))
+                flat.append(int(cu[r]) + t)
+    cu_oracle = np.concatenate([[0], np.cumsum([n for _, n in histories])])
+    scale = spec.get("scale") or 1.0 / float(np.sqrt(d))
+    t0 = time.perf_counter()
+    expected = oracle.projected_gqa(cu_oracle, [h for h, _ in histories], np.concatenate(q_rows), ks, vs, d, hq, hkv,
+                                    scale, host_threads())
+    seconds = time.perf_counter() - t0
+    actual = out_f32.reshape(-1, hq, d)[flat]
+    err = np.abs(actual - expected)
+    ok = (err <= 2e-3) | (err <= 1e-2 * np.abs(expected))
+    beyond = err > 2e-3
+    return {"max_abs": float(err.max()), "max_rel": float((err / np.maximum(np.abs(expected), 1e-30))[beyond].max())
+            if beyond.any() else 0.0, "rows_checked": int(len(flat) * hq), "rows_total": int(cu[-1] * hq),
+            "rule": "per element |a-b| <= 2e-3 or |a-b| <= 1e-2*|b|, against the CPU oracle on the same stored "
+                    "Q/K/V, gathered from the bench's own page pool",
+            "pass": bool(ok.all()) and bool(np.isfinite(actual).all())}, seconds
+
+
+def output_f32(tensor, spec, torch):
+    return tensor.float().cpu().numpy()
+
+
+def init_ranks(torch):
     import torch.distributed as dist
-
-    from khalamari_b200.device import Device, Dtype, PinnedArray, Stream
-    from khalamari_b200.gqa import GQAAttention, GQACore
-    from khalamari_b200.request_page_table import GQAPageTableLayout
-    from khalamari_b200.selector import SelectorPolicy
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from khalamari_b200.device import Device, Dtype, PinnedArray, Stream
+    from khalamari_b200.gqa import GQAAttention, GQACore, HostPipeline
+    from khalamari_b200.request_page_table import GQAPageTableLayout
+    from khalamari_b200.selector import SelectorPolicy
+
+    rank, world, local = init_ranks(torch)
     spec = dict(WORKLOADS[args.workload])
     if args.batch:
         spec["batch"] = args.batch
@@ -246,13 +340,14 @@ def run_ours(args):
     kv_elem = spec.get("kv_elem", 2)
     contexts = contexts_for(spec, rank)
     q_len = spec["q_len"]
+    q_lens = [q_len] * len(contexts)
     device = Device(local)
     case = build_device_case(device, spec, contexts, torch, spec["seed"] + 1000 * rank)
     torch_stream = torch.cuda.current_stream()
     stream = Stream(device, torch_stream.cuda_stream)
     io_dtype = Dtype.Bfloat16 if spec["dtype"] == "bf16" else Dtype.Float16
     layout = GQAPageTableLayout(len(contexts), 1, case["num_blocks"], 1)
-    scale = 1.0 / float(np.sqrt(spec["d"]))
+    scale = spec.get("scale") or 1.0 / float(np.sqrt(spec["d"]))
     attention = GQAAttention(device, GQACore(spec["d"], spec["hq"], spec["hkv"], scale), io_dtype,
                              2 * spec["hkv"] * PAGE * spec["d"] * kv_elem, layout, len(contexts) * q_len,
                              SelectorPolicy.B200, kv_dtype=Dtype.Fp8E4M3FN if kv_elem == 1 else None)
@@ -286,25 +381,24 @@ def run_ours(args):
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches = 0
     sampler.__enter__()
-    if True:
-        # untimed ramp: keep the GPU under this load for about half a second so that clocks settle and the
-        # sampler sees them before the (short) timed region starts
-        ramp_end = time.perf_counter() + args.ramp_ms * 1e-3
-        while time.perf_counter() < ramp_end:
-            for _ in range(20):
-                step()
-            torch.cuda.synchronize()
-        barrier()
+    # untimed ramp: keep the GPU under this load for about half a second so that clocks settle and the
+    # sampler sees them before the (short) timed region starts
+    ramp_end = time.perf_counter() + args.ramp_ms * 1e-3
+    while time.perf_counter() < ramp_end:
+        for _ in range(20):
+            step()
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            events[i][0].record(torch_stream)
-            launches += step(lambda i=i: events[i][1].record(torch_stream))
-            events[i][2].record(torch_stream)
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        barrier()
-        timed_window = (t0, t1)
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        events[i][0].record(torch_stream)
+        launches += step(lambda i=i: events[i][1].record(torch_stream))
+        events[i][2].record(torch_stream)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    barrier()
+    timed_window = (t0, t1)
     device.check(stream)
     step_ms = [events[i][0].elapsed_time(events[i][2]) for i in range(args.steps)]
     if args.fused or attention.metadata.direct_output():
@@ -313,38 +407,55 @@ def run_ours(args):
         map_ms = [events[i][0].elapsed_time(events[i][1]) for i in range(args.steps)]
     total_ms = events[0][0].elapsed_time(events[-1][2])
     ms_per_step = total_ms / args.steps
+    device_out = case["out"].clone()
 
     # ---- end to end through the component seam with host buffers -------------------------------------
-    row_bytes = spec["hq"] * spec["d"] * 2
-    q_host = PinnedArray(len(contexts) * q_len * spec["hq"] * spec["d"], np.uint16)
-    out_host = PinnedArray(len(contexts) * q_len * spec["hq"] * spec["d"], np.uint16)
+    # Every step: Q from page-locked host memory to the device, the batch planned on the host (selector and
+    # metadata: nothing precomputed), the metadata block to the device, map + reduce, the output back to host
+    # memory. Two steps are in flight: a step's output copy runs beside the next step's kernels.
+    elems = len(contexts) * q_len * spec["hq"] * spec["d"]
+    q_host = PinnedArray(elems, np.uint16)
+    out_hosts = [PinnedArray(elems, np.uint16) for _ in range(2)]
     q_host.array[:] = case["q"].view(torch.int16).cpu().numpy().view(np.uint16)
-    e2e_steps = args.steps
-    h2d = d2h = 0
-    for _ in range(3):
-        attention.attend_host(stream, q_host, out_host, case["d_q"], case["d_out"], case["d_pool"], case["d_table"],
-                              req_slots, token_indices, cu_tokens, 0, selection)
-        stream.synchronize()
+    pipeline = HostPipeline(attention, stream)
+    partition = spec["partition"] or None
+
+    def submit(i):
+        return pipeline.submit(q_host, out_hosts[i % 2], case["d_pool"], case["d_table"], req_slots, token_indices,
+                               cu_tokens, 0, partition)
+
+    for i in range(4):
+        submit(i)
+    pipeline.drain()
     barrier()
     torch.cuda.synchronize()
+    e2e_steps = args.steps
+    h2d = d2h = 0
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        _, h2d, d2h = attention.attend_host(stream, q_host, out_host, case["d_q"], case["d_out"], case["d_pool"],
-                                            case["d_table"], req_slots, token_indices, cu_tokens, 0, selection)
-        stream.synchronize()
+    for i in range(e2e_steps):
+        _, _, h2d, d2h = submit(i)
+    pipeline.drain()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    checksum = float(np.abs(out_host.array.view(np.int16).astype(np.float32)).sum())
+    # one step alone, nothing else in flight: the latency a single caller sees
+    t0 = time.perf_counter()
+    ticket = submit(e2e_steps)[0]
+    pipeline.wait(ticket)
+    e2e_latency_s = time.perf_counter() - t0
+    last = out_hosts[e2e_steps % 2].array
+    checksum = float(np.abs(last.view(np.int16).astype(np.float32)).sum())
+    e2e_matches = bool(np.array_equal(last, device_out.view(torch.int16).cpu().numpy().view(np.uint16).reshape(-1)))
     device.check(stream)
     sampler.__exit__(None, None, None)
     clock_summary = sampler.summary(*timed_window)
 
     # ---- max over ranks ----------------------------------------------------------------------------
-    stats = torch.tensor([ms_per_step, e2e_s * 1e3, float(np.mean(map_ms))], device="cuda", dtype=torch.float64)
+    stats = torch.tensor([ms_per_step, e2e_s * 1e3, float(np.mean(map_ms)), e2e_latency_s * 1e3], device="cuda",
+                         dtype=torch.float64)
     totals = torch.tensor([float(kv_bytes), float(len(contexts) * q_len)], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(totals, op=dist.ReduceOp.SUM)
-    ms_per_step, e2e_ms, map_ms_mean = stats.tolist()
+    ms_per_step, e2e_ms, map_ms_mean, e2e_latency_ms = stats.tolist()
     total_kv_bytes, total_tokens = totals.tolist()
 
     result = None
@@ -357,11 +468,8 @@ def run_ours(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if spec["dtype"] == "bf16" else "f16",
             "data": "synthetic",
-            "config": {"workload": spec["label"], "batch_per_gpu": len(contexts), "q_len": q_len,
-                       "kv_tokens_per_gpu": int(sum(contexts)), "map_tasks": shape.num_sdpa_map_task_templates * spec["hkv"],
-                       "l2": "inputs (KV pages read per step) larger than L2; no flush" if kv_bytes > 126e6
-                       else "KV pages read per step fit L2: not an HBM measurement",
-                       "parallelism": f"dp{world} by request"},
+            "config": workload_config(spec, contexts, world),
+            "map_tasks": shape.num_sdpa_map_task_templates * spec["hkv"],
             "tokens_per_s": round(total_tokens / (ms_per_step * 1e-3), 1),
             "tflops": round(attention_flops(spec, contexts) / (ms_per_step * 1e-3) / 1e12, 2),
             "hbm_frac": round(value / world / peak, 4),
@@ -370,56 +478,85 @@ def run_ours(args):
                          "kernel": "sdpa_map_kernel", "kernel_ms": round(map_ms_mean, 5)},
             "e2e": {"value": round(total_kv_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 5),
-                    "tokens_per_s": round(total_tokens / (e2e_ms * 1e-3), 1)},
+                    "tokens_per_s": round(total_tokens / (e2e_ms * 1e-3), 1),
+                    "steps_in_flight": HostPipeline.SLOTS, "single_step_latency_ms": round(e2e_latency_ms, 5),
+                    "selector_in_timed_region": True, "output_equals_device_path": e2e_matches},
             "gpu_launches": launches,
             "clocks": clock_summary,
             "step_ms_min_median_max": [round(min(step_ms), 5), round(sorted(step_ms)[len(step_ms) // 2], 5),
                                        round(max(step_ms), 5)],
             "output_checksum": checksum,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if not args.no_parity:
+            sample = None
+            if q_len > 64:  # prefill chunks: first, middle and last new token of every sequence
+                sample = [[0, q_len // 2, q_len - 1] for _ in contexts]
+            parity, oracle_s = oracle_parity(spec, contexts, q_lens, case, output_f32(device_out, spec, torch), sample)
+            result["parity"] = parity
+            if world == 1 and sample is None and not args.no_cpu_baseline:
+                # the oracle pass of the parity check IS the CPU restatement on this very batch
+                result["cpu_baseline"] = {
+                    "value": round(kv_bytes / oracle_s / 1e9, 4), "unit": "GB/s", "cores": host_threads(),
+                    "kind": "port", "tokens_per_s": round(len(contexts) * q_len / oracle_s, 2),
+                    "sample": f"all {len(contexts)} requests of the bench batch (the stored Q/K/V of the GPU run), "
+                              f"one pass, {oracle_s:.2f} s"}
+        if world == 1 and "cpu_baseline" not in result and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(spec, contexts, sample_requests=len(contexts))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    return result
+    del pipeline
+    return result, dict(device=device, stream=stream, torch_stream=torch_stream)
 
 
-def run_split_sequence(args):
-    """Workload c4: ONE long sequence whose pages are split in token order over the ranks (strong scaling). A step
-    is: local split-KV map, local merge into this rank's record, all-gather of the records (NCCL), merge of the
-    gathered records on every rank. Without --context the sequence holds 1,048,576 tokens."""
-    import torch
+def measure_split_sequence(args, torch, context, rank, world, local, device, stream, torch_stream, steps,
+                           partition=None, check_parity=True):
+    """ONE long sequence whose pages are split in token order over the ranks. A step is: local split-KV map, local
+    merge into this rank's record, all-gather of the records (NCCL), merge of the gathered records on every rank.
+    Measures the step, the local part alone (map + local merge) and, on rank 0, the same sequence on one GPU (the
+    denominator of the scaling efficiency). Returns a dict on rank 0."""
     import torch.distributed as dist
 
     from khalamari_b200 import split_kv
-    from khalamari_b200.device import Device, Dtype, Stream
+    from khalamari_b200.device import Dtype
     from khalamari_b200.gqa import GQAAttention, GQACore
     from khalamari_b200.request_page_table import GQAPageTableLayout
     from khalamari_b200.selector import SelectorPolicy
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     spec = dict(WORKLOADS["c4"])
-    context = args.context or spec["contexts"][0]
+    hq, hkv, d = spec["hq"], spec["hkv"], spec["d"]
+    scale = 1.0 / 16.0
+
+    def build(local_len, seed, ranks):
+        case = build_device_case(device, spec, [max(local_len, 1)], torch, seed)
+        layout = GQAPageTableLayout(1, 1, case["num_blocks"], 1)
+        attention = GQAAttention(device, GQACore(d, hq, hkv, scale), Dtype.Bfloat16, 2 * hkv * PAGE * d * 2, layout, 1,
+                                 SelectorPolicy.B200)
+        decode = split_kv.SplitKvDecode(device, attention, ranks)
+        decode.prepare(0, local_len, partition)
+        return case, attention, decode
+
+    def timed(fn, count):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        first = torch.cuda.Event(enable_timing=True)
+        last = torch.cuda.Event(enable_timing=True)
+        first.record(torch_stream)
+        n = 0
+        for _ in range(count):
+            n += fn() or 0
+        last.record(torch_stream)
+        torch.cuda.synchronize()
+        return first.elapsed_time(last) / count, n
+
     begin, end = split_kv.split_context(context, world, PAGE)[rank]
     local_len = end - begin
-    device = Device(local)
-    case = build_device_case(device, spec, [max(local_len, 1)], torch, spec["seed"] + 1000 * rank)
-    torch_stream = torch.cuda.current_stream()
-    stream = Stream(device, torch_stream.cuda_stream)
-    layout = GQAPageTableLayout(1, 1, case["num_blocks"], 1)
-    attention = GQAAttention(device, GQACore(spec["d"], spec["hq"], spec["hkv"], 1.0 / 16.0), Dtype.Bfloat16,
-                             2 * spec["hkv"] * PAGE * spec["d"] * 2, layout, 1, SelectorPolicy.B200)
-    decode = split_kv.SplitKvDecode(device, attention, world)
-    decode.prepare(0, local_len, args.partition if args.partition > 0 else None)
-    kv_bytes_local = local_len * 2 * spec["hkv"] * spec["d"] * 2
+    # every rank draws the SAME Q row (seed without the rank) and its own K/V pages
+    case, attention, decode = build(local_len, spec["seed"] + 1000 * rank, world)
+    q_shared = torch.randn(hq * d, generator=torch.Generator(device="cuda").manual_seed(spec["seed"]), device="cuda",
+                           dtype=torch.float32).to(torch.bfloat16)
+    case["q"].copy_(q_shared)
 
     def step():
         return decode.record_step(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
@@ -427,81 +564,127 @@ def run_split_sequence(args):
     def local_only():
         return decode.record_local(stream, case["d_q"], case["d_pool"], case["d_table"], 0)
 
-    for _ in range(max(args.warmup, 3)):
+    ramp = max(int(args.ramp_ms), 1) if world > 1 else max(int(args.ramp_ms), 1)
+    for _ in range(min(ramp, 400)):  # a count, not a time limit: every rank must run the same number of collectives
         step()
     torch.cuda.synchronize()
+    step_ms, launches = timed(step, steps)
+    local_ms, _ = timed(local_only, steps)
     device.check(stream)
+    stats = torch.tensor([step_ms, local_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    step_ms, local_ms = stats.tolist()
+
+    # ---- parity: every rank restates its own slice on the CPU as one partial (m, l, o) per head, rank 0 merges the
+    # partials with the reducer's formula and compares the GPU result
+    parity = None
+    if check_parity:
+        import oracle
+        from concurrent.futures import ThreadPoolExecutor
+        q = case["q"].float().cpu().numpy().reshape(hq, d)
+        partials = None
+        if local_len > 0:
+            pool = case["pool"].view(torch.uint8).cpu().numpy()
+            layout_o = oracle.PageTableLayout(1, 1, case["num_blocks"], 1)
+            k_u8, v_u8 = oracle.gather_paged(pool, case["table"].reshape(-1), layout_o, 0, 0, PAGE, hkv, d, 2, local_len)
+            k = oracle.bf16_bits_to_f32(k_u8.view(np.uint16)).reshape(local_len, hkv, d)
+            v = oracle.bf16_bits_to_f32(v_u8.view(np.uint16)).reshape(local_len, hkv, d)
+            with ThreadPoolExecutor(min(hq, host_threads())) as workers:
+                partials = list(workers.map(
+                    lambda h: oracle.partial_row(q[h], k, v, 0, local_len, hkv, d, h // (hq // hkv), scale), range(hq)))
+        gathered = [partials]
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, partials)
+        if rank == 0:
+            expected = np.zeros((hq, d), np.float32)
+            for h in range(hq):
+                rows = [g[h] for g in gathered if g is not None]
+                expected[h] = oracle.merge_partials([r[1] for r in rows], [r[2] for r in rows],
+                                                    np.stack([r[0] for r in rows]))[0]
+            actual = case["out"].float().cpu().numpy().reshape(hq, d)
+            err = np.abs(actual - expected)
+            ok = (err <= 2e-3) | (err <= 1e-2 * np.abs(expected))
+            parity = {"max_abs": float(err.max()), "rows_checked": hq, "pass": bool(ok.all()),
+                      "rule": "per element |a-b| <= 2e-3 or |a-b| <= 1e-2*|b|; oracle partial per rank over its own "
+                              "pages, merged with the reducer's formula"}
+
+    # ---- the same sequence on one GPU (rank 0 only), for the efficiency
+    single_ms = step_ms
+    if world > 1:
+        del case, attention, decode
+        torch.cuda.empty_cache()
+        if rank == 0:
+            case1, attention1, decode1 = build(context, spec["seed"], 1)
+            fn = lambda: decode1.record_step(stream, case1["d_q"], case1["d_pool"], case1["d_table"], case1["d_out"], 0)
+            for _ in range(50):
+                fn()
+            first = torch.cuda.Event(enable_timing=True)
+            last = torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            first.record(torch_stream)
+            for _ in range(steps):
+                fn()
+            last.record(torch_stream)
+            torch.cuda.synchronize()
+            single_ms = first.elapsed_time(last) / steps
+            del case1, attention1, decode1
+            torch.cuda.empty_cache()
+        dist.barrier()
+    if rank != 0:
+        return None
+    total_bytes = context * 2 * hkv * d * 2
+    return {"context_tokens": context, "tokens_per_gpu": local_len, "ms_per_step": round(step_ms, 5),
+            "local_kernel_ms": round(local_ms, 5), "exchange_ms": round(step_ms - local_ms, 5),
+            "kv_gbs_total": round(total_bytes / (step_ms * 1e-3) / 1e9, 1),
+            "kv_gbs_per_gpu_local": round(local_len * 2 * hkv * d * 2 / (local_ms * 1e-3) / 1e9, 1),
+            "one_gpu_ms_per_step": round(single_ms, 5),
+            "efficiency_vs_one_gpu": round(single_ms / (world * step_ms), 4), "gpu_launches_per_step": launches // steps,
+            "parity": parity}
+
+
+def run_split_sequence(args):
+    """Workload c4 alone: the JSON line of one context length (``--context``, default 1,048,576 tokens)."""
+    import torch
+    import torch.distributed as dist
+
+    from khalamari_b200 import split_kv
+    from khalamari_b200.device import Device, Stream
+
+    rank, world, local = init_ranks(torch)
+    spec = dict(WORKLOADS["c4"])
+    context = args.context or spec["contexts"][0]
+    device = Device(local)
+    torch_stream = torch.cuda.current_stream()
+    stream = Stream(device, torch_stream.cuda_stream)
     props = torch.cuda.get_device_properties(local)
     sampler = ClockSampler(str(getattr(props, "uuid", "")) or None, local)
     sampler.__enter__()
-    # untimed load so that clocks settle. Every step holds a collective, so all ranks must run the SAME number
-    # of steps: a count, not a time limit (about args.ramp_ms at 0.5 ms per step).
-    for _ in range(int(args.ramp_ms * 2)):
-        step()
-    torch.cuda.synchronize()
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
-    launches = 0
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        events[i][0].record(torch_stream)
-        launches += step()
-        events[i][1].record(torch_stream)
-    torch.cuda.synchronize()
+    m = measure_split_sequence(args, torch, context, rank, world, local, device, stream, torch_stream, args.steps,
+                               args.partition if args.partition > 0 else None, not args.no_parity)
     t1 = time.perf_counter()
-    if world > 1:
-        dist.barrier()
-    step_ms = [a.elapsed_time(b) for a, b in events]
-    ms_per_step = events[0][0].elapsed_time(events[-1][1]) / args.steps
-    # the local part alone (map + local merge), to separate kernel time from the exchange
-    local_events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
-    for i in range(args.steps):
-        local_events[i][0].record(torch_stream)
-        local_only()
-        local_events[i][1].record(torch_stream)
-    torch.cuda.synchronize()
-    local_ms = float(np.mean([a.elapsed_time(b) for a, b in local_events]))
-    device.check(stream)
     sampler.__exit__(None, None, None)
-    clock_summary = sampler.summary(t0, t1)
-    checksum = float(case["out"].float().abs().sum().item())
-    stats = torch.tensor([ms_per_step, local_ms], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms_per_step, local_ms = stats.tolist()
-    result = None
-    if rank == 0:
-        peak, peak_kind = load_peaks()
-        total_bytes = context * 2 * spec["hkv"] * spec["d"] * 2
-        value = total_bytes / (ms_per_step * 1e-3) / 1e9
-        achieved = kv_bytes_local / (local_ms * 1e-3) / 1e9
-        record_bytes = split_kv.record_floats(spec["hq"], spec["d"]) * 4
-        result = {
-            "metric": "GQA decode KV-read GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": spec["label"], "context_tokens": context, "tokens_per_gpu": local_len,
-                       "map_tasks": attention.metadata.replay_shape().num_sdpa_map_task_templates * spec["hkv"],
-                       "l2": "inputs (KV pages read per step) larger than L2; no flush" if kv_bytes_local > 126e6
-                       else "per-GPU KV pages fit L2: not an HBM measurement",
-                       "parallelism": f"split-KV over {world} GPUs, all-gather of {record_bytes} B per rank"},
-            "tokens_per_s": round(1.0 / (ms_per_step * 1e-3), 1),
-            "hbm_frac": round(value / world / peak, 4),
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"of {peak_kind}",
-                         "kernel": "sdpa_map_kernel + local merge (rank 0)", "kernel_ms": round(local_ms, 5)},
-            "exchange_ms": round(ms_per_step - local_ms, 5),
-            "gpu_launches": launches, "clocks": clock_summary,
-            "step_ms_min_median_max": [round(min(step_ms), 5), round(sorted(step_ms)[len(step_ms) // 2], 5),
-                                       round(max(step_ms), 5)],
-            "output_checksum": checksum,
-        }
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    return result
+    if rank != 0:
+        return None
+    peak, peak_kind = load_peaks()
+    record_bytes = split_kv.record_floats(spec["hq"], spec["d"]) * 4
+    return {
+        "metric": "GQA decode KV-read GB/s", "value": m["kv_gbs_total"], "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": 3, "ms_per_step": m["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": spec["label"], "context_tokens": context, "tokens_per_gpu": m["tokens_per_gpu"],
+                   "l2": "inputs (KV pages read per step) larger than L2; no flush"
+                   if m["tokens_per_gpu"] * 2048 > 126e6 else "per-GPU KV pages fit L2: not an HBM measurement",
+                   "parallelism": f"split-KV over {world} GPUs, all-gather of {record_bytes} B per rank"},
+        "tokens_per_s": round(1.0 / (m["ms_per_step"] * 1e-3), 1), "hbm_frac": round(m["kv_gbs_total"] / world / peak, 4),
+        "roofline": {"bound": "hbm", "achieved": m["kv_gbs_per_gpu_local"], "peak": peak, "unit": "GB/s",
+                     "frac": round(m["kv_gbs_per_gpu_local"] / peak, 4), "traffic": None, "peak_source": f"of {peak_kind}",
+                     "kernel": "sdpa_map_kernel + local merge (slowest rank)", "kernel_ms": m["local_kernel_ms"]},
+        "split_kv": [m], "gpu_launches": m["gpu_launches_per_step"] * args.steps,
+        "clocks": sampler.summary(t0, t1), "parity": m["parity"],
+    }
 
 
 def cpu_inputs(spec, contexts, sample_requests, seed):
@@ -527,23 +710,28 @@ def host_threads():
 def cpu_pass(spec, inputs, threads):
     import oracle
     cu, ti, q, ks, vs = inputs
-    scale = 1.0 / float(np.sqrt(spec["d"]))
+    scale = spec.get("scale") or 1.0 / float(np.sqrt(spec["d"]))
     t0 = time.perf_counter()
     oracle.projected_gqa(cu, ti, q, ks, vs, spec["d"], spec["hq"], spec["hkv"], scale, threads)
     return time.perf_counter() - t0
 
 
+def bounded_sample(spec, contexts, threads, passes):
+    """How many of the batch's requests one CPU pass takes so that `passes` passes stay near two minutes: the whole
+    batch when that fits (about 1.1 GFLOP/s per thread for the scalar restatement), else a prefix, halved until
+    it does."""
+    sample = len(contexts)
+    rate = 1.1e9 * threads
+    while sample > 1 and attention_flops(spec, contexts[:sample]) / rate * passes > 120.0:
+        sample //= 2
+    return sample
+
+
 def cpu_baseline(spec, contexts, sample_requests):
     """The CPU restatement of the reference's GQA SDPA (oracle/, kind "port") on the host cores, contiguous
     per-request K/V as the reference's CPU path takes them, one pass over a bounded sample."""
-    import oracle
     threads = host_threads()
-    # keep the sample near 10-30 s of CPU work: about 0.4 core-seconds per 4.6k-token Hq64/D128 request
-    work = sum(contexts[:sample_requests]) * spec["hq"] * spec["d"] * spec["q_len"]
-    budget = 2.0e11 * threads / 8
-    while sample_requests > 1 and work > budget:
-        sample_requests //= 2
-        work = sum(contexts[:sample_requests]) * spec["hq"] * spec["d"] * spec["q_len"]
+    sample_requests = min(sample_requests, bounded_sample(spec, contexts, threads, 6))
     inputs = cpu_inputs(spec, contexts, sample_requests, spec["seed"])
     seconds = cpu_pass(spec, inputs, threads)
     sample_bytes = sum(contexts[:sample_requests]) * 2 * spec["hkv"] * spec["d"] * 2
@@ -554,30 +742,33 @@ def cpu_baseline(spec, contexts, sample_requests):
 
 def run_reference(args):
     """The reference arm: the reference's own CPU implementation of the path. The reference is Rust and
-    cannot be built in this image, so this times its C restatement (oracle/) on all host threads."""
+    cannot be built in this image, so this times its C restatement (oracle/) on all host threads: the whole batch
+    of the workload per step when `steps + warmup` passes fit about two minutes, else a prefix of it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
-    import oracle
-    spec = WORKLOADS[args.workload]
+    spec = dict(WORKLOADS[args.workload])
     contexts = contexts_for(spec, 0)
     threads = host_threads()
-    sample = max(1, min(len(contexts), 8))
+    warmup = max(args.warmup, 0)
+    sample = bounded_sample(spec, contexts, threads, args.steps + warmup)
     inputs = cpu_inputs(spec, contexts, sample, spec["seed"])
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(warmup):
         cpu_pass(spec, inputs, threads)
     times = [cpu_pass(spec, inputs, threads) for _ in range(args.steps)]
     seconds = float(np.mean(times))
     sample_bytes = sum(contexts[:sample]) * 2 * spec["hkv"] * spec["d"] * 2
     value = round(sample_bytes / seconds / 1e9, 4)
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    described = (f"all {sample} requests of the batch per step" if sample == len(contexts)
+                 else f"first {sample} of {len(contexts)} requests per step")
     return {
         "impl": "reference", "metric": "GQA decode KV-read GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": round(seconds * 1e3, 3),
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(seconds * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": spec["label"], "sample": f"first {sample} of {len(contexts)} requests per step"},
+        "config": workload_config(spec, contexts, world),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": f"first {sample} of {len(contexts)} requests per step, {args.steps} steps"},
+                         "sample": f"{described}, {args.steps} steps"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "tokens_per_s": round(sample * spec["q_len"] / seconds, 2),
@@ -592,6 +783,9 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-parity", action="store_true", help="skip the oracle check of the bench's own output")
+    parser.add_argument("--no-split-kv", action="store_true",
+                        help="default workload: skip the one-long-sequence measurements that follow the headline")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")
     parser.add_argument("--pool-pages", type=int, default=0, help="override the page pool size (profiling captures)")
     parser.add_argument("--partition", type=int, default=-1, help="override the split-KV partition (0: selector)")
@@ -608,10 +802,29 @@ def main():
         result = run_reference(args)
     elif args.workload == "c4":
         result = run_split_sequence(args)
+        finish_ranks()
     else:
-        result = run_ours(args)
+        import torch
+        result, ctx = run_ours(args)
+        if args.workload == "c2" and not args.no_split_kv and args.kv_dtype == "io" and not args.batch:
+            # after the headline: one long sequence split over the same ranks, at the three stated context lengths
+            rank, world, local = init_ranks(torch)
+            torch.cuda.empty_cache()
+            split = [measure_split_sequence(args, torch, context, rank, world, local, ctx["device"], ctx["stream"],
+                                            ctx["torch_stream"], args.steps, None, not args.no_parity)
+                     for context in SPLIT_CONTEXTS]
+            if result is not None:
+                result["split_kv"] = split
+        finish_ranks()
     if result is not None:
         print(json.dumps(result), flush=True)
+
+
+def finish_ranks():
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

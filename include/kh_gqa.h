@@ -109,6 +109,18 @@ KH_API kh_status kh_stream_write(kh_stream* stream, kh_buffer_ref buffer, uint64
 KH_API kh_status kh_stream_read(kh_stream* stream, kh_buffer_ref buffer, uint64_t offset, void* dst, uint64_t bytes);
 KH_API kh_status kh_host_alloc_pinned(uint64_t bytes, void** out);
 KH_API kh_status kh_host_free_pinned(void* ptr);
+/* Completion of one submission, the analogue of ReplaySubmission (BM/metal/stream/submission.rs:41-101): an event
+ * is recorded on a stream after the work it stands for; kh_event_synchronize blocks the host until that work is
+ * done (ReplaySubmission::wait, submission.rs:88), kh_stream_wait_event orders another stream of the same device
+ * after it without blocking the host (the recorded barrier of BM/metal/stream/dependency.rs:11-16 across two
+ * queues). With them a caller keeps two steps in flight: the output copy of one step runs on a second stream
+ * while the next step's kernels run on the first. */
+typedef struct kh_event kh_event;
+KH_API kh_status kh_event_create(kh_device* device, kh_event** out);
+KH_API kh_status kh_event_destroy(kh_event* event);
+KH_API kh_status kh_stream_record_event(kh_stream* stream, kh_event* event);
+KH_API kh_status kh_stream_wait_event(kh_stream* stream, kh_event* event);
+KH_API kh_status kh_event_synchronize(kh_event* event);
 
 /* ---- SDPA capability registry: BM/components/gqa/sdpa.rs ----------------------------------- */
 /* sdpa::Config (sdpa.rs:219-241). */
@@ -594,8 +606,15 @@ KH_API uint16_t kh_fp8_e4m3_to_bf16(uint8_t fp8_bits);
 /* ---- device status word: the analogue of SubmissionCheck (BM/metal/stream/check.rs:8-13) ---- */
 /* Reads (after synchronising the stream) and clears the sticky status the kernels of `device`
  * write: 0 = clean; bit 0 = a bounded wait inside a kernel ran out; bit 1 = a page id addressed
- * beyond the KV pool. Nonzero also returns KH_ABORTED. */
+ * beyond the KV pool (the copy or write was skipped); bit 2 = batch metadata named a request slot or a KV range
+ * beyond the page table (the task or token write was skipped). Nonzero also returns KH_ABORTED. */
 KH_API kh_status kh_device_check(kh_device* device, kh_stream* stream, uint32_t* out_status_word);
+/* Every wait inside a kernel (on a copy or on another warp) polls at most `polls` times, then the kernel sets
+ * bit 0 of the status word, lets its copies in flight land and returns. The default (2^24 polls, seconds) is far
+ * above any healthy wait; a watchdog-style caller, or a test of the abort path, lowers it. 0 restores the default.
+ * Applies to launches recorded after the call. No reference counterpart: Metal command buffers carry their own
+ * GPU timeout (surfaced by SubmissionCheck, BM/metal/stream/check.rs:8-13). */
+KH_API kh_status kh_device_set_wait_limit(kh_device* device, uint32_t polls);
 
 /* ---- cross-partition / cross-GPU LSE combine ------------------------------------------------ */
 /* Merges `num_partials` partial triples per (token, head) row with the partial-state merge of

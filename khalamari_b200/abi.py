@@ -6,6 +6,7 @@ The shared library is the product. If it is missing or cannot be loaded, importi
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from . import build as _build
@@ -197,6 +198,12 @@ PROTOTYPES = {
     "kh_stream_synchronize": [_vp],
     "kh_stream_write": [_vp, BufferRef, C.c_uint64, _vp, C.c_uint64],
     "kh_stream_read": [_vp, BufferRef, C.c_uint64, _vp, C.c_uint64],
+    "kh_event_create": [_vp, P(_vp)],
+    "kh_event_destroy": [_vp],
+    "kh_stream_record_event": [_vp, _vp],
+    "kh_stream_wait_event": [_vp, _vp],
+    "kh_event_synchronize": [_vp],
+    "kh_device_set_wait_limit": [_vp, _u32],
     "kh_host_alloc_pinned": [C.c_uint64, P(_vp)],
     "kh_host_free_pinned": [_vp],
     "kh_sdpa_config_validate": [P(SdpaConfig)],
@@ -268,14 +275,17 @@ _lib = None
 
 
 def library_path() -> Path:
-    return _build.LIBRARY
+    """The product library, or the measurement build (compiled with ``KH_GQA_MEASURE``: kernel parts can be
+    switched off through ``KH_GQA_DEBUG`` to time the others) when ``KH_GQA_LIBRARY=measure`` asks for it. The
+    product library itself reads no environment variable."""
+    return _build.MEASURE_LIBRARY if os.environ.get("KH_GQA_LIBRARY") == "measure" else _build.LIBRARY
 
 
 def lib() -> C.CDLL:
     """Loads ``libkhcuda_gqa.so`` (building it first when the sources are newer). Fails loudly."""
     global _lib
     if _lib is None:
-        path = _build.build()
+        path = _build.build(measure=library_path() == _build.MEASURE_LIBRARY)
         handle = C.CDLL(str(path))
         for name, argtypes in PROTOTYPES.items():
             fn = getattr(handle, name)  # AttributeError if the header and the library drift apart

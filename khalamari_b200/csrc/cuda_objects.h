@@ -9,7 +9,8 @@
 struct kh_device {
     int32_t ordinal;
     int32_t sm_count;
-    uint32_t* status;  // device status word
+    uint32_t* status;     // device status word
+    uint32_t wait_limit;  // polls a bounded wait inside a kernel makes before it gives up (kh_device_set_wait_limit)
 };
 
 struct kh_stream {
@@ -17,6 +18,11 @@ struct kh_stream {
     cudaStream_t stream;
     bool owned;
     kh_buffer_ref active_counts;  // bound by kh_stream_bind_active_counts: launches read their counts from it
+};
+
+struct kh_event {
+    kh_device* device;
+    cudaEvent_t event;
 };
 
 namespace kh {

@@ -90,6 +90,7 @@ struct PageWriteParams {
     uint32_t* status;
     uint32_t num_active_token_writes;
     uint32_t layer_index;
+    uint32_t num_req_slots;
     uint32_t num_gqa_layers;
     uint32_t num_blocks;
     uint32_t num_page_ids_per_block;
@@ -117,6 +118,10 @@ __global__ void __launch_bounds__(256) kv_page_write_kernel(const PageWriteParam
         const uint32_t token = p.flat_token_indices[write];
         const uint32_t block = token / (p.tokens_per_page * p.num_page_ids_per_block);
         const uint32_t id_in_block = (token / p.tokens_per_page) % p.num_page_ids_per_block;
+        if (slot >= p.num_req_slots || block >= p.num_blocks) {  // metadata that points past the page table
+            atomicOr(p.status, 4u);
+            continue;
+        }
         const uint64_t entry =
             ((uint64_t(slot) * p.num_gqa_layers + p.layer_index) * p.num_blocks + block) * p.num_page_ids_per_block +
             id_in_block;
@@ -169,6 +174,10 @@ __global__ void __launch_bounds__(256) kv_page_write_scalar_kernel(const PageWri
         const uint32_t token = p.flat_token_indices[write];
         const uint32_t block = token / (p.tokens_per_page * p.num_page_ids_per_block);
         const uint32_t id_in_block = (token / p.tokens_per_page) % p.num_page_ids_per_block;
+        if (slot >= p.num_req_slots || block >= p.num_blocks) {  // metadata that points past the page table
+            atomicOr(p.status, 4u);
+            continue;
+        }
         const uint64_t entry =
             ((uint64_t(slot) * p.num_gqa_layers + p.layer_index) * p.num_blocks + block) * p.num_page_ids_per_block +
             id_in_block;
@@ -290,6 +299,7 @@ kh_status kh_kv_page_write_invoke(kh_kv_page_write* compute, kh_stream* stream, 
         p.status = compute->device->status;
         p.num_active_token_writes = num_active_token_writes;
         p.layer_index = page_table_index;
+        p.num_req_slots = l.num_req_slots;
         p.num_gqa_layers = l.num_gqa_layers;
         p.num_blocks = l.num_blocks;
         p.num_page_ids_per_block = l.num_page_ids_per_block;

@@ -44,6 +44,7 @@ struct ReduceParams {
     uint32_t fixed_partials;
     uint64_t stat_stride;      // floats between consecutive partials of a row; 0: dense [partial][Hq][maxq]
     uint64_t out_stride;       // same for the partial outputs; 0: dense [partial][Hq][maxq][D]
+    uint32_t num_partials;     // partials the buffers hold: bounds what `cu` may name
     uint32_t heads_per_block;  // > 1 (one-token ranges only): a block serves this many consecutive heads
     const uint32_t* active;    // replay: device words {tokens, Q-token tiles, templates}; the counts above bound them
     uint32_t active_range_word; // which of the words counts this launch's ranges (0: tokens, 1: Q-token tiles)
@@ -93,8 +94,9 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
         if (head >= p.num_q_heads || threadIdx.x / slots >= p.heads_per_block) return;
         const uint32_t tok = p.q_ranges != nullptr ? p.q_ranges[range * 2] : range;
         if (tok >= num_active_tokens) return;
-        const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
-        const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
+        // `cu` comes from the caller's device memory: a stale entry must not reach past the partial buffers
+        const uint32_t last = min(p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials, p.num_partials);
+        const uint32_t first = min(p.cu != nullptr ? p.cu[range] : 0u, last);
         const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads);
         const uint64_t out_stride = p.out_stride != 0 ? p.out_stride : stride * D;
         const uint64_t first_index = uint64_t(first) * p.num_q_heads + head;
@@ -117,8 +119,8 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
     }
     if (tok_begin >= num_active_tokens || tok_end > num_active_tokens || tok_end <= tok_begin) return;
     const uint32_t num_toks = min(tok_end - tok_begin, p.max_q_tokens);
-    const uint32_t first = p.cu != nullptr ? p.cu[range] : 0u;
-    const uint32_t last = p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials;
+    const uint32_t last = min(p.cu != nullptr ? p.cu[range + 1] : p.fixed_partials, p.num_partials);
+    const uint32_t first = min(p.cu != nullptr ? p.cu[range] : 0u, last);
     const uint32_t D = p.head_dim;
     const uint64_t stride = p.stat_stride != 0 ? p.stat_stride : uint64_t(p.num_q_heads) * p.max_q_tokens;
     const uint64_t out_stride = p.out_stride != 0 ? p.out_stride : stride * D;
@@ -196,7 +198,7 @@ static MapInstance make_instance() {
 // MMAs. head_dim 256: a stage is 16 KV tokens (one page) and a thread carries a 16 x 256 f32 accumulator
 // (128 registers), so 4 consumer warps run with up to 255 registers each.
 // Tasks of more than 64 rows (prefill and long verify tiles) at head_dim 128 run on tcgen05 with tensor-memory
-// accumulators; KH_GQA_NO_TCGEN05 selects the warp-level instance instead (comparison runs).
+// accumulators (a library compiled with KH_GQA_MEASURE can be told to take the warp-level instance instead).
 template <typename T, int D, int P>
 static MapInstance make_tc_instance() {
     using G = TcGeometry<D, P>;
@@ -214,8 +216,11 @@ static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     if (rows <= 32) return make_instance<T, D, P, 2, 2, PS, false>();
     if (rows <= 64) return make_instance<T, D, P, 4, 1, PS, false>();
     if constexpr (D == 128 && P == 16) {
-        static const bool warp_level = std::getenv("KH_GQA_NO_TCGEN05") != nullptr;
-        if (tensor_memory && !warp_level) return make_tc_instance<T, D, P>();
+#ifdef KH_GQA_MEASURE
+        // measurement build only: compare against the warp-level instance
+        if (std::getenv("KH_GQA_NO_TCGEN05") != nullptr) tensor_memory = false;
+#endif
+        if (tensor_memory) return make_tc_instance<T, D, P>();
     }
     return make_instance<T, D, P, 8, 1, 1, false>();
 }
@@ -394,13 +399,18 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
     p.pages_per_request_layer = c.layout.num_blocks * c.layout.num_page_ids_per_block;
     p.pool_pages = static_cast<uint32_t>(std::min<uint64_t>(kv_pages.bytes / c.page_bytes, 0xffffffffull));
     p.scale_log2e = c.scale * 1.4426950408889634f;
-    // Measurement aid: KH_GQA_DEBUG=<bits> switches parts of the kernel off (see MapParams::debug) so that the
-    // paged TMA gather, the tensor-core math and the hand-offs can be timed separately.
-    static const uint32_t debug_bits = [] {
+    p.num_req_slots = c.layout.num_req_slots;
+    p.tokens_per_page = c.tokens_per_page;
+    p.wait_limit = c.device->wait_limit;
+#ifdef KH_GQA_MEASURE
+    // Measurement build only: KH_GQA_DEBUG=<bits> switches parts of the kernel off (see MapParams::debug) so that
+    // the paged TMA gather, the tensor-core math and the hand-offs can be timed separately. Read at every launch,
+    // so that one process can time several settings. The product library never reads the variable.
+    {
         const char* value = std::getenv("KH_GQA_DEBUG");
-        return value != nullptr ? uint32_t(std::atoi(value)) : 0u;
-    }();
-    p.debug = debug_bits;
+        p.debug = value != nullptr ? uint32_t(std::atoi(value)) : 0u;
+    }
+#endif
     if (num_templates == 0) return;
     const uint64_t tasks = uint64_t(num_templates) * c.num_kv_heads * p.head_ranges;
     KH_REQUIRE(tasks <= 0xffffffffull, "GQA SDPA map task count must fit u32");
@@ -580,6 +590,7 @@ kh_status kh_device_open(int32_t ordinal, kh_device** out) {
         auto device = std::make_unique<kh_device>();
         device->ordinal = ordinal;
         device->sm_count = prop.multiProcessorCount;
+        device->wait_limit = kDefaultWaitLimit;
         KH_CUDA(cudaMalloc(&device->status, sizeof(uint32_t)));
         KH_CUDA(cudaMemset(device->status, 0, sizeof(uint32_t)));
         *out = device.release();
@@ -741,6 +752,65 @@ kh_status kh_stream_read(kh_stream* stream, kh_buffer_ref buffer, uint64_t offse
     });
 }
 
+kh_status kh_event_create(kh_device* device, kh_event** out) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(out != nullptr, "null argument");
+        use_device(device);
+        auto event = std::make_unique<kh_event>();
+        event->device = device;
+        KH_CUDA(cudaEventCreateWithFlags(&event->event, cudaEventDisableTiming));
+        *out = event.release();
+        return KH_OK;
+    });
+}
+
+kh_status kh_event_destroy(kh_event* event) {
+    return guarded([&]() -> kh_status {
+        if (event == nullptr) return KH_OK;
+        cudaSetDevice(event->device->ordinal);
+        cudaEventDestroy(event->event);
+        delete event;
+        return KH_OK;
+    });
+}
+
+kh_status kh_stream_record_event(kh_stream* stream, kh_event* event) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(stream && event, "null argument");
+        KH_REQUIRE(stream->device == event->device, "event does not belong to the stream's device");
+        use_device(stream->device);
+        KH_CUDA(cudaEventRecord(event->event, stream->stream));
+        return KH_OK;
+    });
+}
+
+kh_status kh_stream_wait_event(kh_stream* stream, kh_event* event) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(stream && event, "null argument");
+        KH_REQUIRE(stream->device == event->device, "event does not belong to the stream's device");
+        use_device(stream->device);
+        KH_CUDA(cudaStreamWaitEvent(stream->stream, event->event, 0));
+        return KH_OK;
+    });
+}
+
+kh_status kh_event_synchronize(kh_event* event) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(event != nullptr, "null argument");
+        use_device(event->device);
+        KH_CUDA(cudaEventSynchronize(event->event));
+        return KH_OK;
+    });
+}
+
+kh_status kh_device_set_wait_limit(kh_device* device, uint32_t polls) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(device != nullptr, "null argument");
+        device->wait_limit = polls != 0 ? polls : kDefaultWaitLimit;
+        return KH_OK;
+    });
+}
+
 kh_status kh_host_alloc_pinned(uint64_t bytes, void** out) {
     return guarded([&]() -> kh_status {
         KH_REQUIRE(out != nullptr && bytes > 0, "invalid pinned allocation request");
@@ -766,9 +836,11 @@ kh_status kh_device_check(kh_device* device, kh_stream* stream, uint32_t* out_st
         if (word != 0) KH_CUDA(cudaMemset(device->status, 0, sizeof(word)));
         if (out_status_word) *out_status_word = word;
         if (word != 0) {
-            return fail(KH_ABORTED, "device status word 0x%x:%s%s", word,
+            return fail(KH_ABORTED, "device status word 0x%x:%s%s%s", word,
                         (word & kStatusWaitExpired) ? " a bounded wait inside a kernel ran out;" : "",
-                        (word & kStatusPageOutOfPool) ? " a page id addressed beyond the KV pool;" : "");
+                        (word & kStatusPageOutOfPool) ? " a page id addressed beyond the KV pool;" : "",
+                        (word & kStatusMetadataOutOfRange)
+                            ? " batch metadata named a request slot or KV range beyond the page table;" : "");
         }
         return KH_OK;
     });
@@ -995,6 +1067,7 @@ kh_status kh_sliced_kv_reduce(kh_sliced_kv* compute, kh_stream* stream, const kh
         p.max_q_tokens = 1;
         p.num_active_ranges = num_active_tokens;
         p.num_active_tokens = num_active_tokens;
+        p.num_partials = s.num_total_sdpa_map_task_templates;
         p.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
         p.active_range_word = 0;
         launch_reduce(compute->config.dtype, p, num_active_tokens, stream->stream);
@@ -1204,6 +1277,7 @@ kh_status kh_sliced_q_reduce(kh_sliced_q* compute, kh_stream* stream, const kh_s
         p.max_q_tokens = compute->common.variant.max_q_tokens;
         p.num_active_ranges = num_active_q_token_tiles;
         p.num_active_tokens = s.num_total_tokens;
+        p.num_partials = s.num_total_sdpa_map_task_templates;
         p.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
         p.active_range_word = 1;
         launch_reduce(compute->config.dtype, p, num_active_q_token_tiles, stream->stream);
@@ -1240,6 +1314,7 @@ kh_status kh_combine_partials(kh_device* device, kh_stream* stream, uint32_t num
         p.q_ranges = nullptr;
         p.cu = nullptr;
         p.fixed_partials = num_partials;
+        p.num_partials = num_partials;
         p.out = output.ptr;
         p.out_sum = chain ? static_cast<float*>(out_exp_sums.ptr) : nullptr;
         p.out_max = chain ? static_cast<float*>(out_max_logits.ptr) : nullptr;
@@ -1274,6 +1349,7 @@ kh_status kh_combine_packed_partials(kh_device* device, kh_stream* stream, uint3
         p.partial_max = base + num_rows;
         p.partial_out = base + 2 * uint64_t(num_rows);
         p.fixed_partials = num_partials;
+        p.num_partials = num_partials;
         p.stat_stride = record;
         p.out_stride = record;
         p.out = output.ptr;
@@ -1399,6 +1475,7 @@ kh_status kh_sliced_kv_attend_static(kh_sliced_kv* compute, kh_stream* stream,
         r.max_q_tokens = 1;
         r.num_active_ranges = num_active_tokens;
         r.num_active_tokens = num_active_tokens;
+        r.num_partials = num_active_kv_splits;  // the sections of the shared array are sized for exactly these
         r.active = static_cast<const uint32_t*>(stream->active_counts.ptr);
         r.active_range_word = 0;
         launch_reduce(config.dtype, r, num_active_tokens, stream->stream);

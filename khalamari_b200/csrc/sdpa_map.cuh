@@ -69,7 +69,11 @@ struct MapParams {
     // word triple when the kernel runs (a captured launch replays with new counts); num_active_tokens,
     // num_active_q_tiles and num_templates are then the recorded capacities and only bound the values read.
     const uint32_t* active;
-    // Measurement aid (KH_GQA_DEBUG, 0 in normal use; outputs are meaningless when set). Bits: 1 consumers release
+    uint32_t num_req_slots;           // request slots of the page table (bounds the slots the metadata names)
+    uint32_t tokens_per_page;
+    uint32_t wait_limit;              // polls a bounded wait makes before it gives up (kDefaultWaitLimit)
+    // Measurement aid. Only a library compiled with KH_GQA_MEASURE reads these bits (debug_bits() below); the
+    // product build compiles every test of them away. Outputs are meaningless when set. Bits: 1 consumers release
     // every stage without computing; 2 skip the task-end merge and publish; 4 skip the Q copies; 8 issue no K/V
     // copies (consumers run on stale shared memory); 16 / 32 / 64 skip QK / softmax / PV; 128 never run the
     // in-kernel group merge; 256 do not count arrivals; 512 visit tasks template-major and never carry the running
@@ -80,7 +84,14 @@ struct MapParams {
 
 constexpr uint32_t kStatusWaitExpired = 1u;
 constexpr uint32_t kStatusPageOutOfPool = 2u;
-constexpr uint32_t kWaitLimit = 1u << 24;
+constexpr uint32_t kStatusMetadataOutOfRange = 4u;  // a request slot or KV range beyond the page table
+constexpr uint32_t kDefaultWaitLimit = 1u << 24;
+
+#ifdef KH_GQA_MEASURE
+__device__ __forceinline__ uint32_t debug_bits(const MapParams& p) { return p.debug; }
+#else
+__device__ __forceinline__ constexpr uint32_t debug_bits(const MapParams&) { return 0u; }
+#endif
 constexpr int kMaxPidsPerSegment = 160;  // page ids staged per task segment (2048 tokens of 16 + slack)
 constexpr uint32_t kBalanceMaxTemplates = 16384;  // above this, tasks are dealt round-robin (many tasks per CTA anyway)
 constexpr uint32_t kTaskOverheadTokens = 48;      // fixed cost of a task, in KV tokens of streaming time
@@ -125,14 +136,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // wait returns at once and the kernel runs to its end without touching the rings again; the host
 // reads the sticky status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status) {
+                                          const MapParams& p) {
     if (mbar_try_wait(bar, parity)) return true;  // common case: no shared-memory flag read on the way
     if (*abort_flag) return false;
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    for (uint32_t i = 0; i < p.wait_limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     *abort_flag = 1;
-    atomicOr(status, kStatusWaitExpired);
+    atomicOr(p.status, kStatusWaitExpired);
     return false;
 }
 
@@ -520,6 +531,14 @@ __device__ __forceinline__ TaskInfo decode_task(const MapParams& p, const Active
     t.kv_begin = p.templates[t.tmpl * 3 + 1];
     t.kv_end = p.templates[t.tmpl * 3 + 2];
     t.req_slot = p.req_slots[t.tok_begin];
+    // The slot and the KV range index the page table: metadata that points past it (a stale or padded entry) must
+    // not become an address. The task is dropped and the status word says so; its partial keeps whatever it held.
+    if (t.req_slot >= p.num_req_slots ||
+        (t.kv_end > t.kv_begin &&
+         (uint64_t(t.kv_end) + p.tokens_per_page - 1) / p.tokens_per_page > p.pages_per_request_layer)) {
+        atomicOr(p.status, kStatusMetadataOutOfRange);
+        return t;
+    }
     if (p.cu != nullptr) {
         t.part_begin = p.cu[q_range];
         t.part_count = p.cu[q_range + 1] - t.part_begin;
@@ -639,7 +658,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     // are consecutive KV slices of the same Q rows, so the consumers can carry their running state from one
     // task into the next instead of merging and publishing at every slice boundary.
     const uint32_t cells = p.num_kv_heads * p.head_ranges;
-    const bool by_cell = c.allow_carry && balanced && cells <= 64 && task_limit > task_base && (p.debug & 512) == 0;
+    const bool by_cell = c.allow_carry && balanced && cells <= 64 && task_limit > task_base && (debug_bits(p) & 512) == 0;
     const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
     const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
     auto visit_to_task = [&](uint64_t visit) -> uint64_t {
@@ -689,7 +708,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
             const uint32_t slot = pushed % TQ;
             const uint32_t phase = (pushed / TQ) & 1;
             // the slot is free once the consumers AND the stream warp are done with the task it held
-            if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) aborted = true;
+            if (!mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p)) aborted = true;
             if (!aborted) {
                 TaskSlot* ts = task_ring + slot;
                 const uint32_t first_page = tile_begin / P;
@@ -732,7 +751,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
                     }
                 }
                 if (p.visible != nullptr) mbar_arrive_after_cp_async(task_full_bar + 8 * slot);
-                const uint32_t q_boxes = (p.debug & 4) ? 0u : cur.num_toks * NH;
+                const uint32_t q_boxes = (debug_bits(p) & 4) ? 0u : cur.num_toks * NH;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(task_full_bar + 8 * slot, q_boxes * p.heads_per_task * 128);
                 }
@@ -765,7 +784,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     if (!aborted) {
         const uint32_t slot = pushed % TQ;
         const uint32_t phase = (pushed / TQ) & 1;
-        if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p.status)) {
+        if (mbar_wait(task_empty_bar + 8 * slot, phase ^ 1, abort_flag, p)) {
             if (lane == 0) {
                 task_ring[slot].done = 1;
                 mbar_arrive_expect_tx(task_full_bar + 8 * slot, 0);
@@ -778,7 +797,7 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     if (*abort_flag) {
         for (uint32_t back = 0; back < uint32_t(TQ) && back < pushed; ++back) {
             const uint32_t c = pushed - 1 - back;
-            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+            for (uint32_t i = 0; i < p.wait_limit; ++i) {
                 if (mbar_try_wait(task_full_bar + 8 * (c % TQ), (c / TQ) & 1)) break;
             }
         }
@@ -815,7 +834,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
     const uint64_t kv_policy = l2_evict_first_policy();
     for (uint32_t taken = 0; !aborted; ++taken) {
         const uint32_t tslot = taken % TQ;
-        if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+        if (!mbar_wait(stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) break;
         const TaskSlot* ts = task_ring + tslot;
         if (ts->done) break;
         const uint32_t tile_begin = ts->tile_begin, num_tiles = ts->num_tiles, kv_end = ts->kv_end;
@@ -851,18 +870,21 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
                     uint32_t page_in_seg = lane * (ST / P);
                     for (uint32_t tile = lane; tile < seg_tiles; tile += L) {
                         const uint32_t bar = full_bar + 8 * slot;
-                        if (!mbar_wait(empty_bar + 8 * slot, parity, abort_flag, p.status)) {
+                        if (!mbar_wait(empty_bar + 8 * slot, parity, abort_flag, p)) {
                             failed = tile + 1;
                             break;
                         }
                         const uint32_t dst = smem_addr(ring) + slot * G::kStageBytes;
-                        if (tile_tok + ST <= kv_end && !(p.debug & 8)) {
+                        // measurement build only: the bytes of a task's first stage are announced and never copied
+                        const bool withhold = (debug_bits(p) & 8192) != 0 && seg_tile + tile == 0;
+                        if (tile_tok + ST <= kv_end && !(debug_bits(p) & 8)) {
                             mbar_arrive_expect_tx(bar, G::kStageBytes);
 #pragma unroll
                             for (int b = 0; b < G::kBoxesPerPlane; ++b) {
                                 const uint32_t tok_in_page = (b * G::kBoxRows) % P;
                                 const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
                                 if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                if (withhold) continue;
                                 tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
                                             static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0, bar, kv_policy);
                             }
@@ -874,7 +896,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
                             for (int b = 0; b < G::kBoxesPerPlane; ++b) {
                                 if (tile_tok + b * G::kBoxRows < kv_end) ++boxes_needed;
                             }
-                            if (p.debug & 8) boxes_needed = 0;
+                            if (debug_bits(p) & 8) boxes_needed = 0;
                             mbar_arrive_expect_tx(bar, boxes_needed * G::kCopyBytes);
 #pragma unroll
                             for (int b = 0; b < G::kBoxesPerPlane; ++b) {
@@ -882,6 +904,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
                                     const uint32_t tok_in_page = (b * G::kBoxRows) % P;
                                     const uint32_t pid = pids[page_in_seg + (b * G::kBoxRows) / P];
                                     if (pid >= p.pool_pages) atomicOr(p.status, kStatusPageOutOfPool);
+                                    if (withhold) continue;
                                     tma_load_4d(dst + b * G::kCopyBytes, &kv_map, 0,
                                                 static_cast<int32_t>(pid * rows_per_page + head_row + tok_in_page), 0, 0,
                                                 bar, kv_policy);
@@ -921,7 +944,7 @@ __device__ __forceinline__ void run_stream_warp(const MapParams& p, const CUtens
     if (*abort_flag) {
         for (uint32_t back = 0; back < uint32_t(NS) && back < stage_counter; ++back) {
             const uint32_t c = stage_counter - 1 - back;
-            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+            for (uint32_t i = 0; i < p.wait_limit; ++i) {
                 if (mbar_try_wait(full_bar + 8 * (c % NS), (c / NS) & 1)) break;
             }
         }
@@ -1006,7 +1029,7 @@ __device__ __forceinline__ void run_decode_warps(const MapParams& p, const Produ
     uint32_t stage_base = 0;  // running number of the task's first stage
     for (uint32_t taken = 0;; ++taken) {
         const uint32_t tslot = taken % TQ;
-        if (!mbar_wait(c.stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) return;
+        if (!mbar_wait(c.stream_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) return;
         const TaskSlot* ts = c.task_ring + tslot;
         const uint32_t done = ts->done, num_tiles = ts->num_tiles;
         __syncwarp();
@@ -1015,8 +1038,8 @@ __device__ __forceinline__ void run_decode_warps(const MapParams& p, const Produ
         uint32_t stage = stage_base + (dw + DW - stage_base % DW) % DW;  // this warp's first stage of the task
         for (; stage < stage_base + num_tiles; stage += DW) {
             const uint32_t rslot = stage % NR, sslot = stage % NS;
-            if (!mbar_wait(c.full_bar + 8 * rslot, (stage / NR) & 1, abort_flag, p.status)) return;
-            if (!mbar_wait(stage_empty_bar + 8 * sslot, ((stage / NS) & 1) ^ 1, abort_flag, p.status)) return;
+            if (!mbar_wait(c.full_bar + 8 * rslot, (stage / NR) & 1, abort_flag, p)) return;
+            if (!mbar_wait(stage_empty_bar + 8 * sslot, ((stage / NS) & 1) ^ 1, abort_flag, p)) return;
             const uint32_t raw = smem_addr(c.ring + rslot * R::kStageBytes) + raw_lane;
             const uint32_t out = smem_addr(stage_ring + sslot * G::kStageBytes);
             // The common pass has no branches (the loads, conversions and stores of the 16 units interleave
@@ -1061,7 +1084,7 @@ __device__ __forceinline__ void run_decode_warps(const MapParams& p, const Produ
                     }
                 }
             };
-            if (!(p.debug & 4096)) {
+            if (!(debug_bits(p) & 4096)) {
                 decode_stage(std::false_type{});
                 if (__any_sync(0xffffffffu, suspect != 0)) decode_stage(std::true_type{});
             }
@@ -1218,7 +1241,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         for (int n = 0; n < DN; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
-            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p.status)) break;
+            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
             const TaskSlot* ts = task_ring + tslot;
             if (ts->done) break;
             const uint32_t t_tmpl = ts->tmpl, t_head_begin = ts->head_begin, t_num_heads = ts->num_heads;
@@ -1289,8 +1312,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     my_slot -= NS;
                     my_parity ^= 1;
                 }
-                if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p.status)) continue;
-                if (p.debug & 1) {
+                if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p)) continue;
+                if (debug_bits(p) & 1) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
                     continue;
@@ -1335,7 +1358,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 float s[NT][4];
 #pragma unroll
                 for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-                const uint32_t knock = (p.debug >> 4) & 7;  // measurement aid
+                const uint32_t knock = (debug_bits(p) >> 4) & 7;  // measurement aid
                 if (!(knock & 1))
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
@@ -1463,7 +1486,7 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
             }
             stage_counter += t_num_tiles;
 
-            if (p.debug & 2) {
+            if (debug_bits(p) & 2) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
                 continue;
@@ -1629,8 +1652,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                 consumer_barrier<3>(NCW * 32);     // every consumer thread has issued its partial stores
                 if (threadIdx.x == 0) {
                     __threadfence();               // cumulative: orders the whole CTA's stores before the count
-                    const uint32_t seen = (p.debug & 256) ? 0u : atomicAdd(p.arrivals + t_group, 1u);
-                    const uint32_t last = (seen + 1 == t_part_count && !(p.debug & 128)) ? 1u : 0u;
+                    const uint32_t seen = (debug_bits(p) & 256) ? 0u : atomicAdd(p.arrivals + t_group, 1u);
+                    const uint32_t last = (seen + 1 == t_part_count && !(debug_bits(p) & 128)) ? 1u : 0u;
                     if (last) p.arrivals[t_group] = 0;
                     *last_flag = last;
                 }

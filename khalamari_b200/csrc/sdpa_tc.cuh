@@ -258,17 +258,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             bool ok = true;
             for (uint32_t taken = 0; ok; ++taken) {
                 const uint32_t tslot = taken % TQ;
-                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) break;
                 const TaskSlot* ts = task_ring + tslot;
                 if (ts->done) break;
                 const uint32_t num_tiles = ts->num_tiles;
-                if (!mbar_wait(q_ready_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(q_ready_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) break;
                 const uint32_t q_tmem = tmem_q + 64 * tslot;
                 for (uint32_t i = 0; i < num_tiles; ++i) {
                     const uint32_t g = stage_base + i;
                     const uint32_t slot = g % NS, sb = g & 1;
-                    if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p.status)) { ok = false; break; }
-                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
+                    if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p)) { ok = false; break; }
+                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p)) { ok = false; break; }
                     tmem_fence_after();
                     const uint64_t k_desc = k_desc0 + uint64_t((ring_addr + slot * G::kStageBytes) >> 4);
 #pragma unroll
@@ -288,7 +288,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             }
             // nothing issued here may still be running when tensor memory is freed (bounded, also on the abort path)
             umma_commit(drain_bar);
-            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+            for (uint32_t i = 0; i < p.wait_limit; ++i) {
                 if (mbar_try_wait(drain_bar, 0)) break;
             }
         }
@@ -306,17 +306,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             bool ok = true;
             for (uint32_t taken = 0; ok; ++taken) {
                 const uint32_t tslot = taken % TQ;
-                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(task_full_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) break;
                 const TaskSlot* ts = task_ring + tslot;
                 if (ts->done) break;
                 const uint32_t num_tiles = ts->num_tiles;
                 for (uint32_t i = 0; i < num_tiles; ++i) {
                     const uint32_t g = stage_base + i;
                     const uint32_t slot = g % NS, pb = g & 1;
-                    if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                    if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p)) { ok = false; break; }
                     if (i == 0 && pv_tasks > 0) {
                         // this task's first product overwrites O: the previous task's epilogue must have read it
-                        if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                        if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p)) { ok = false; break; }
                     }
                     tmem_fence_after();
                     const uint64_t v_desc = v_desc0 + uint64_t((ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes) >> 4);
@@ -325,7 +325,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
                         const uint64_t v = v_desc + uint64_t(((2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024) >> 4);
                         umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
-                        if (!(p.debug & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
+                        if (!(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
                     }
                     umma_commit(empty_bar + 8 * slot);  // K and V of the stage are consumed (its Q K^T completed
                                                         // before the probabilities could be computed)
@@ -336,7 +336,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 if (ok) mbar_arrive(task_empty_bar + 8 * tslot);  // done with the task's descriptor
             }
             umma_commit(drain_bar + 8);
-            for (uint32_t i = 0; i < kWaitLimit; ++i) {
+            for (uint32_t i = 0; i < p.wait_limit; ++i) {
                 if (mbar_try_wait(drain_bar + 8, 0)) break;
             }
         }
@@ -356,7 +356,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         uint32_t stage_base = 0;
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
-            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p.status)) break;
+            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
             const TaskSlot* ts = task_ring + tslot;
             if (ts->done) break;
             const uint32_t t_tmpl = ts->tmpl, t_head_begin = ts->head_begin, t_num_heads = ts->num_heads;
@@ -404,7 +404,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t g = stage_base + i;
                 if ((g & 1) != wg) continue;
                 const uint32_t sb = wg;
-                if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p)) { failed = true; break; }
                 tmem_fence_after();
                 // the row's 64 scores, kept as bit patterns in one register array (register pressure decides the
                 // speed of this loop: twelve warps leave 170 registers per thread)
@@ -434,7 +434,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 float m_prev = -INFINITY;
                 if (i > 0) {
                     const uint32_t gp = g - 1;  // handled by the other group
-                    if (!mbar_wait(decided_bar + 8 * (wg ^ 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                    if (!mbar_wait(decided_bar + 8 * (wg ^ 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                     m_prev = row_max[row];
                 }
                 if (m_ref != m_prev) {
@@ -454,7 +454,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     if (i > 0) {
                         // O holds this task's earlier stages: wait for the previous stage's products, then scale
                         const uint32_t gp = g - 1;
-                        if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                        if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                         tmem_fence_after();
 #pragma unroll
                         for (int c0 = 0; c0 < D; c0 += 32) {
@@ -477,7 +477,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 // the probability buffer is free once the products of this group's previous stage have completed
                 if (g >= 2) {
                     const uint32_t gp = g - 2;
-                    if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p.status)) { failed = true; break; }
+                    if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                 }
                 tmem_fence_after();
 #pragma unroll
@@ -523,13 +523,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             // publishes 64 of the row's columns
             __syncwarp();
             if (lane == 0) mbar_arrive(epilogue_bar);      // every decision of the task has been made
-            if (!mbar_wait(epilogue_bar, popped & 1, abort_flag, p.status)) break;
+            if (!mbar_wait(epilogue_bar, popped & 1, abort_flag, p)) break;
             const float m_fin = t_num_tiles > 0 ? row_max[row] : -INFINITY;
             if (m_ref != m_fin && m_ref != -INFINITY) l_run *= fast_exp2((m_ref - m_fin) * p.scale_log2e);
             row_sum[wg * 128 + row] = l_run;
             __syncwarp();
             if (lane == 0) mbar_arrive(epilogue_bar + 8);  // every group's sum is written
-            if (!mbar_wait(epilogue_bar + 8, popped & 1, abort_flag, p.status)) break;
+            if (!mbar_wait(epilogue_bar + 8, popped & 1, abort_flag, p)) break;
             const float l_tot = row_sum[row] + row_sum[128 + row];
             const bool write_final = p.direct != 0;
             const float inv_l = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
@@ -537,7 +537,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
             if (t_num_tiles > 0) {
                 const uint32_t gl = stage_base - 1;
-                if (!mbar_wait(pv_done_bar + 8 * (gl & 1), (gl >> 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(pv_done_bar + 8 * (gl & 1), (gl >> 1) & 1, abort_flag, p)) break;
                 tmem_fence_after();
 #pragma unroll
                 for (int c0 = 0; c0 < D / 2; c0 += 32) {

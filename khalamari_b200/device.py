@@ -47,6 +47,11 @@ class Device:
         abi.call("kh_device_check", self.handle, stream.handle if stream else None, C.byref(word))
         return word.value
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls a wait inside a kernel makes before it gives up and the kernel returns with bit 0 of the status
+        word set (``kh_device_set_wait_limit``); 0 restores the default."""
+        abi.call("kh_device_set_wait_limit", self.handle, int(polls))
+
     def close(self) -> None:
         if self.handle:
             abi.call("kh_device_close", self.handle)
@@ -143,9 +148,35 @@ class Stream:
         run (four u32: tokens, Q-token tiles, map task templates, 0); ``None`` returns to by-value counts."""
         abi.call("kh_stream_bind_active_counts", self.handle, counts.ref if counts is not None else abi.BufferRef())
 
+    def record_event(self, event: "Event") -> None:
+        abi.call("kh_stream_record_event", self.handle, event.handle)
+
+    def wait_event(self, event: "Event") -> None:
+        """Orders the work recorded on this stream from now on after ``event``; the host does not block."""
+        abi.call("kh_stream_wait_event", self.handle, event.handle)
+
     def destroy(self) -> None:
         if self.handle:
             abi.call("kh_stream_destroy", self.handle)
+            self.handle = None
+
+
+class Event:
+    """Completion of the work recorded on a stream so far: the analogue of ``ReplaySubmission``
+    (metal/stream/submission.rs:41-101); ``synchronize`` is its ``wait``."""
+
+    def __init__(self, device: Device):
+        handle = C.c_void_p()
+        abi.call("kh_event_create", device.handle, C.byref(handle))
+        self.handle = handle
+        self.device = device
+
+    def synchronize(self) -> None:
+        abi.call("kh_event_synchronize", self.handle)
+
+    def destroy(self) -> None:
+        if self.handle:
+            abi.call("kh_event_destroy", self.handle)
             self.handle = None
 
 

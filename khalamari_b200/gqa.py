@@ -82,6 +82,16 @@ class GQAAttention:
         num_tokens = int(cu_tokens[-1]) if len(cu_tokens) else 0
         if num_tokens <= 0:
             raise abi.InvalidArgument(1, "GQA replay requires active tokens")
+        # the page table's shape is known here: a slot or a context beyond it must not reach the kernels
+        capacity = self.layout.num_blocks * self.layout.num_page_ids_per_block * self.tokens_per_page
+        for r, slot in enumerate(req_slots):
+            if not 0 <= int(slot) < self.layout.num_req_slots:
+                raise abi.InvalidArgument(1, f"GQA request slot {int(slot)} out of range: num_req_slots="
+                                             f"{self.layout.num_req_slots}")
+            context = int(token_indices[r]) + int(cu_tokens[r + 1]) - int(cu_tokens[r])
+            if context > capacity:
+                raise abi.InvalidArgument(1, f"GQA request context of {context} tokens exceeds the page table's "
+                                             f"{capacity} tokens per request")
         if num_total_tokens is None:
             # the executor records token capacities in replay buckets; a Q-tile capacity (bucketed by the selector)
             # can never exceed it
@@ -200,6 +210,85 @@ class GQAAttention:
         launches = self.record_sdpa(stream, q_dev, kv_pages, page_ids, out_dev, gqa_layer_index)
         stream.read(out_dev, 0, out_host.ptr, num_tokens * row)
         return launches, num_tokens * row + self.metadata.upload_bytes(), num_tokens * row
+
+
+class HostPipeline:
+    """Attention calls with host buffers, two steps in flight.
+
+    A step is what a host-side caller issues per batch: copy Q from page-locked host memory, plan the batch
+    (selector + metadata, on the host, while the copy runs), run map + reduce over the resident KV pages, copy
+    the output back. ``submit`` enqueues one step and returns without waiting; the output copy of a step runs on a
+    second stream while the kernels of the next step run on the first (``ReplaySubmission`` handles in the
+    reference, metal/stream/submission.rs:41-101: a caller may hold several submissions and wait for each). Two
+    slots of device Q / output buffers and batch metadata alternate; ``submit`` first waits for the step that used
+    the slot two submissions ago, so at most two steps are in flight. ``wait(ticket)`` blocks until that step's
+    output is in its host buffer."""
+
+    SLOTS = 2
+
+    def __init__(self, attention: GQAAttention, compute_stream: Stream):
+        from .device import Event
+
+        self.attention = attention
+        self.compute = compute_stream
+        self.copy = Stream(attention.device)
+        core = attention.core
+        limits = attention.limits
+        row = core.num_q_heads * core.head_dim * attention.io_dtype.item_size()
+        capacity = attention.policy.q_token_ranges.capacity(limits.max_tokens)
+        self.row_bytes = row
+        self.q = [Buffer.new_zeroed(attention.device, capacity * row) for _ in range(self.SLOTS)]
+        self.out = [Buffer.new_zeroed(attention.device, capacity * row) for _ in range(self.SLOTS)]
+        self.metadata = [attention.metadata] + [
+            GQAMetadataBuffers(attention.device, limits.max_tokens, limits.max_map_task_templates)
+            for _ in range(self.SLOTS - 1)]
+        self.kernels_done = [Event(attention.device) for _ in range(self.SLOTS)]
+        self.copied = [Event(attention.device) for _ in range(self.SLOTS)]
+        self.in_flight = [False] * self.SLOTS
+        self.submitted = 0
+
+    def submit(self, q_host: PinnedArray, out_host: PinnedArray, kv_pages: Buffer, page_ids: Buffer, req_slots,
+               token_indices, cu_tokens, gqa_layer_index: int = 0, partition: int | None = None):
+        """Enqueues one step. ``partition``: force split-KV slices of that many tokens (the selector still runs,
+        through ``select_partitioned``); None lets the selector choose. Returns (ticket, kernel launches,
+        host->device bytes, device->host bytes). ``q_host`` may be reused once ``submit`` returns the ticket of
+        the step after next; ``out_host`` is valid after ``wait(ticket)``."""
+        attention = self.attention
+        slot = self.submitted % self.SLOTS
+        if self.in_flight[slot]:
+            self.copied[slot].synchronize()  # the slot's buffers and its metadata host block are free again
+        num_tokens = int(cu_tokens[-1])
+        nbytes = num_tokens * self.row_bytes
+        self.compute.write(self.q[slot], 0, q_host.ptr, nbytes)  # runs while the host plans the batch
+        attention.metadata = self.metadata[slot]
+        selection = None
+        if partition:
+            variant = next(v for v in attention.selector.variants()
+                           if v.kind == 0 and v.thread_block.max_q_tokens == 1)
+            selection = attention.select_partitioned(variant, partition, False, token_indices, cu_tokens, num_tokens)
+        attention.prepare(req_slots, token_indices, cu_tokens, num_tokens, self.compute, selection)
+        launches = attention.record_sdpa(self.compute, self.q[slot], kv_pages, page_ids, self.out[slot],
+                                         gqa_layer_index)
+        self.compute.record_event(self.kernels_done[slot])
+        self.copy.wait_event(self.kernels_done[slot])
+        self.copy.read(self.out[slot], 0, out_host.ptr, nbytes)
+        self.copy.record_event(self.copied[slot])
+        # the next user of this slot's device buffers is two steps away and ordered by `copied` on the host
+        self.in_flight[slot] = True
+        ticket = self.submitted
+        self.submitted += 1
+        return ticket, launches, nbytes + attention.metadata.upload_bytes(), nbytes
+
+    def wait(self, ticket: int) -> None:
+        if ticket < self.submitted - self.SLOTS:
+            return  # its slot has been reused, which waited for it
+        self.copied[ticket % self.SLOTS].synchronize()
+
+    def drain(self) -> None:
+        for slot in range(self.SLOTS):
+            if self.in_flight[slot]:
+                self.copied[slot].synchronize()
+                self.in_flight[slot] = False
 
 
 def combine_partials(device: Device, stream: Stream, num_partials: int, num_rows: int, head_dim: int,

@@ -95,13 +95,17 @@ class PagedCase:
 def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, head_dim: int, histories, q_lens,
               tokens_per_page: int = 16, num_gqa_layers: int = 1, layer_index: int = 0, num_page_ids_per_block: int = 1,
               pool_pages: int | None = None, extra_slots: int = 0, poison: bool = True, scale: float | None = None,
-              keep_f32: bool = True, q_std: float = 1.0, kv_fp8: bool = False, kv_std: float = 1.0) -> PagedCase:
+              keep_f32: bool = True, q_std: float = 1.0, kv_fp8: bool = False, kv_std: float = 1.0,
+              workers: int = 1) -> PagedCase:
     """Builds requests with ``histories[r]`` cached tokens and ``q_lens[r]`` new tokens (already in the cache,
     as after the page-write step), a shared pool whose pages are handed out by a seeded permutation, and an
     unwritten pool filled with NaN bit patterns when ``poison`` (the tail of a last page must not leak).
     ``kv_fp8``: K and V go through the reference's page-write conversion (rounded to bf16, then to FP8 E4M3FN,
     components/gqa/fp8.rs:19-44); the pool holds the codes and the oracle sees their decoded values, as in
-    sliced_kv_test.rs:171-182."""
+    sliced_kv_test.rs:171-182.
+    ``workers`` > 1 (the full-size configurations): K and V are drawn in chunks of 16,384 tokens, each from a
+    generator of its own seeded ``[seed, request, first token]``, on a pool of threads; chunk boundaries fall on page
+    boundaries, so the chunks fill disjoint pages side by side."""
     rng = np.random.default_rng(seed)
     num_reqs = len(histories)
     contexts = [int(h) + int(q) for h, q in zip(histories, q_lens)]
@@ -119,21 +123,23 @@ def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, h
     if kv_fp8:
         pool = np.full(pool_pages * page_bytes, 0x7F if poison else 0, dtype=np.uint8)  # 0x7f: the NaN code
     else:
-        pool16 = np.full(pool_pages * page_bytes // 2, nan_bits(dtype_name) if poison else 0, dtype=np.uint16)
-        pool = pool16.view(np.uint8)
+        if poison:
+            pool = np.full(pool_pages * page_bytes // 2, nan_bits(dtype_name), dtype=np.uint16).view(np.uint8)
+        else:
+            pool = np.zeros(pool_pages * page_bytes, dtype=np.uint8)
     table = np.zeros(layout.num_page_ids(), dtype=np.uint32)
     # request r lives in slot order shuffled so that slot != request index
     slots = rng.permutation(num_slots)[:num_reqs].astype(np.uint32)
     free_pages = rng.permutation(pool_pages).astype(np.uint32)
-    cursor = 0
-    case_k, case_v = [], []
+    first_page = np.concatenate([[0], np.cumsum(pages_needed)]).astype(np.int64)
     for r in range(num_reqs):
-        ids = free_pages[cursor:cursor + pages_needed[r]]
-        cursor += pages_needed[r]
+        ids = free_pages[first_page[r]:first_page[r + 1]]
         base = ((int(slots[r]) * num_gqa_layers + layer_index) * num_blocks) * num_page_ids_per_block
         table[base:base + ids.size] = ids
-        k = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
-        v = rng.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
+
+    def fill(r, generator):
+        k = generator.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
+        v = generator.standard_normal((contexts[r], num_kv_heads, head_dim), dtype=np.float32) * np.float32(kv_std)
         if kv_fp8:
             k_bits, k_round = fp8_codes(k)
             v_bits, v_round = fp8_codes(v)
@@ -142,9 +148,37 @@ def make_case(seed: int, dtype_name: str, num_q_heads: int, num_kv_heads: int, h
             v_bits, v_round = round_to(dtype_name, v)
         oracle.scatter_paged(pool, table, layout, int(slots[r]), layer_index, tokens_per_page, num_kv_heads,
                              head_dim, kv_elem, 0, k_bits, v_bits)
-        if keep_f32:
-            case_k.append(k_round)
-            case_v.append(v_round)
+        return (k_round, v_round) if keep_f32 else None
+
+    if workers > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        chunk_tokens = 16384
+        whole = [(np.empty((c, num_kv_heads, head_dim), np.float32), np.empty((c, num_kv_heads, head_dim), np.float32))
+                 if keep_f32 else None for c in contexts]
+
+        def fill_chunk(unit):
+            r, begin = unit
+            end = min(begin + chunk_tokens, contexts[r])
+            generator = np.random.default_rng([seed, r, begin])
+            shape = (end - begin, num_kv_heads, head_dim)
+            k = generator.standard_normal(shape, dtype=np.float32) * np.float32(kv_std)
+            v = generator.standard_normal(shape, dtype=np.float32) * np.float32(kv_std)
+            k_bits, k_round = fp8_codes(k) if kv_fp8 else round_to(dtype_name, k)
+            v_bits, v_round = fp8_codes(v) if kv_fp8 else round_to(dtype_name, v)
+            oracle.scatter_paged(pool, table, layout, int(slots[r]), layer_index, tokens_per_page, num_kv_heads,
+                                 head_dim, kv_elem, begin, k_bits, v_bits)
+            if keep_f32:
+                whole[r][0][begin:end] = k_round
+                whole[r][1][begin:end] = v_round
+
+        units = [(r, begin) for r in range(num_reqs) for begin in range(0, contexts[r], chunk_tokens)]
+        with ThreadPoolExecutor(workers) as pool_of_threads:
+            list(pool_of_threads.map(fill_chunk, units))
+        filled = whole
+    else:
+        filled = [fill(r, rng) for r in range(num_reqs)]
+    case_k = [f[0] for f in filled] if keep_f32 else []
+    case_v = [f[1] for f in filled] if keep_f32 else []
     cu = [0]
     for q in q_lens:
         cu.append(cu[-1] + int(q))

@@ -5,6 +5,8 @@ import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
 
 
 def test_reference_arm_prints_one_contract_line():
@@ -20,7 +22,11 @@ def test_reference_arm_prints_one_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["cpu_baseline"]["value"] == line["value"]
     assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-    assert "workload" in line["config"] and "sample" in line["config"]
+    # the same `config` object as the GPU arm prints, so that the two lines describe one configuration
+    import bench
+    spec = bench.WORKLOADS["c2"]
+    assert line["config"] == bench.workload_config(spec, bench.contexts_for(spec, 0), 1)
+    assert "requests" in line["cpu_baseline"]["sample"]
 
 
 def test_other_ranks_of_the_reference_arm_exit_quietly():
