@@ -533,11 +533,11 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
         decode.prepare(0, local_len, partition)
         return case, attention, decode
 
-    def timed(fn, count):
+    def timed(fn, count, all_ranks):
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
-        if world > 1:
+        if world > 1 and all_ranks:
             dist.barrier()
         torch.cuda.synchronize()
         first = torch.cuda.Event(enable_timing=True)
@@ -550,31 +550,60 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
         torch.cuda.synchronize()
         return first.elapsed_time(last) / count, n
 
+    def measure(decode, case, all_ranks):
+        """Times one decode object: the eager step, the step and its local part (map + local merge) replayed as CUDA
+        graphs (the analogue of the reference's recorded replay program; removes the host's launch gaps). Returns
+        (step ms, eager step ms, local ms, launches per step)."""
+        def eager_step():
+            return decode.record_step(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
+
+        def eager_local():
+            return decode.record_local(stream, case["d_q"], case["d_pool"], case["d_table"], 0)
+
+        for _ in range(min(max(int(args.ramp_ms), 1), 400)):  # a count: every rank runs the same number of collectives
+            eager_step()
+        torch.cuda.synchronize()
+        eager_ms, launches = timed(eager_step, steps, all_ranks)
+        if args.no_graph:
+            local_ms, _ = timed(eager_local, steps, all_ranks)
+            return eager_ms, eager_ms, local_ms, launches // steps
+        from khalamari_b200.device import Stream as KhStream
+        side = torch.cuda.Stream()
+        side_stream = KhStream(device, side.cuda_stream)
+
+        def captured(record):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    record(side_stream)
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    record(side_stream)
+            torch.cuda.synchronize()
+            return graph
+
+        step_graph = captured(lambda s: decode.record_step(s, case["d_q"], case["d_pool"], case["d_table"],
+                                                           case["d_out"], 0))
+        local_graph = captured(lambda s: decode.record_local(s, case["d_q"], case["d_pool"], case["d_table"], 0))
+        step_ms, _ = timed(lambda: step_graph.replay(), steps, all_ranks)
+        local_ms, _ = timed(lambda: local_graph.replay(), steps, all_ranks)
+        return step_ms, eager_ms, local_ms, launches // steps
+
     begin, end = split_kv.split_context(context, world, PAGE)[rank]
     local_len = end - begin
     # every rank draws the SAME Q row (seed without the rank) and its own K/V pages
     case, attention, decode = build(local_len, spec["seed"] + 1000 * rank, world)
-    q_shared = torch.randn(hq * d, generator=torch.Generator(device="cuda").manual_seed(spec["seed"]), device="cuda",
-                           dtype=torch.float32).to(torch.bfloat16)
+    # (a seed of its own: the page pool of rank 0 starts from spec["seed"], and a Q row equal to a cached K row
+    # would make the softmax one-hot)
+    q_shared = torch.randn(hq * d, generator=torch.Generator(device="cuda").manual_seed(spec["seed"] + 424243),
+                           device="cuda", dtype=torch.float32).to(torch.bfloat16)
     case["q"].copy_(q_shared)
-
-    def step():
-        return decode.record_step(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0)
-
-    def local_only():
-        return decode.record_local(stream, case["d_q"], case["d_pool"], case["d_table"], 0)
-
-    ramp = max(int(args.ramp_ms), 1) if world > 1 else max(int(args.ramp_ms), 1)
-    for _ in range(min(ramp, 400)):  # a count, not a time limit: every rank must run the same number of collectives
-        step()
-    torch.cuda.synchronize()
-    step_ms, launches = timed(step, steps)
-    local_ms, _ = timed(local_only, steps)
+    step_ms, eager_ms, local_ms, launches = measure(decode, case, True)
     device.check(stream)
-    stats = torch.tensor([step_ms, local_ms], device="cuda", dtype=torch.float64)
+    stats = torch.tensor([step_ms, local_ms, eager_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    step_ms, local_ms = stats.tolist()
+    step_ms, local_ms, eager_ms = stats.tolist()
 
     # ---- parity: every rank restates its own slice on the CPU as one partial (m, l, o) per head, rank 0 merges the
     # partials with the reducer's formula and compares the GPU result
@@ -617,18 +646,7 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
         torch.cuda.empty_cache()
         if rank == 0:
             case1, attention1, decode1 = build(context, spec["seed"], 1)
-            fn = lambda: decode1.record_step(stream, case1["d_q"], case1["d_pool"], case1["d_table"], case1["d_out"], 0)
-            for _ in range(50):
-                fn()
-            first = torch.cuda.Event(enable_timing=True)
-            last = torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            first.record(torch_stream)
-            for _ in range(steps):
-                fn()
-            last.record(torch_stream)
-            torch.cuda.synchronize()
-            single_ms = first.elapsed_time(last) / steps
+            single_ms = measure(decode1, case1, False)[0]
             del case1, attention1, decode1
             torch.cuda.empty_cache()
         dist.barrier()
@@ -636,11 +654,12 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
         return None
     total_bytes = context * 2 * hkv * d * 2
     return {"context_tokens": context, "tokens_per_gpu": local_len, "ms_per_step": round(step_ms, 5),
+            "form": "eager launches" if args.no_graph else "replayed CUDA graph", "eager_ms_per_step": round(eager_ms, 5),
             "local_kernel_ms": round(local_ms, 5), "exchange_ms": round(step_ms - local_ms, 5),
             "kv_gbs_total": round(total_bytes / (step_ms * 1e-3) / 1e9, 1),
             "kv_gbs_per_gpu_local": round(local_len * 2 * hkv * d * 2 / (local_ms * 1e-3) / 1e9, 1),
             "one_gpu_ms_per_step": round(single_ms, 5),
-            "efficiency_vs_one_gpu": round(single_ms / (world * step_ms), 4), "gpu_launches_per_step": launches // steps,
+            "efficiency_vs_one_gpu": round(single_ms / (world * step_ms), 4), "gpu_launches_per_step": launches,
             "parity": parity}
 
 
@@ -784,6 +803,8 @@ def main():
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-parity", action="store_true", help="skip the oracle check of the bench's own output")
+    parser.add_argument("--no-graph", action="store_true",
+                        help="one long sequence: time eager launches only, not the step replayed as a CUDA graph")
     parser.add_argument("--no-split-kv", action="store_true",
                         help="default workload: skip the one-long-sequence measurements that follow the headline")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")

@@ -20,7 +20,9 @@ struct MapInstance {
 };
 
 // Warp-level instance for K/V pages of FP8 E4M3FN elements (sdpa_fp8.cu; compiled apart from the 16-bit instances
-// so that the two translation units build side by side). `rows` = Q rows per task.
-MapInstance pick_instance_fp8(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows);
+// so that the two translation units build side by side). `rows` = Q rows per task; `one_launch`: the instance
+// must support the map + reduce in one launch form (arrival counters).
+MapInstance pick_instance_fp8(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows,
+                              bool one_launch);
 
 }  // namespace kh

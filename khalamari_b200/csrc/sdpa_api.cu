@@ -370,10 +370,11 @@ static void init_common(ComputeCommon& c, kh_device* device, kh_dtype dtype, kh_
     c.variant = variant;
     c.tokens_per_page = page_bytes / (2 * num_kv_heads * head_dim * dtype_size(kv_dtype));
     const uint32_t rows = variant.max_q_tokens * variant.max_q_heads;
-    c.instance = fp8 ? pick_instance_fp8(dtype, head_dim, c.tokens_per_page, rows)
+    c.instance = fp8 ? pick_instance_fp8(dtype, head_dim, c.tokens_per_page, rows, false)
                      : pick_instance(dtype, head_dim, c.tokens_per_page, rows, true);
     // the one-launch map + reduce form counts arrivals inside the warp-level kernel
-    c.fused_instance = fp8 ? c.instance : pick_instance(dtype, head_dim, c.tokens_per_page, rows, false);
+    c.fused_instance = fp8 ? pick_instance_fp8(dtype, head_dim, c.tokens_per_page, rows, true)
+                           : pick_instance(dtype, head_dim, c.tokens_per_page, rows, false);
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.instance.kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, c.instance.smem_bytes));
     KH_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(c.fused_instance.kernel),

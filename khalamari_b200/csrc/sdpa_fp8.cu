@@ -7,6 +7,7 @@
 
 #include "common.h"
 #include "map_instance.h"
+#include "sdpa_tm.cuh"
 
 namespace kh {
 
@@ -17,13 +18,29 @@ static MapInstance make_fp8_instance() {
                        G::kBoxRows, G::kRawStages};
 }
 
+// Token-major instance (sdpa_tm.cuh): the raw bytes are consumed from the copied stage, no decode warps.
+template <typename T, int D, int P, int NQ, int CW>
+static MapInstance make_tm_instance() {
+    using G = TmGeometry<D, P, NQ, CW>;
+    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
+                       G::kStages};
+}
+
 // Same consumer shapes by task rows as the 16-bit table; tasks of more than 64 rows stay on the warp-level
 // instance (the tensor-memory kernel reads 16-bit pages only).
 // Decode shapes (one row tile) at head_dim 128: two KV warp groups of two warps that split a stage's tokens,
 // instead of four groups of one. The 16-bit ring (two slots per group) then takes 64 KB instead of 128 KB, and
 // the raw ring, whose depth is what covers the HBM latency, twice as many stages.
 template <typename T, int D, int P>
-static MapInstance pick_fp8_rows(uint32_t rows) {
+static MapInstance pick_fp8_rows(uint32_t rows, bool one_launch) {
+    // Decode and short verify tasks take the token-major kernel; the one-launch map + reduce form (arrival
+    // counters) exists in the decode-warp kernel only.
+    if (!one_launch) {
+        if (rows <= 8) return make_tm_instance<T, D, P, 1, 8>();
+        if constexpr (D == 128) {
+            if (rows <= 16) return make_tm_instance<T, D, P, 2, 8>();
+        }
+    }
     if constexpr (D == 128) {
         if (rows <= 8) return make_fp8_instance<T, D, P, 1, 2, true, 2>();
         if (rows <= 16) return make_fp8_instance<T, D, P, 1, 2, false, 2>();
@@ -39,18 +56,19 @@ static MapInstance pick_fp8_rows(uint32_t rows) {
 }
 
 template <typename T>
-static MapInstance pick_fp8_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+static MapInstance pick_fp8_geometry(uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows, bool one_launch) {
     KH_REQUIRE(tokens_per_page == 16, "FP8 pages: this build instantiates 16-token pages (got %u)", tokens_per_page);
-    if (head_dim == 128) return pick_fp8_rows<T, 128, 16>(rows);
+    if (head_dim == 128) return pick_fp8_rows<T, 128, 16>(rows, one_launch);
     KH_REQUIRE(head_dim == 256, "this build instantiates head_dim 128 and 256 only (got %u)", head_dim);
-    return pick_fp8_rows<T, 256, 16>(rows);
+    return pick_fp8_rows<T, 256, 16>(rows, one_launch);
 }
 
-MapInstance pick_instance_fp8(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows) {
+MapInstance pick_instance_fp8(kh_dtype dtype, uint32_t head_dim, uint32_t tokens_per_page, uint32_t rows,
+                              bool one_launch) {
     KH_REQUIRE(rows >= 1 && rows <= 128, "a Map task holds at most 128 (Q token, Q head) rows (got %u)", rows);
-    if (dtype == KH_DTYPE_BFLOAT16) return pick_fp8_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows);
+    if (dtype == KH_DTYPE_BFLOAT16) return pick_fp8_geometry<__nv_bfloat16>(head_dim, tokens_per_page, rows, one_launch);
     KH_REQUIRE(dtype == KH_DTYPE_FLOAT16, "Q/output dtype must be Bfloat16 or Float16 on this backend");
-    return pick_fp8_geometry<__half>(head_dim, tokens_per_page, rows);
+    return pick_fp8_geometry<__half>(head_dim, tokens_per_page, rows, one_launch);
 }
 
 }  // namespace kh

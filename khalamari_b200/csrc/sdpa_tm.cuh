@@ -1,0 +1,569 @@
+// Map / direct kernel for K/V pages of FP8 E4M3FN elements, "token-major" form: the KV tokens of a stage are the
+// M dimension of the warp-level tensor-core tiles and the task's Q rows - (Q tokens of the range) x (Q heads of
+// the KV group), at most 32 - are the N dimension (8 rows per n-tile).
+//
+//   S^T = K Q^T   m16n8k16, A = 16 KV tokens x 16 head-dim elements, B = the Q rows.
+//   O^T += V^T P^T  m16n8k16, A = 16 head-dim elements x 16 KV tokens, B = the probabilities.
+//
+// Why this form for one-byte pages. The pages are the reference's cache format (one byte per stored element, one
+// unit scale; components/gqa/sdpa/sliced_kv.rs:113-125, decoded on load by metal/gqa_fp8.metal:1-25). At the HBM
+// rate a one-byte page delivers twice the tokens per second of a 16-bit page, so everything per token has to
+// cost half as much:
+//  - The raw bytes are consumed straight from the copied stage, with no intermediate 16-bit copy in shared memory:
+//    K through ldmatrix as if the bytes were 16-bit pairs (a thread receives four consecutive head-dim elements of
+//    one token), V through the 8-bit transposing matrix load (ldmatrix .m16n16 .trans .b8: a thread receives four
+//    consecutive tokens of one head-dim element). Both hand a thread *four consecutive* indices of the contraction
+//    dimension where the MMA fragment wants the pairs (2t, 2t+1) and (2t+8, 2t+9): a fixed permutation of the 16
+//    contraction indices. A sum is order-free, so the other operand is simply read under the same permutation: Q
+//    (for K's head-dim order) by an 8-byte shared-memory load per fragment, P (for V's token order) by choosing
+//    which token each row of the K tile is (ldmatrix takes a row address per lane) and transposing the packed
+//    probabilities with movmatrix.
+//  - Conversion is one instruction per element pair (cvt.rn.f16x2.e4m3x2, exact; the NaN codes become NaN) and the
+//    MMAs run in f16 whatever the Q/output type: every E4M3 value is an f16 value, bf16 Q values convert exactly
+//    inside f16's range (beyond it they saturate), and f16 probabilities carry 11 significant bits.
+//  - With the tokens on M, a decode task (8 rows) costs one MMA per 16 tokens x 16 head-dim elements instead of two
+//    half-empty ones, and each K/V fragment is loaded once for all Q rows of the task.
+//  - A thread's accumulator is D/16 x (rows/8) x 4 registers (32 for decode at head_dim 128), so eight consumer
+//    warps fit an SM and hide one another's ldmatrix, MMA and MUFU latencies.
+// Task ABI, task warp, stream warp, rings and partial-state layout are those of sdpa_map_kernel (sdpa_map.cuh).
+// Synchronisation between the consumer warps goes through mbarriers with bounded waits only.
+#pragma once
+
+#include "sdpa_map.cuh"
+
+namespace kh {
+
+// D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps.
+template <int D, int P, int NQ, int CW>
+struct TmGeometry {
+    static_assert(P == 16, "the token-major kernel is built for 16-token pages (one page = one 16-token MMA tile)");
+    static_assert(D == 128 || D == 256, "head_dim 128 or 256");
+    static constexpr int kStageTokens = (D == 128) ? 32 : 16;
+    static constexpr int kBoxRows = P;
+    static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;   // pages per stage
+    static constexpr int kColumnGroups = D / 128;                     // 128-byte lines per stored row
+    static constexpr int kBoxBytes = kBoxRows * 128;                  // one column group of one page
+    static constexpr int kPlaneBoxBytes = kColumnGroups * kBoxBytes;  // K (or V) rows of one page
+    static constexpr int kCopyBytes = 2 * kPlaneBoxBytes;             // one TMA copy: K and V of one (page, KV head)
+    static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;   // 8 KiB
+    static constexpr int kColumnHalves = D / 64;                      // Q tile: 64-element column halves (16-bit)
+    static constexpr int kQRows = NQ * 8;
+    static constexpr int kQBytes = kQRows * D * 2;
+    static constexpr int kTaskSlots = 2;
+    static constexpr int kConsumerWarps = CW;
+    static constexpr int kThreads = (CW + 2) * 32;                    // + stream warp + task warp
+    static constexpr int kRowStride = D + 4;                          // floats; makes the parking stores conflict free
+    static constexpr int kParkFloats = kQRows * kRowStride + 2 * kQRows;  // O rows, then (max, sum) per row
+    static constexpr int kMergeBytes = CW * kParkFloats * 4;
+    static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
+    static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
+    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 1024;
+    static constexpr int kSmemLimit = 227 * 1024 - 1024;
+    static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+    static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
+    static constexpr int kStages = kStagesCapped / CW * CW;          // a ring slot always belongs to the same warp
+    static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
+    static constexpr int kPagesPerStage = kBoxesPerPlane;
+    // Q fragments of a task stay in registers for the whole task
+    static constexpr bool kQInRegisters = NQ * (D / 16) * 2 <= 32;
+    static_assert(kStages >= CW && kStages >= 4, "shared memory ring too small");
+    static_assert(kQInRegisters, "this build keeps a task's Q fragments in registers (at most 16 rows at head_dim 128, 8 at 256)");
+    static_assert(NQ >= 1 && NQ <= 4, "a task holds at most 32 Q rows here");
+};
+
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t pair) {
+    uint32_t out;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"(pair));
+    return out;
+}
+
+__device__ __forceinline__ void ldmatrix_m16n16_x2_trans_b8(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+    uint32_t out;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(out) : "r"(v));
+    return out;
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Two Q elements of type T (packed) as f16x2; bf16 values beyond f16's range saturate.
+template <typename T>
+__device__ __forceinline__ uint32_t q_pair_to_f16x2(uint32_t packed);
+template <>
+__device__ __forceinline__ uint32_t q_pair_to_f16x2<__half>(uint32_t packed) { return packed; }
+template <>
+__device__ __forceinline__ uint32_t q_pair_to_f16x2<__nv_bfloat16>(uint32_t packed) {
+    const float lo = fminf(fmaxf(__uint_as_float(packed << 16), -65504.0f), 65504.0f);
+    const float hi = fminf(fmaxf(__uint_as_float(packed & 0xffff0000u), -65504.0f), 65504.0f);
+    return pack_f16x2(lo, hi);
+}
+
+template <typename T, int D, int P, int NQ, int CW>
+__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW>::kThreads, 1)
+sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
+    using G = TmGeometry<D, P, NQ, CW>;
+    constexpr int ST = G::kStageTokens;
+    constexpr int NS = G::kStages;
+    constexpr int TQ = G::kTaskSlots;
+    constexpr int MTK = ST / 16;  // 16-token tiles (pages) per stage
+    constexpr int DK = D / 16;    // contraction steps of K Q^T = 16-element m-tiles of O^T
+    constexpr int RS = G::kRowStride;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    uint8_t* q_ring = ring + NS * G::kStageBytes;
+    float* merge = reinterpret_cast<float*>(q_ring + TQ * G::kQBytes);
+    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
+    TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
+    constexpr int kNumBars = 2 * NS + 3 * TQ + 2;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
+    uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 2;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t full_bar = smem_addr(bars);
+    const uint32_t empty_bar = smem_addr(bars + NS);
+    const uint32_t task_full_bar = smem_addr(bars + 2 * NS);
+    const uint32_t task_empty_bar = smem_addr(bars + 2 * NS + TQ);
+    const uint32_t stream_full_bar = smem_addr(bars + 2 * NS + 2 * TQ);
+    const uint32_t parked_bar = smem_addr(bars + 2 * NS + 3 * TQ);      // every consumer warp parked its state
+    const uint32_t merged_bar = smem_addr(bars + 2 * NS + 3 * TQ + 1);  // every consumer warp read the parked states
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int s = 0; s < TQ; ++s) {
+            mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
+            mbar_init(task_empty_bar + 8 * s, CW + 1);  // every consumer warp and the stream warp
+            mbar_init(stream_full_bar + 8 * s, 1);
+        }
+        mbar_init(parked_bar, CW);
+        mbar_init(merged_bar, CW);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Q rows no copy ever writes (row padding of the tile) must not hold NaN bit patterns.
+    for (int i = threadIdx.x; i < TQ * G::kQBytes / 16; i += G::kThreads) {
+        reinterpret_cast<uint4*>(q_ring)[i] = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+
+    const ActiveCounts active = resolve_active(p);
+    const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
+    const bool balanced =
+        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+
+    ProducerContext producer{};
+    producer.ring = ring;
+    producer.q_ring = q_ring;
+    producer.pid_smem = pid_smem;
+    producer.task_ring = task_ring;
+    producer.full_bar = full_bar;
+    producer.empty_bar = empty_bar;
+    producer.task_full_bar = task_full_bar;
+    producer.task_empty_bar = task_empty_bar;
+    producer.stream_full_bar = stream_full_bar;
+    producer.abort_flag = abort_flag;
+    producer.task_base = balanced ? task_range[0] : blockIdx.x;
+    producer.task_step = balanced ? 1u : gridDim.x;
+    producer.task_limit = balanced ? task_range[1] : total_tasks;
+    producer.balanced = balanced;
+    producer.allow_carry = true;
+    producer.active = active;
+    producer.lane = lane;
+
+    if (warp == CW + 1) {
+        run_task_warp<G, P>(p, q_map, producer);
+    } else if (warp == CW) {
+        run_stream_warp<G, P, stream_lanes(G::kStages)>(p, kv_map, producer);
+    } else {
+        // ------------------------------ consumer warps ----------------------------------------
+        const int g = lane >> 2;   // fragment row group
+        const int tq = lane & 3;   // thread in quad
+        // Row r (0-7) of a 16-token MMA tile is token 4 * (r / 2) + r % 2 of its page, row r + 8 is that token + 2:
+        // a thread's accumulator pair (rows g, g + 8) then holds tokens t and t + 2, and after the transposition of
+        // the packed probabilities thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of Q row g - the four consecutive
+        // tokens the 8-bit transposing load of V gives it.
+        const uint32_t sig = 4u * (g >> 1) + (g & 1);
+        // K: ldmatrix .x4 of raw bytes; matrix (lane >> 3): bit 0 picks the row half (tokens +2), bit 1 the next
+        // 16-byte chunk (= the next 16 head-dim elements)
+        const uint32_t k_mat = lane >> 3, k_r = lane & 7;
+        const uint32_t k_tok = 4u * (k_r >> 1) + (k_r & 1) + 2u * (k_mat & 1);
+        const uint32_t k_lane = k_tok * 128u;
+        const uint32_t k_y4 = ((k_mat >> 1) ^ (k_tok & 7)) << 4;
+        // V: ldmatrix .m16n16 .x2 .trans of raw bytes; lanes 0-15 address the 16 token rows of one 16-byte chunk,
+        // lanes 16-31 those of the next chunk
+        const uint32_t v_tok = lane & 15;
+        const uint32_t v_lane = v_tok * 128u;
+        const uint32_t v_y4 = ((uint32_t(lane) >> 4) ^ (v_tok & 7)) << 4;
+
+        float o[DK][NQ][4];
+        float m_run[NQ][2], l_run[NQ][2];
+#pragma unroll
+        for (int c = 0; c < DK; ++c)
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) {
+            m_run[n][0] = m_run[n][1] = -INFINITY;
+            l_run[n][0] = l_run[n][1] = 0.0f;
+        }
+        uint32_t stage_counter = 0;
+        uint32_t my_stage = warp, my_slot = warp, my_parity = 0;
+        uint32_t merges = 0;  // merges this CTA has run (phase of the two merge barriers)
+        float* const my_park = merge + warp * G::kParkFloats;
+
+        for (uint32_t popped = 0;; ++popped) {
+            const uint32_t tslot = popped % TQ;
+            if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
+            const TaskSlot* ts = task_ring + tslot;
+            if (ts->done) break;
+            const uint32_t t_tmpl = ts->tmpl, t_head_begin = ts->head_begin, t_num_heads = ts->num_heads;
+            const uint32_t t_tok_begin = ts->tok_begin, t_num_toks = ts->num_toks;
+            const uint32_t t_kv_begin = ts->kv_begin, t_kv_end = ts->kv_end;
+            const uint32_t t_tile_begin = ts->tile_begin, t_num_tiles = ts->num_tiles;
+            const uint32_t t_carry = ts->carry;
+            const bool write_final = p.direct != 0;
+
+            // ---- per-thread row bounds: Q rows 8 n + 2 tq + j of the task
+            uint32_t lo[NQ][2], hi[NQ][2];
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t row = 8 * n + 2 * tq + j;
+                    const uint32_t row_tok = row / p.heads_per_task;
+                    const uint32_t row_head = row % p.heads_per_task;
+                    lo[n][j] = 0;
+                    hi[n][j] = 0xffffffffu;  // rows that hold nothing are never published: left unmasked
+                    if (row_tok < t_num_toks && row_head < t_num_heads) {
+                        uint32_t vb = 0, ve = 0xffffffffu;
+                        if (p.visible != nullptr) {
+                            vb = ts->visible[row_tok * 2];
+                            ve = ts->visible[row_tok * 2 + 1];
+                        }
+                        lo[n][j] = max(vb, t_kv_begin);
+                        hi[n][j] = min(ve, t_kv_end);
+                        if (hi[n][j] < lo[n][j]) hi[n][j] = lo[n][j];
+                    }
+                }
+            }
+            if (!(t_carry & 1u)) {
+#pragma unroll
+                for (int c = 0; c < DK; ++c)
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
+#pragma unroll
+                for (int n = 0; n < NQ; ++n) {
+                    m_run[n][0] = m_run[n][1] = -INFINITY;
+                    l_run[n][0] = l_run[n][1] = 0.0f;
+                }
+            }
+
+            // ---- Q as the B operand of K Q^T, under K's head-dim permutation: for contraction step kk thread
+            // (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g (two f16 pairs)
+            const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes);
+            uint32_t qb[NQ][DK][2];
+            {
+#pragma unroll
+                for (int n = 0; n < NQ; ++n) {
+                    const uint32_t row = 8 * n + g;
+#pragma unroll
+                    for (int kk = 0; kk < DK; ++kk) {
+                        const uint32_t chunk = (2 * (kk & 3) + (tq >> 1)) ^ (row & 7);
+                        const uint32_t addr = q_tile + (kk >> 2) * (G::kQRows * 128) + row * 128 + (chunk << 4) + 8 * (tq & 1);
+                        uint32_t w0, w1;
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(addr));
+                        qb[n][kk][0] = q_pair_to_f16x2<T>(w0);
+                        qb[n][kk][1] = q_pair_to_f16x2<T>(w1);
+                    }
+                }
+            }
+
+            for (; my_stage < stage_counter + t_num_tiles; my_stage += CW) {
+                const uint32_t tile = my_stage - stage_counter;
+                const uint32_t slot = my_slot;
+                const uint32_t phase = my_parity;
+                my_slot += CW;
+                if (my_slot >= uint32_t(NS)) {
+                    my_slot -= NS;
+                    my_parity ^= 1;
+                }
+                if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p)) continue;
+                if (debug_bits(p) & 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
+                    continue;
+                }
+                const uint32_t tile_tok = t_tile_begin + tile * ST;
+                const uint32_t stage_base = smem_addr(ring + slot * G::kStageBytes);
+
+                // Rows of tokens at or past kv_end may hold anything (the tail of a page, or nothing was copied):
+                // clear them in V so that a zero probability times a NaN code cannot produce NaN.
+                if (tile_tok + ST > t_kv_end) {
+                    const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0u;
+                    constexpr uint32_t kChunksPerRow = D / 16;
+                    for (uint32_t idx = first_bad * kChunksPerRow + lane; idx < uint32_t(ST) * kChunksPerRow; idx += 32) {
+                        const uint32_t r = idx / kChunksPerRow, c = idx % kChunksPerRow;
+                        const uint32_t addr = stage_base + (r / 16) * G::kCopyBytes + G::kPlaneBoxBytes +
+                                              (c >> 3) * G::kBoxBytes + (r % 16) * 128 + (c & 7) * 16;
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+                    }
+                    __syncwarp();
+                }
+
+                // ---- S^T = K Q^T (raw dot products; the softmax scale is folded into the exponent below)
+                float s[MTK][NQ][4];
+#pragma unroll
+                for (int mt = 0; mt < MTK; ++mt)
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n) s[mt][n][0] = s[mt][n][1] = s[mt][n][2] = s[mt][n][3] = 0.0f;
+#pragma unroll
+                for (int mt = 0; mt < MTK; ++mt) {
+                    const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+#pragma unroll
+                    for (int kk = 0; kk < DK; kk += 2) {
+                        uint32_t r[4];
+                        ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t a[4];
+                            a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                            a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                            a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                            a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+#pragma unroll
+                            for (int n = 0; n < NQ; ++n) {
+                                mma_16816<__half>(s[mt][n], a, qb[n][kk + h][0], qb[n][kk + h][1]);
+                            }
+                        }
+                    }
+                }
+
+                // ---- mask (only where a row's visible range cuts the stage) and running maximum
+                bool cut = false;
+#pragma unroll
+                for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) cut = cut || tile_tok < lo[n][j] || tile_tok + ST > hi[n][j];
+                if (__any_sync(0xffffffffu, cut)) {
+#pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt)
+#pragma unroll
+                        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t tok = tile_tok + 16 * mt + sig + 2 * (e >> 1);
+                                if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
+                            }
+                }
+                float alpha[NQ][2], shift[NQ][2];
+                bool rescale = false;
+#pragma unroll
+                for (int n = 0; n < NQ; ++n) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float tile_max = fmaxf(s[0][n][j], s[0][n][j + 2]);
+#pragma unroll
+                        for (int mt = 1; mt < MTK; ++mt) tile_max = fmaxf(tile_max, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
+                        // the row's tokens are spread over the eight row groups of the warp
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+                        const float m_new = fmaxf(m_run[n][j], tile_max);
+                        const float base = m_new == -INFINITY ? 0.0f : m_new;
+                        alpha[n][j] = m_run[n][j] == -INFINITY ? 1.0f : fast_exp2((m_run[n][j] - base) * p.scale_log2e);
+                        shift[n][j] = -base * p.scale_log2e;
+                        m_run[n][j] = m_new;
+                        rescale = rescale || alpha[n][j] != 1.0f;
+                    }
+                }
+                if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+                    for (int c = 0; c < DK; ++c)
+#pragma unroll
+                        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n) {
+                        l_run[n][0] *= alpha[n][0];
+                        l_run[n][1] *= alpha[n][1];
+                    }
+                }
+
+                // ---- P^T as the B operand of V^T P^T: exponentials, packed f16 pairs (rows 2 tq, 2 tq + 1 of one
+                // token), transposed across the warp so that thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of row g
+                uint32_t pb[MTK][NQ][2];
+#pragma unroll
+                for (int mt = 0; mt < MTK; ++mt) {
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n) {
+                        float pv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
+                        l_run[n][0] += pv[0] + pv[2];
+                        l_run[n][1] += pv[1] + pv[3];
+                        pb[mt][n][0] = movmatrix_trans(pack_f16x2(pv[0], pv[1]));
+                        pb[mt][n][1] = movmatrix_trans(pack_f16x2(pv[2], pv[3]));
+                    }
+                }
+
+                // ---- O^T += V^T P^T
+#pragma unroll
+                for (int mt = 0; mt < MTK; ++mt) {
+                    const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
+#pragma unroll
+                    for (int c = 0; c < DK; c += 2) {
+                        uint32_t r[4];
+                        ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t a[4];
+                            a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                            a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                            a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                            a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+#pragma unroll
+                            for (int n = 0; n < NQ; ++n) mma_16816<__half>(o[c + h][n], a, pb[mt][n][0], pb[mt][n][1]);
+                        }
+                    }
+                }
+
+                // ---- release the stage
+                if (tile_tok + ST > t_kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
+            }
+            stage_counter += t_num_tiles;
+
+            if (t_carry & 2u) {
+                // The next task of this CTA continues these rows: nothing is merged or published now. This task's
+                // template still gets a partial, an empty one (weight zero in every merge).
+                if (warp == 0 && g == 0) {
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t row = 8 * n + 2 * tq + j;
+                            const uint32_t row_tok = row / p.heads_per_task;
+                            const uint32_t row_head = row % p.heads_per_task;
+                            if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
+                            const uint64_t index =
+                                (uint64_t(t_tmpl) * p.num_q_heads + t_head_begin + row_head) * p.max_q_tokens + row_tok;
+                            p.partial_sum[index] = 0.0f;
+                            p.partial_max[index] = -INFINITY;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+                continue;
+            }
+
+            // ---- task end: every warp parks (max, sum, O^T) of its share of the stages, then every thread merges
+            // and publishes a slice of the rows. Row sums first: a row's tokens are spread over the row groups.
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 4);
+                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 8);
+                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 16);
+                }
+            }
+            bool merge_ok = true;
+            if (merges > 0) merge_ok = mbar_wait(merged_bar, (merges - 1) & 1, abort_flag, p);  // parked states are free
+            if (merge_ok) {
+#pragma unroll
+                for (int c = 0; c < DK; ++c)
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            my_park[(8 * n + 2 * tq + (e & 1)) * RS + 16 * c + g + 8 * (e >> 1)] = o[c][n][e];
+                        }
+                if (g == 0) {
+#pragma unroll
+                    for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            my_park[G::kQRows * RS + 8 * n + 2 * tq + j] = m_run[n][j];
+                            my_park[G::kQRows * RS + G::kQRows + 8 * n + 2 * tq + j] = l_run[n][j];
+                        }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(parked_bar);
+                merge_ok = mbar_wait(parked_bar, merges & 1, abort_flag, p);
+            }
+            if (merge_ok) {
+                constexpr uint32_t kVecs = D / 4;
+                const uint32_t tid = warp * 32 + lane;
+                for (uint32_t idx = tid; idx < uint32_t(G::kQRows) * kVecs; idx += CW * 32) {
+                    const uint32_t row = idx / kVecs, d = (idx % kVecs) * 4;
+                    const uint32_t row_tok = row / p.heads_per_task;
+                    const uint32_t row_head = row % p.heads_per_task;
+                    if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
+                    float m_max = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) m_max = fmaxf(m_max, merge[w * G::kParkFloats + G::kQRows * RS + row]);
+                    const float base = m_max == -INFINITY ? 0.0f : m_max;
+                    float l_sum = 0.0f;
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) {
+                        const float* park = merge + w * G::kParkFloats;
+                        const float m_w = park[G::kQRows * RS + row];
+                        const float weight = m_w == -INFINITY ? 0.0f : fast_exp2((m_w - base) * p.scale_log2e);
+                        l_sum += park[G::kQRows * RS + G::kQRows + row] * weight;
+                        const float4 v = *reinterpret_cast<const float4*>(park + row * RS + d);
+                        acc.x += weight * v.x;
+                        acc.y += weight * v.y;
+                        acc.z += weight * v.z;
+                        acc.w += weight * v.w;
+                    }
+                    const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+                    acc.x *= inv;
+                    acc.y *= inv;
+                    acc.z *= inv;
+                    acc.w *= inv;
+                    const uint32_t head = t_head_begin + row_head;
+                    if (write_final) {
+                        T* dst = reinterpret_cast<T*>(p.out) + (uint64_t(t_tok_begin + row_tok) * p.num_q_heads + head) * D + d;
+                        store_out4<T>(dst, acc);
+                    } else {
+                        const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
+                        *reinterpret_cast<float4*>(p.partial_out + index * D + d) = acc;
+                        if (d == 0) {
+                            p.partial_sum[index] = l_sum;
+                            // the running maximum is a raw dot product; publish the natural-log-domain logit
+                            p.partial_max[index] = l_sum > 0.0f ? m_max * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(merged_bar);
+                ++merges;
+            }
+            // ---- hand the task slot (descriptor + Q rows) back to the producer
+            __syncwarp();
+            if (lane == 0) mbar_arrive(task_empty_bar + 8 * tslot);
+        }
+    }
+    __syncthreads();
+}
+
+}  // namespace kh
