@@ -18,6 +18,7 @@
 #include "map_instance.h"
 #include "sdpa_map.cuh"
 #include "sdpa_tc.cuh"
+#include "sdpa_tm.cuh"
 
 namespace kh {
 
@@ -205,9 +206,27 @@ static MapInstance make_tc_instance() {
     return MapInstance{sdpa_tc_kernel<T, D, P>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows, G::kStages};
 }
 
+// Token-major instance over 16-bit pages (sdpa_tm.cuh): the KV tokens on the M side of the tiles, warp pairs that
+// split the head dimension.
+template <typename T, int D, int P, int NQ, int CW, int DS>
+static MapInstance make_tm_instance() {
+    using G = TmGeometry<D, P, NQ, CW, DS, 2>;
+    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, DS, 2>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
+                       G::kStages};
+}
+
 template <typename T, int D, int P>
 static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     constexpr int PS = 1;
+    // Verify tiles of 17-32 rows (four tokens x six or eight heads): token-major, every K/V fragment loaded once
+    // for all rows. `tensor_memory` is false for the one-launch map + reduce form, which this kernel does not have.
+    if constexpr (P == 16) {
+        // (head_dim 256: six consumer warps, because eight warps per block leave a thread 255 registers, ten only 168)
+        if (tensor_memory && rows > 16 && rows <= 24) return make_tm_instance<T, D, P, 3, D == 256 ? 6 : 8, 2>();
+        if constexpr (D == 128) {
+            if (tensor_memory && rows > 24 && rows <= 32) return make_tm_instance<T, D, P, 4, 6, 2>();
+        }
+    }
     if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();
     if (rows <= 16) return make_instance<T, D, P, 1, 4, PS, false>();
     // 17-24 rows (verify of four tokens with a group of six heads): three half tiles; the same tensor-core work as

@@ -9,6 +9,11 @@
 #include "map_instance.h"
 #include "sdpa_tm.cuh"
 
+// Consumer warps of the token-major decode instance (eight: two per scheduler).
+#ifndef KH_TM_CONSUMER_WARPS
+#define KH_TM_CONSUMER_WARPS 8
+#endif
+
 namespace kh {
 
 template <typename T, int D, int P, int MT, int KVW, bool HALF, int PS = 1>
@@ -19,10 +24,10 @@ static MapInstance make_fp8_instance() {
 }
 
 // Token-major instance (sdpa_tm.cuh): the raw bytes are consumed from the copied stage, no decode warps.
-template <typename T, int D, int P, int NQ, int CW>
+template <typename T, int D, int P, int NQ, int CW, int DS>
 static MapInstance make_tm_instance() {
-    using G = TmGeometry<D, P, NQ, CW>;
-    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
+    using G = TmGeometry<D, P, NQ, CW, DS, 1>;
+    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, DS, 1>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
                        G::kStages};
 }
 
@@ -35,10 +40,18 @@ template <typename T, int D, int P>
 static MapInstance pick_fp8_rows(uint32_t rows, bool one_launch) {
     // Decode and short verify tasks take the token-major kernel; the one-launch map + reduce form (arrival
     // counters) exists in the decode-warp kernel only.
+    // Tasks of up to 32 rows (24 at head_dim 256) take the token-major kernel; wider accumulators are shared by
+    // warp pairs that split the head dimension.
     if (!one_launch) {
-        if (rows <= 8) return make_tm_instance<T, D, P, 1, 8>();
+        if (rows <= 8) return make_tm_instance<T, D, P, 1, KH_TM_CONSUMER_WARPS, 1>();
         if constexpr (D == 128) {
-            if (rows <= 16) return make_tm_instance<T, D, P, 2, 8>();
+            if (rows <= 16) return make_tm_instance<T, D, P, 2, 8, 1>();
+            if (rows <= 24) return make_tm_instance<T, D, P, 3, 8, 2>();
+            if (rows <= 32) return make_tm_instance<T, D, P, 4, 6, 2>();
+        } else {
+            // (six consumer warps: eight warps per block leave a thread 255 registers, ten only 168)
+            if (rows <= 16) return make_tm_instance<T, D, P, 2, 8, 2>();
+            if (rows <= 24) return make_tm_instance<T, D, P, 3, 6, 2>();
         }
     }
     if constexpr (D == 128) {

@@ -1,14 +1,21 @@
-// Map / direct kernel for K/V pages of FP8 E4M3FN elements, "token-major" form: the KV tokens of a stage are the
-// M dimension of the warp-level tensor-core tiles and the task's Q rows - (Q tokens of the range) x (Q heads of
-// the KV group), at most 32 - are the N dimension (8 rows per n-tile).
+// Map / direct kernel in "token-major" form: the KV tokens of a stage are the M dimension of the warp-level
+// tensor-core tiles and the task's Q rows - (Q tokens of the range) x (Q heads of the KV group), at most 32 - are
+// the N dimension (8 rows per n-tile).
 //
-//   S^T = K Q^T   m16n8k16, A = 16 KV tokens x 16 head-dim elements, B = the Q rows.
+//   S^T = K Q^T     m16n8k16, A = 16 KV tokens x 16 head-dim elements, B = the Q rows.
 //   O^T += V^T P^T  m16n8k16, A = 16 head-dim elements x 16 KV tokens, B = the probabilities.
 //
-// Why this form for one-byte pages. The pages are the reference's cache format (one byte per stored element, one
-// unit scale; components/gqa/sdpa/sliced_kv.rs:113-125, decoded on load by metal/gqa_fp8.metal:1-25). At the HBM
-// rate a one-byte page delivers twice the tokens per second of a 16-bit page, so everything per token has to
-// cost half as much:
+// With the tokens on M a decode task (8 rows) costs one MMA per 16 tokens x 16 head-dim elements instead of two
+// half-empty ones, every K/V fragment is loaded (and, for one-byte pages, converted) once for all Q rows of the
+// task, and a thread's accumulator is D/16 x (rows/8) x 4 registers, small enough for eight consumer warps per SM.
+// Tasks whose accumulator would still be too wide (24-32 rows, or head_dim 256 with more than 8 rows) are run by
+// warp PAIRS that split the head dimension (DS = 2): each warp of a pair contracts K Q^T over its half of the head
+// dimension, the two exchange their partial scores through shared memory, both run the (cheap) softmax on the full
+// scores and each accumulates its half of the output columns.
+//
+// K/V pages of FP8 E4M3FN elements (KVB = 1; the reference's cache format: one byte per stored element, one unit
+// scale; components/gqa/sdpa/sliced_kv.rs:113-125, decoded on load by metal/gqa_fp8.metal:1-25). At the HBM rate a
+// one-byte page delivers twice the tokens per second of a 16-bit page, so everything per token has to cost half:
 //  - The raw bytes are consumed straight from the copied stage, with no intermediate 16-bit copy in shared memory:
 //    K through ldmatrix as if the bytes were 16-bit pairs (a thread receives four consecutive head-dim elements of
 //    one token), V through the 8-bit transposing matrix load (ldmatrix .m16n16 .trans .b8: a thread receives four
@@ -21,10 +28,10 @@
 //  - Conversion is one instruction per element pair (cvt.rn.f16x2.e4m3x2, exact; the NaN codes become NaN) and the
 //    MMAs run in f16 whatever the Q/output type: every E4M3 value is an f16 value, bf16 Q values convert exactly
 //    inside f16's range (beyond it they saturate), and f16 probabilities carry 11 significant bits.
-//  - With the tokens on M, a decode task (8 rows) costs one MMA per 16 tokens x 16 head-dim elements instead of two
-//    half-empty ones, and each K/V fragment is loaded once for all Q rows of the task.
-//  - A thread's accumulator is D/16 x (rows/8) x 4 registers (32 for decode at head_dim 128), so eight consumer
-//    warps fit an SM and hide one another's ldmatrix, MMA and MUFU latencies.
+// K/V pages of 16-bit elements (KVB = 2): K through ldmatrix, V through ldmatrix .trans, in natural order; the MMAs
+// run in the Q/output type, and bf16 probabilities carry their rounding remainder in a second MMA (a bf16
+// probability alone costs up to 2^-9 of |p v| per term, which short contexts turn into errors beyond 2e-3).
+//
 // Task ABI, task warp, stream warp, rings and partial-state layout are those of sdpa_map_kernel (sdpa_map.cuh).
 // Synchronisation between the consumer warps goes through mbarriers with bounded waits only.
 #pragma once
@@ -33,41 +40,55 @@
 
 namespace kh {
 
-// D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps.
-template <int D, int P, int NQ, int CW>
+// D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps. DS: warps that
+// share a stage by splitting the head dimension (1 or 2). KVB: bytes of a stored K/V element.
+template <int D, int P, int NQ, int CW, int DS, int KVB>
 struct TmGeometry {
     static_assert(P == 16, "the token-major kernel is built for 16-token pages (one page = one 16-token MMA tile)");
     static_assert(D == 128 || D == 256, "head_dim 128 or 256");
+    static_assert(KVB == 1 || KVB == 2, "K/V elements are stored in one or two bytes");
+    static_assert(DS == 1 || DS == 2, "a stage is shared by at most two warps");
+    static_assert(CW % DS == 0, "consumer warps come in groups of DS");
     static constexpr int kStageTokens = (D == 128) ? 32 : 16;
     static constexpr int kBoxRows = P;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;   // pages per stage
-    static constexpr int kColumnGroups = D / 128;                     // 128-byte lines per stored row
+    static constexpr int kLineElems = 128 / KVB;                      // stored elements of a 128-byte line
+    static constexpr int kColumnGroups = D / kLineElems;              // 128-byte lines per stored row
     static constexpr int kBoxBytes = kBoxRows * 128;                  // one column group of one page
     static constexpr int kPlaneBoxBytes = kColumnGroups * kBoxBytes;  // K (or V) rows of one page
     static constexpr int kCopyBytes = 2 * kPlaneBoxBytes;             // one TMA copy: K and V of one (page, KV head)
-    static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;   // 8 KiB
+    static constexpr int kStageBytes = kBoxesPerPlane * kCopyBytes;   // 8 KiB (one-byte pages) or 16 KiB
     static constexpr int kColumnHalves = D / 64;                      // Q tile: 64-element column halves (16-bit)
     static constexpr int kQRows = NQ * 8;
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;
     static constexpr int kConsumerWarps = CW;
+    static constexpr int kGroups = CW / DS;                           // warp groups; a stage goes to one group
     static constexpr int kThreads = (CW + 2) * 32;                    // + stream warp + task warp
     static constexpr int kRowStride = D + 4;                          // floats; makes the parking stores conflict free
-    static constexpr int kParkFloats = kQRows * kRowStride + 2 * kQRows;  // O rows, then (max, sum) per row
-    static constexpr int kMergeBytes = CW * kParkFloats * 4;
+    static constexpr int kParkFloats = kQRows * kRowStride + 4 * kQRows;  // O rows, then two sets of (max, sum) per row
+    // Task-end merge of the groups' states through shared memory: one parking slot per group, or - where that would
+    // take the stage ring's memory - half as many slots in two rounds (the second half of the groups folds its
+    // state into the slots the first half parked)
+    static constexpr bool kTwoRounds = kGroups >= 3 && kGroups * kParkFloats * 4 > 64 * 1024;
+    static constexpr int kSlots = kTwoRounds ? (kGroups + 1) / 2 : kGroups;
+    static constexpr int kMergeBytes = kSlots * kParkFloats * 4;
+    static constexpr int kScoreFloats = (kStageTokens / 16) * NQ * 4;    // a thread's scores of one stage
+    // partial scores a warp hands its partner: [stage parity][warp of the pair][score][lane]
+    static constexpr int kExchangeBytes = (DS == 2) ? kGroups * 2 * 2 * kScoreFloats * 32 * 4 : 0;
     static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
-    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 1024;
+    static constexpr int kFixedBytes =
+        kTaskSlots * kQBytes + kMergeBytes + kExchangeBytes + kPidBytes + kTaskBytes + 1024;
     static constexpr int kSmemLimit = 227 * 1024 - 1024;
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
     static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
-    static constexpr int kStages = kStagesCapped / CW * CW;          // a ring slot always belongs to the same warp
+    static constexpr int kStages = kStagesCapped / kGroups * kGroups;  // a ring slot always belongs to the same group
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
-    static constexpr int kPagesPerStage = kBoxesPerPlane;
-    // Q fragments of a task stay in registers for the whole task
-    static constexpr bool kQInRegisters = NQ * (D / 16) * 2 <= 32;
-    static_assert(kStages >= CW && kStages >= 4, "shared memory ring too small");
-    static_assert(kQInRegisters, "this build keeps a task's Q fragments in registers (at most 16 rows at head_dim 128, 8 at 256)");
+    // Q fragments of a task stay in registers for the whole task (each warp holds those of its head-dim share)
+    static constexpr int kQFragmentRegs = NQ * (D / 16 / DS) * 2;
+    static_assert(kStages >= kGroups && kStages >= 4, "shared memory ring too small");
+    static_assert(kQFragmentRegs <= 48, "the task's Q fragments must fit registers");
     static_assert(NQ >= 1 && NQ <= 4, "a task holds at most 32 Q rows here");
 };
 
@@ -106,26 +127,34 @@ __device__ __forceinline__ uint32_t q_pair_to_f16x2<__nv_bfloat16>(uint32_t pack
     return pack_f16x2(lo, hi);
 }
 
-template <typename T, int D, int P, int NQ, int CW>
-__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW>::kThreads, 1)
+template <typename T, int D, int P, int NQ, int CW, int DS, int KVB>
+__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW, DS, KVB>::kThreads, 1)
 sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
-    using G = TmGeometry<D, P, NQ, CW>;
+    using G = TmGeometry<D, P, NQ, CW, DS, KVB>;
+    // the element type the MMAs run in: f16 over one-byte pages, the Q/output type over 16-bit pages
+    using M = std::conditional_t<KVB == 1, __half, T>;
+    constexpr bool kRemainder = KVB == 2 && std::is_same<T, __nv_bfloat16>::value;  // P V carries P's rounding remainder
     constexpr int ST = G::kStageTokens;
     constexpr int NS = G::kStages;
     constexpr int TQ = G::kTaskSlots;
-    constexpr int MTK = ST / 16;  // 16-token tiles (pages) per stage
-    constexpr int DK = D / 16;    // contraction steps of K Q^T = 16-element m-tiles of O^T
+    constexpr int NG = G::kGroups;
+    constexpr int MTK = ST / 16;      // 16-token tiles (pages) per stage
+    constexpr int DK = D / 16;        // contraction steps of K Q^T = 16-element m-tiles of O^T
+    constexpr int DKW = DK / DS;      // ... of which a warp takes this many
     constexpr int RS = G::kRowStride;
+    constexpr int SF = G::kScoreFloats;
+    static_assert(DKW % 2 == 0, "a warp takes an even number of 16-element steps");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
     uint8_t* q_ring = ring + NS * G::kStageBytes;
     float* merge = reinterpret_cast<float*>(q_ring + TQ * G::kQBytes);
-    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
+    float* exchange = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
+    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(exchange) + G::kExchangeBytes);
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
-    constexpr int kNumBars = 2 * NS + 3 * TQ + 2;
+    constexpr int kNumBars = 2 * NS + 3 * TQ + 3 + NG;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
     uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 2;
 
@@ -138,11 +167,13 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t stream_full_bar = smem_addr(bars + 2 * NS + 2 * TQ);
     const uint32_t parked_bar = smem_addr(bars + 2 * NS + 3 * TQ);      // every consumer warp parked its state
     const uint32_t merged_bar = smem_addr(bars + 2 * NS + 3 * TQ + 1);  // every consumer warp read the parked states
+    const uint32_t folded_bar = smem_addr(bars + 2 * NS + 3 * TQ + 2);  // second merge round: every warp folded its state
+    const uint32_t exchange_bar = smem_addr(bars + 2 * NS + 3 * TQ + 3);  // [NG] both warps of a pair wrote their scores
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, DS);
         }
         for (int s = 0; s < TQ; ++s) {
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
@@ -151,6 +182,8 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         }
         mbar_init(parked_bar, CW);
         mbar_init(merged_bar, CW);
+        mbar_init(folded_bar, CW);
+        for (int s = 0; s < NG; ++s) mbar_init(exchange_bar + 8 * s, DS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -193,27 +226,32 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // ------------------------------ consumer warps ----------------------------------------
         const int g = lane >> 2;   // fragment row group
         const int tq = lane & 3;   // thread in quad
-        // Row r (0-7) of a 16-token MMA tile is token 4 * (r / 2) + r % 2 of its page, row r + 8 is that token + 2:
-        // a thread's accumulator pair (rows g, g + 8) then holds tokens t and t + 2, and after the transposition of
-        // the packed probabilities thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of Q row g - the four consecutive
-        // tokens the 8-bit transposing load of V gives it.
-        const uint32_t sig = 4u * (g >> 1) + (g & 1);
-        // K: ldmatrix .x4 of raw bytes; matrix (lane >> 3): bit 0 picks the row half (tokens +2), bit 1 the next
-        // 16-byte chunk (= the next 16 head-dim elements)
+        const int group = warp / DS;   // which stages this warp works on
+        const int half = warp % DS;    // which share of the head dimension
+        // One-byte pages: row r (0-7) of a 16-token MMA tile is token 4 * (r / 2) + r % 2 of its page, row r + 8 is
+        // that token + 2: a thread's accumulator pair (rows g, g + 8) then holds tokens t and t + 2, and after the
+        // transposition of the packed probabilities thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of Q row g - the
+        // four consecutive tokens the 8-bit transposing load of V gives it. 16-bit pages: natural order.
+        const uint32_t sig = KVB == 1 ? 4u * (g >> 1) + (g & 1) : uint32_t(g);
+        constexpr uint32_t kUpperRow = KVB == 1 ? 2u : 8u;  // token distance between fragment rows g and g + 8
+        // K: ldmatrix .x4. One-byte pages: matrix (lane >> 3) bit 0 picks the row half (tokens + 2), bit 1 the next
+        // 16-byte chunk (= the next 16 head-dim elements). 16-bit pages: bit 0 picks rows 8-15, bit 1 the upper 8
+        // elements of the 16-element step.
         const uint32_t k_mat = lane >> 3, k_r = lane & 7;
-        const uint32_t k_tok = 4u * (k_r >> 1) + (k_r & 1) + 2u * (k_mat & 1);
+        const uint32_t k_tok = KVB == 1 ? 4u * (k_r >> 1) + (k_r & 1) + 2u * (k_mat & 1) : k_r + 8u * (k_mat & 1);
         const uint32_t k_lane = k_tok * 128u;
         const uint32_t k_y4 = ((k_mat >> 1) ^ (k_tok & 7)) << 4;
-        // V: ldmatrix .m16n16 .x2 .trans of raw bytes; lanes 0-15 address the 16 token rows of one 16-byte chunk,
-        // lanes 16-31 those of the next chunk
-        const uint32_t v_tok = lane & 15;
+        // V. One-byte pages: ldmatrix .m16n16 .x2 .trans; lanes 0-15 address the 16 token rows of one 16-byte chunk,
+        // lanes 16-31 those of the next chunk. 16-bit pages: ldmatrix .x4 .trans; matrix bit 0 picks the upper 8
+        // elements of a 16-element m-tile, bit 1 tokens 8-15.
+        const uint32_t v_tok = KVB == 1 ? uint32_t(lane & 15) : k_r + 8u * (k_mat >> 1);
         const uint32_t v_lane = v_tok * 128u;
-        const uint32_t v_y4 = ((uint32_t(lane) >> 4) ^ (v_tok & 7)) << 4;
+        const uint32_t v_y4 = ((KVB == 1 ? uint32_t(lane) >> 4 : (k_mat & 1)) ^ (v_tok & 7)) << 4;
 
-        float o[DK][NQ][4];
+        float o[DKW][NQ][4];
         float m_run[NQ][2], l_run[NQ][2];
 #pragma unroll
-        for (int c = 0; c < DK; ++c)
+        for (int c = 0; c < DKW; ++c)
 #pragma unroll
             for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
@@ -222,9 +260,14 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             l_run[n][0] = l_run[n][1] = 0.0f;
         }
         uint32_t stage_counter = 0;
-        uint32_t my_stage = warp, my_slot = warp, my_parity = 0;
-        uint32_t merges = 0;  // merges this CTA has run (phase of the two merge barriers)
-        float* const my_park = merge + warp * G::kParkFloats;
+        uint32_t my_stage = group, my_slot = group, my_parity = 0;
+        uint32_t my_stages_done = 0;  // stages this group has worked on (phase of its exchange barrier)
+        uint32_t merges = 0;          // merges this CTA has run (phase of the two merge barriers)
+        constexpr int NSLOT = G::kSlots;
+        const int merge_round = G::kTwoRounds ? group / NSLOT : 0;  // which merge round this warp writes in
+        float* const my_park = merge + (group % NSLOT) * G::kParkFloats;
+        float* const my_stats = my_park + G::kQRows * RS + merge_round * 2 * G::kQRows;
+        float* const my_exchange = exchange + group * (2 * 2 * SF * 32);
 
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
@@ -263,7 +306,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             }
             if (!(t_carry & 1u)) {
 #pragma unroll
-                for (int c = 0; c < DK; ++c)
+                for (int c = 0; c < DKW; ++c)
 #pragma unroll
                     for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
@@ -273,35 +316,45 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 }
             }
 
-            // ---- Q as the B operand of K Q^T, under K's head-dim permutation: for contraction step kk thread
-            // (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g (two f16 pairs)
+            // ---- Q as the B operand of K Q^T for this warp's contraction steps. One-byte pages: under K's head-dim
+            // permutation, thread (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g as two f16 pairs.
+            // 16-bit pages: the natural fragment, elements 16 kk + 2 tq, + 1 and 16 kk + 8 + 2 tq, + 1.
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes);
-            uint32_t qb[NQ][DK][2];
-            {
+            uint32_t qb[NQ][DKW][2];
 #pragma unroll
-                for (int n = 0; n < NQ; ++n) {
-                    const uint32_t row = 8 * n + g;
+            for (int n = 0; n < NQ; ++n) {
+                const uint32_t row = 8 * n + g;
 #pragma unroll
-                    for (int kk = 0; kk < DK; ++kk) {
+                for (int k = 0; k < DKW; ++k) {
+                    const int kk = half * DKW + k;
+                    const uint32_t row_addr = q_tile + (kk >> 2) * (G::kQRows * 128) + row * 128;
+                    if constexpr (KVB == 1) {
                         const uint32_t chunk = (2 * (kk & 3) + (tq >> 1)) ^ (row & 7);
-                        const uint32_t addr = q_tile + (kk >> 2) * (G::kQRows * 128) + row * 128 + (chunk << 4) + 8 * (tq & 1);
                         uint32_t w0, w1;
-                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(addr));
-                        qb[n][kk][0] = q_pair_to_f16x2<T>(w0);
-                        qb[n][kk][1] = q_pair_to_f16x2<T>(w1);
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
+                                     : "=r"(w0), "=r"(w1)
+                                     : "r"(row_addr + (chunk << 4) + 8 * (tq & 1)));
+                        qb[n][k][0] = q_pair_to_f16x2<T>(w0);
+                        qb[n][k][1] = q_pair_to_f16x2<T>(w1);
+                    } else {
+                        const uint32_t c0 = (2 * (kk & 3)) ^ (row & 7), c1 = (2 * (kk & 3) + 1) ^ (row & 7);
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][k][0]) : "r"(row_addr + (c0 << 4) + 4 * tq));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][k][1]) : "r"(row_addr + (c1 << 4) + 4 * tq));
                     }
                 }
             }
 
-            for (; my_stage < stage_counter + t_num_tiles; my_stage += CW) {
+            for (; my_stage < stage_counter + t_num_tiles; my_stage += NG) {
                 const uint32_t tile = my_stage - stage_counter;
                 const uint32_t slot = my_slot;
                 const uint32_t phase = my_parity;
-                my_slot += CW;
+                my_slot += NG;
                 if (my_slot >= uint32_t(NS)) {
                     my_slot -= NS;
                     my_parity ^= 1;
                 }
+                const uint32_t exchange_phase = my_stages_done & 1;
+                ++my_stages_done;
                 if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p)) continue;
                 if (debug_bits(p) & 1) {
                     __syncwarp();
@@ -312,14 +365,16 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t stage_base = smem_addr(ring + slot * G::kStageBytes);
 
                 // Rows of tokens at or past kv_end may hold anything (the tail of a page, or nothing was copied):
-                // clear them in V so that a zero probability times a NaN code cannot produce NaN.
+                // clear them in V (this warp's share of the columns) so that a zero probability times a NaN cannot
+                // produce NaN.
                 if (tile_tok + ST > t_kv_end) {
                     const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0u;
-                    constexpr uint32_t kChunksPerRow = D / 16;
+                    constexpr uint32_t kChunksPerRow = D * KVB / 16 / DS;  // 16-byte chunks of this warp's columns
                     for (uint32_t idx = first_bad * kChunksPerRow + lane; idx < uint32_t(ST) * kChunksPerRow; idx += 32) {
-                        const uint32_t r = idx / kChunksPerRow, c = idx % kChunksPerRow;
+                        const uint32_t r = idx / kChunksPerRow, c = half * kChunksPerRow + idx % kChunksPerRow;
+                        // (chunk c of row r sits at position c ^ (r & 7) of its 128-byte line)
                         const uint32_t addr = stage_base + (r / 16) * G::kCopyBytes + G::kPlaneBoxBytes +
-                                              (c >> 3) * G::kBoxBytes + (r % 16) * 128 + (c & 7) * 16;
+                                              (c >> 3) * G::kBoxBytes + (r % 16) * 128 + (((c & 7) ^ (r & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
@@ -334,23 +389,54 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 #pragma unroll
                 for (int mt = 0; mt < MTK; ++mt) {
                     const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+                    if constexpr (KVB == 1) {
 #pragma unroll
-                    for (int kk = 0; kk < DK; kk += 2) {
-                        uint32_t r[4];
-                        ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
+                        for (int k = 0; k < DKW; k += 2) {
+                            const int kk = half * DKW + k;  // 16-byte chunk kk of the row = elements 16 kk .. + 15
+                            uint32_t r[4];
+                            ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            uint32_t a[4];
-                            a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                            a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                            a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                            a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t a[4];
+                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
 #pragma unroll
-                            for (int n = 0; n < NQ; ++n) {
-                                mma_16816<__half>(s[mt][n], a, qb[n][kk + h][0], qb[n][kk + h][1]);
+                                for (int n = 0; n < NQ; ++n) mma_16816<M>(s[mt][n], a, qb[n][k + h][0], qb[n][k + h][1]);
                             }
                         }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < DKW; ++k) {
+                            const int kk = half * DKW + k;  // elements 16 kk .. + 15 = 16-byte chunks 2 kk, 2 kk + 1
+                            uint32_t a[4];
+                            ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
+#pragma unroll
+                            for (int n = 0; n < NQ; ++n) mma_16816<M>(s[mt][n], a, qb[n][k][0], qb[n][k][1]);
+                        }
                     }
+                }
+                if constexpr (DS == 2) {
+                    // hand the partial scores to the partner and add the partner's (addition commutes: both warps
+                    // end with the same bits)
+                    float* mine = my_exchange + (exchange_phase * 2 + half) * (SF * 32);
+                    const float* theirs = my_exchange + (exchange_phase * 2 + (half ^ 1)) * (SF * 32);
+#pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt)
+#pragma unroll
+                        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) mine[((mt * NQ + n) * 4 + e) * 32 + lane] = s[mt][n][e];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
+                    if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
+#pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt)
+#pragma unroll
+                        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) s[mt][n][e] += theirs[((mt * NQ + n) * 4 + e) * 32 + lane];
                 }
 
                 // ---- mask (only where a row's visible range cuts the stage) and running maximum
@@ -366,7 +452,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         for (int n = 0; n < NQ; ++n)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const uint32_t tok = tile_tok + 16 * mt + sig + 2 * (e >> 1);
+                                const uint32_t tok = tile_tok + 16 * mt + sig + kUpperRow * (e >> 1);
                                 if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
                             }
                 }
@@ -393,7 +479,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 }
                 if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-                    for (int c = 0; c < DK; ++c)
+                    for (int c = 0; c < DKW; ++c)
 #pragma unroll
                         for (int n = 0; n < NQ; ++n)
 #pragma unroll
@@ -405,9 +491,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     }
                 }
 
-                // ---- P^T as the B operand of V^T P^T: exponentials, packed f16 pairs (rows 2 tq, 2 tq + 1 of one
-                // token), transposed across the warp so that thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of row g
-                uint32_t pb[MTK][NQ][2];
+                // ---- P^T as the B operand of V^T P^T: exponentials, packed 16-bit pairs (rows 2 tq, 2 tq + 1 of one
+                // token), transposed across the warp so that thread (g, tq) holds its four tokens of Q row g
+                uint32_t pb[MTK][NQ][2], pr[kRemainder ? MTK : 1][kRemainder ? NQ : 1][2];
 #pragma unroll
                 for (int mt = 0; mt < MTK; ++mt) {
 #pragma unroll
@@ -417,28 +503,49 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
                         l_run[n][0] += pv[0] + pv[2];
                         l_run[n][1] += pv[1] + pv[3];
-                        pb[mt][n][0] = movmatrix_trans(pack_f16x2(pv[0], pv[1]));
-                        pb[mt][n][1] = movmatrix_trans(pack_f16x2(pv[2], pv[3]));
+                        const uint32_t x0 = pack2<M>(pv[0], pv[1]), x1 = pack2<M>(pv[2], pv[3]);
+                        pb[mt][n][0] = movmatrix_trans(x0);
+                        pb[mt][n][1] = movmatrix_trans(x1);
+                        if constexpr (kRemainder) {
+                            const float2 r0 = unpack2<M>(x0), r1 = unpack2<M>(x1);
+                            pr[mt][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
+                            pr[mt][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
+                        }
                     }
                 }
 
-                // ---- O^T += V^T P^T
+                // ---- O^T += V^T P^T over this warp's output columns
 #pragma unroll
                 for (int mt = 0; mt < MTK; ++mt) {
                     const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
+                    if constexpr (KVB == 1) {
 #pragma unroll
-                    for (int c = 0; c < DK; c += 2) {
-                        uint32_t r[4];
-                        ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
+                        for (int k = 0; k < DKW; k += 2) {
+                            const int c = half * DKW + k;  // 16-byte chunk c = output columns 16 c .. + 15
+                            uint32_t r[4];
+                            ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t a[4];
+                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+#pragma unroll
+                                for (int n = 0; n < NQ; ++n) mma_16816<M>(o[k + h][n], a, pb[mt][n][0], pb[mt][n][1]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < DKW; ++k) {
+                            const int c = half * DKW + k;  // output columns 16 c .. + 15 = 16-byte chunks 2 c, 2 c + 1
                             uint32_t a[4];
-                            a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                            a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                            a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                            a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                            ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
 #pragma unroll
-                            for (int n = 0; n < NQ; ++n) mma_16816<__half>(o[c + h][n], a, pb[mt][n][0], pb[mt][n][1]);
+                            for (int n = 0; n < NQ; ++n) {
+                                mma_16816<M>(o[k][n], a, pb[mt][n][0], pb[mt][n][1]);
+                                if constexpr (kRemainder) mma_16816<M>(o[k][n], a, pr[mt][n][0], pr[mt][n][1]);
+                            }
                         }
                     }
                 }
@@ -474,40 +581,85 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 continue;
             }
 
-            // ---- task end: every warp parks (max, sum, O^T) of its share of the stages, then every thread merges
-            // and publishes a slice of the rows. Row sums first: a row's tokens are spread over the row groups.
+            // ---- task end: every warp parks its share of (max, sum, O^T), then every thread merges and publishes a
+            // slice of the rows. Row sums first: a row's tokens are spread over the row groups.
+            float l_row[NQ][2];
 #pragma unroll
             for (int n = 0; n < NQ; ++n) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 4);
-                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 8);
-                    l_run[n][j] += __shfl_xor_sync(0xffffffffu, l_run[n][j], 16);
+                    float l = l_run[n][j];
+                    l += __shfl_xor_sync(0xffffffffu, l, 4);
+                    l += __shfl_xor_sync(0xffffffffu, l, 8);
+                    l += __shfl_xor_sync(0xffffffffu, l, 16);
+                    l_row[n][j] = l;
                 }
             }
             bool merge_ok = true;
             if (merges > 0) merge_ok = mbar_wait(merged_bar, (merges - 1) & 1, abort_flag, p);  // parked states are free
+            auto weight_of = [&](float m, float base) {
+                return m == -INFINITY ? 0.0f : fast_exp2((m - base) * p.scale_log2e);
+            };
             if (merge_ok) {
+                if (merge_round == 0) {
 #pragma unroll
-                for (int c = 0; c < DK; ++c)
+                    for (int c = 0; c < DKW; ++c)
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n)
+                        for (int n = 0; n < NQ; ++n)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            my_park[(8 * n + 2 * tq + (e & 1)) * RS + 16 * c + g + 8 * (e >> 1)] = o[c][n][e];
-                        }
-                if (g == 0) {
+                            for (int e = 0; e < 4; ++e) {
+                                my_park[(8 * n + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1)] = o[c][n][e];
+                            }
+                }
+                if (g == 0 && half == 0) {
 #pragma unroll
                     for (int n = 0; n < NQ; ++n)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            my_park[G::kQRows * RS + 8 * n + 2 * tq + j] = m_run[n][j];
-                            my_park[G::kQRows * RS + G::kQRows + 8 * n + 2 * tq + j] = l_run[n][j];
+                            my_stats[8 * n + 2 * tq + j] = m_run[n][j];
+                            my_stats[G::kQRows + 8 * n + 2 * tq + j] = l_row[n][j];
+                            if (G::kTwoRounds && merge_round == 0 && group + NSLOT >= NG) {
+                                // no second-round group folds into this slot: its second statistics are empty
+                                my_stats[2 * G::kQRows + 8 * n + 2 * tq + j] = -INFINITY;
+                                my_stats[3 * G::kQRows + 8 * n + 2 * tq + j] = 0.0f;
+                            }
                         }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(parked_bar);
                 merge_ok = mbar_wait(parked_bar, merges & 1, abort_flag, p);
+            }
+            if constexpr (G::kTwoRounds) {
+                if (merge_ok) {
+                    if (merge_round == 1) {
+                        // fold this warp's state into the slot a first-round group parked: both become relative to
+                        // the larger of the two maxima (the statistics of the two rounds stay side by side)
+                        const float* first = my_park + G::kQRows * RS;
+                        float w_slot[NQ][2], w_mine[NQ][2];
+#pragma unroll
+                        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const float m_first = first[8 * n + 2 * tq + j];
+                                const float m_new = fmaxf(m_first, m_run[n][j]);
+                                const float base = m_new == -INFINITY ? 0.0f : m_new;
+                                w_slot[n][j] = weight_of(m_first, base);
+                                w_mine[n][j] = weight_of(m_run[n][j], base);
+                            }
+#pragma unroll
+                        for (int c = 0; c < DKW; ++c)
+#pragma unroll
+                            for (int n = 0; n < NQ; ++n)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float* at = my_park + (8 * n + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1);
+                                    *at = *at * w_slot[n][e & 1] + o[c][n][e] * w_mine[n][e & 1];
+                                }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(folded_bar);
+                    merge_ok = mbar_wait(folded_bar, merges & 1, abort_flag, p);
+                }
             }
             if (merge_ok) {
                 constexpr uint32_t kVecs = D / 4;
@@ -517,19 +669,32 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     const uint32_t row_tok = row / p.heads_per_task;
                     const uint32_t row_head = row % p.heads_per_task;
                     if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
+                    // (max, sum) of every slot: with two rounds, of the two states folded into it
+                    float m_slot[NSLOT], l_slot[NSLOT];
                     float m_max = -INFINITY;
 #pragma unroll
-                    for (int w = 0; w < CW; ++w) m_max = fmaxf(m_max, merge[w * G::kParkFloats + G::kQRows * RS + row]);
+                    for (int w = 0; w < NSLOT; ++w) {
+                        const float* stats = merge + w * G::kParkFloats + G::kQRows * RS;
+                        m_slot[w] = stats[row];
+                        l_slot[w] = stats[G::kQRows + row];
+                        if constexpr (G::kTwoRounds) {
+                            const float m_second = stats[2 * G::kQRows + row];
+                            const float m_new = fmaxf(m_slot[w], m_second);
+                            const float base = m_new == -INFINITY ? 0.0f : m_new;
+                            l_slot[w] = l_slot[w] * weight_of(m_slot[w], base) +
+                                        stats[3 * G::kQRows + row] * weight_of(m_second, base);
+                            m_slot[w] = m_new;
+                        }
+                        m_max = fmaxf(m_max, m_slot[w]);
+                    }
                     const float base = m_max == -INFINITY ? 0.0f : m_max;
                     float l_sum = 0.0f;
                     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int w = 0; w < CW; ++w) {
-                        const float* park = merge + w * G::kParkFloats;
-                        const float m_w = park[G::kQRows * RS + row];
-                        const float weight = m_w == -INFINITY ? 0.0f : fast_exp2((m_w - base) * p.scale_log2e);
-                        l_sum += park[G::kQRows * RS + G::kQRows + row] * weight;
-                        const float4 v = *reinterpret_cast<const float4*>(park + row * RS + d);
+                    for (int w = 0; w < NSLOT; ++w) {
+                        const float weight = weight_of(m_slot[w], base);
+                        l_sum += l_slot[w] * weight;
+                        const float4 v = *reinterpret_cast<const float4*>(merge + w * G::kParkFloats + row * RS + d);
                         acc.x += weight * v.x;
                         acc.y += weight * v.y;
                         acc.z += weight * v.z;
