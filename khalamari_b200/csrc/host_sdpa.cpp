@@ -420,7 +420,8 @@ Route lookup_route_reference(const kh_sdpa_config& c, const kh_request_shape* re
 //  - Q tile: as many of the request's Q tokens as fit 128 rows together with the whole group.
 //  - KV slice: a power of two such that every SM sees about `kTasksPerSm` tasks (balance across
 //    148 SMs with static task striding), never below 256 tokens (sixteen 16-token pages keep the
-//    ring busy) and never above 2048 (bounds the per-task tail).
+//    ring busy; 64 for batches too small to give every SM a task) and never above 2048 (bounds the per-task
+//    tail).
 Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* requests, uint32_t num_requests,
                         uint32_t sm_count) {
     // measured: decode (one Q token per task) runs best with about 4 tasks per SM (2,048-token slices on the decode
@@ -467,6 +468,17 @@ Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* request
         } else {
             slice = decode_slice(end, work * head_groups, 256, 2048,
                                  (unsigned __int128)sm_count * (sliced_q ? kTasksPerSm : kDecodeTasksPerSm));
+            // A small batch cut at 256 tokens leaves most SMs without a task (four short decode requests with two
+            // KV heads: 32 tasks on 148 SMs, and the batch sits in L2, so the step is pure latency). When the tasks
+            // at this slice do not reach the SM count, aim at one task per SM and allow slices down to 64 tokens.
+            uint64_t tasks = 0;
+            for (uint32_t r = 0; r < num_requests; ++r) {
+                const uint32_t ctx = requests[r].num_history_tokens + requests[r].num_q_tokens;
+                tasks += uint64_t(div_ceil(requests[r].num_q_tokens, variant.max_q_tokens)) * div_ceil(ctx, slice);
+            }
+            if (tasks * head_groups < sm_count) {
+                slice = decode_slice(end, work * head_groups, 64, 2048, (unsigned __int128)sm_count);
+            }
         }
     }
     const bool direct = sliced_q && slice == end;

@@ -247,7 +247,12 @@ static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
 template <typename T, int D>
 static MapInstance pick_page(uint32_t tokens_per_page, uint32_t rows, bool tensor_memory) {
     if (tokens_per_page == 16) return pick_rows<T, D, 16>(rows, tensor_memory);
-    KH_REQUIRE(tokens_per_page == 8, "this build instantiates 8- and 16-token pages (got %u)", tokens_per_page);
+    if constexpr (D == 256) {
+        // the reference's head_dim 256 profiles include 32-token pages (components/gqa/sdpa.rs:162-215)
+        if (tokens_per_page == 32) return pick_rows<T, D, 32>(rows, tensor_memory);
+    }
+    KH_REQUIRE(tokens_per_page == 8, "this build instantiates 8- and 16-token pages, and 32-token pages at head_dim 256 (got %u)",
+               tokens_per_page);
     return pick_rows<T, D, 8>(rows, tensor_memory);
 }
 

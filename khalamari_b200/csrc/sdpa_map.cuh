@@ -408,7 +408,8 @@ struct TaskSlot {
 template <int D, int P, int MT, int KVW, int PS, bool HALF, int KVB = 2>
 struct MapGeometry {
     static_assert(KVB == 1 || KVB == 2, "K/V elements are stored in one or two bytes");
-    static constexpr int kStageTokens = (D == 128) ? 32 : 16;
+    // a stage holds whole pages: 32 tokens at head_dim 128, one page (16 tokens, or 32 with 32-token pages) at 256
+    static constexpr int kStageTokens = (D == 128) ? 32 : (P > 16 ? P : 16);
     static constexpr int kBoxRows = (P < kStageTokens) ? P : kStageTokens;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;  // token boxes per stage
     static constexpr int kColumnHalves = D / 64;                      // 128-byte column groups
@@ -1226,7 +1227,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
         // ldmatrix lane roles. K (B operand, rows = KV tokens): matrix pair (lm_mat >> 1) picks the 8-token
         // group, (lm_mat & 1) the 16-byte chunk. V (transposed) and Q (A operand): (lm_mat & 1) picks the
         // 8-row group, (lm_mat >> 1) the chunk. Rows are taken relative to a 16-token group / 16-row tile.
-        static_assert(G::kBoxRows % 8 == 0 && 16 % G::kBoxRows == 0 || G::kBoxRows == 16, "box rows must tile 16 tokens");
+        static_assert(G::kBoxRows % 8 == 0 && (16 % G::kBoxRows == 0 || G::kBoxRows % 16 == 0),
+                      "token boxes must tile, or be tiled by, 16-token groups");
         const uint32_t k_row = (lm_mat >> 1) * 8 + lm_row;
         const uint32_t v_row = (lm_mat & 1) * 8 + lm_row;
         const uint32_t k_lane = (k_row / G::kBoxRows) * G::kCopyBytes + (k_row % G::kBoxRows) * 128;
@@ -1375,7 +1377,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     for (int jp = 0; jp < NT / 2; ++jp) {
                         uint32_t b[4];
                         ldmatrix_x4(b, k_addr[kk & 3] + ((2 * kk) / 8) * G::kBoxBytes +
-                                           ((ps * WT + 16 * jp) / G::kBoxRows) * G::kCopyBytes);
+                                           ((ps * WT + 16 * jp) / G::kBoxRows) * G::kCopyBytes +
+                                           ((ps * WT + 16 * jp) % G::kBoxRows) * 128);
                         mma_16816<T>(s[2 * jp], a, b[0], b[1]);
                         mma_16816<T>(s[2 * jp + 1], a, b[2], b[3]);
                     }
@@ -1469,7 +1472,8 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
                     for (int np = 0; np < DN / 2; ++np) {
                         uint32_t b[4];
                         ldmatrix_x4_trans(b, v_addr[np & 3] + ((2 * np) / 8) * G::kBoxBytes +
-                                                 ((ps * WT + 16 * kt) / G::kBoxRows) * G::kCopyBytes);
+                                                 ((ps * WT + 16 * kt) / G::kBoxRows) * G::kCopyBytes +
+                                                 ((ps * WT + 16 * kt) % G::kBoxRows) * 128);
                         mma_16816<T>(o[2 * np], pa[kt], b[0], b[1]);
                         mma_16816<T>(o[2 * np + 1], pa[kt], b[2], b[3]);
                         if (!HALF) {

@@ -416,6 +416,11 @@ def test_b200_policy_sizes_slices_for_148_sms():
     result = sel.select([RequestShape(4607, 1)] * 64, policy, 64)
     sizes = {len(m.request_local_kv_token_indices) for m in result.map_task_templates()}
     assert max(sizes) == 2048
-    # a single short request cannot fill the machine: the floor of 256 tokens applies
-    result = sel.select([RequestShape(2047, 1)], policy, 64)
+    # four short requests give every SM a task at the floor of 256 tokens (4 x 8 slices x 8 KV heads = 256 tasks)
+    result = sel.select([RequestShape(2047, 1)] * 4, policy, 64)
     assert {len(m.request_local_kv_token_indices) for m in result.map_task_templates()} == {256}
+    # a single short request does not (64 tasks on 148 SMs): the slice drops towards one task per SM, not below 64
+    result = sel.select([RequestShape(2047, 1)], policy, 64)
+    assert {len(m.request_local_kv_token_indices) for m in result.map_task_templates()} == {64}
+    result = sel.select([RequestShape(255, 1)], policy, 64)
+    assert {len(m.request_local_kv_token_indices) for m in result.map_task_templates()} == {64}
