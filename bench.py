@@ -44,6 +44,11 @@ WORKLOADS = {
     # prefill half of configuration 5: eight causal 2,048-token chunks appended to prefixes U[0, 30720]
     "c5p": dict(batch=8, q_len=2048, hq=64, hkv=8, d=128, dtype="bf16", lo=2048, hi=32768, seed=4, partition=0,
                 pool_pages=0, label="chunked prefill B8 chunk 2048 Hq64/Hkv8/D128 bf16 prefix U[0,30720] P16"),
+    # configuration 5: eight causal 2,048-token prefill chunks on prefixes U[0, 30720] plus 56 decode requests with
+    # contexts U[1024, 8192], one call
+    "c5": dict(batch=64, q_len=0, hq=64, hkv=8, d=128, dtype="bf16", lo=0, hi=0, seed=4, partition=0, pool_pages=0,
+               label="8 prefill chunks of 2048 on prefixes U[0,30720] + 56 decode ctx U[1024,8192], one call, "
+                     "Hq64/Hkv8/D128 bf16 P16"),
     "c1": dict(batch=4, q_len=1, hq=16, hkv=2, d=256, dtype="f16", lo=0, hi=0, seed=0, partition=0, pool_pages=0,
                contexts=[128, 517, 1024, 2048], label="decode B4 Hq16/Hkv2/D256 fp16 ctx {128,517,1024,2048} P16"),
 }
@@ -506,6 +511,120 @@ def run_ours(args):
     return result, dict(device=device, stream=stream, torch_stream=torch_stream)
 
 
+def run_mixed(args):
+    """Workload c5: prefill chunks and decode requests in ONE call (MixedBatchAttention: the decode requests through
+    the SlicedKv kernels, the prefill chunks through the tensor-memory kernel, recorded back to back). Reports the
+    whole call, each part (events between the parts), and the same batch through a single selection."""
+    import torch
+
+    from khalamari_b200.device import Device, Dtype, Stream
+    from khalamari_b200.gqa import GQACore, MixedBatchAttention
+    from khalamari_b200.request_page_table import GQAPageTableLayout
+
+    rank, world, local = init_ranks(torch)
+    spec = dict(WORKLOADS["c5"])
+    chunk = args.chunk or 2048
+    rng = np.random.default_rng(spec["seed"] + 1000 * rank)
+    prefixes = rng.integers(0, 30720 + 1, size=8).tolist()
+    decode_contexts = rng.integers(1024, 8192 + 1, size=56).tolist()
+    contexts = [p + chunk for p in prefixes] + decode_contexts
+    q_lens = [chunk] * 8 + [1] * 56
+    spec["q_lens"] = q_lens
+    hq, hkv, d = spec["hq"], spec["hkv"], spec["d"]
+    device = Device(local)
+    case = build_device_case(device, spec, contexts, torch, spec["seed"] + 1000 * rank)
+    torch_stream = torch.cuda.current_stream()
+    stream = Stream(device, torch_stream.cuda_stream)
+    layout = GQAPageTableLayout(len(contexts), 1, case["num_blocks"], 1)
+    total_tokens = sum(q_lens)
+    scale = 1.0 / float(np.sqrt(d))
+    mixed = MixedBatchAttention(device, GQACore(d, hq, hkv, scale), Dtype.Bfloat16, 2 * hkv * PAGE * d * 2, layout,
+                                total_tokens, max_decode_tokens=64)
+    req_slots = list(range(len(contexts)))
+    token_indices = [c - q for c, q in zip(contexts, q_lens)]
+    cu_tokens = np.concatenate([[0], np.cumsum(q_lens)]).tolist()
+
+    def timed(record, count, marks):
+        for _ in range(max(args.warmup, 3)):
+            record(None)
+        torch.cuda.synchronize()
+        events = [[torch.cuda.Event(enable_timing=True) for _ in range(marks + 1)] for _ in range(count)]
+        launches = 0
+        for i in range(count):
+            events[i][0].record(torch_stream)
+            seen = [0]
+
+            def between(i=i, seen=seen):
+                seen[0] += 1
+                events[i][seen[0]].record(torch_stream)
+
+            launches += record(between)
+        torch.cuda.synchronize()
+        device.check(stream)
+        per_mark = [float(np.mean([e[k].elapsed_time(e[k + 1]) for e in events])) for k in range(marks)]
+        return events[0][0].elapsed_time(events[-1][marks]) / count, per_mark, launches
+
+    steps = min(args.steps, 10)
+    mixed.prepare(req_slots, token_indices, cu_tokens)
+    names = ["decode" if part is mixed._parts.get("decode") else "prefill" for part, _, _ in mixed.plan]
+    props = torch.cuda.get_device_properties(local)
+    sampler = ClockSampler(str(getattr(props, "uuid", "")) or None, local)
+    sampler.__enter__()
+    t0 = time.perf_counter()
+    split_ms, part_ms, launches = timed(
+        lambda between: mixed.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0, between),
+        steps, len(mixed.plan))
+    t1 = time.perf_counter()
+    sampler.__exit__(None, None, None)
+    out_split = case["out"].clone()
+    # the same batch through one selection (the reference's form: the decode rows ride the prefill tiles)
+    whole = mixed._part("whole", total_tokens)
+    whole.prepare(req_slots, token_indices, cu_tokens, total_tokens)
+    case["out"].zero_()
+    single_ms, _, _ = timed(
+        lambda between: (whole.record_sdpa(stream, case["d_q"], case["d_pool"], case["d_table"], case["d_out"], 0),
+                         between() if between else None)[0], steps, 1)
+    agree = float((out_split.float() - case["out"].float()).abs().max().item())
+    if rank != 0:
+        return None
+    prefill_pairs = sum(chunk * p + chunk * (chunk + 1) // 2 for p in prefixes)
+    prefill_flops = 4.0 * hq * d * prefill_pairs
+    decode_bytes = sum(decode_contexts) * 2 * hkv * d * 2
+    prefill_min_bytes = sum(p + chunk for p in prefixes) * 2 * hkv * d * 2
+    by_name = dict(zip(names, part_ms))
+    peak, peak_kind = load_peaks()
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
+    result = {
+        "metric": "GQA decode KV-read GB/s", "value": round((decode_bytes + prefill_min_bytes) / (split_ms * 1e-3) / 1e9, 2),
+        "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(split_ms, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": spec["label"], "batch_per_gpu": len(contexts), "new_tokens": total_tokens,
+                   "kv_tokens_per_gpu": int(sum(contexts)), "l2": "inputs larger than L2; no flush",
+                   "parallelism": f"dp{world} by request"},
+        "tflops": round((prefill_flops + 4.0 * hq * d * sum(decode_contexts)) / (split_ms * 1e-3) / 1e12, 2),
+        "tokens_per_s": round(total_tokens / (split_ms * 1e-3), 1),
+        "mix": {"form": "two selections recorded back to back (decode: SlicedKv map + reduce; prefill: tensor-memory "
+                        "tiles, direct or map + reduce)",
+                "prefill_ms": round(by_name.get("prefill", 0.0), 5), "decode_ms": round(by_name.get("decode", 0.0), 5),
+                "prefill_tflops": round(prefill_flops / (by_name["prefill"] * 1e-3) / 1e12, 2) if by_name.get("prefill") else None,
+                "decode_kv_gbs": round(decode_bytes / (by_name["decode"] * 1e-3) / 1e9, 1) if by_name.get("decode") else None,
+                "single_selection_ms": round(single_ms, 5),
+                "max_abs_difference_between_the_two_forms": agree},
+        "roofline": {"bound": "tensor", "achieved": round(prefill_flops / (by_name.get("prefill", split_ms) * 1e-3) / 1e12, 2),
+                     "peak": tensor_peak, "unit": "TFLOP/s",
+                     "frac": round(prefill_flops / (by_name.get("prefill", split_ms) * 1e-3) / 1e12 / tensor_peak, 4),
+                     "traffic": None, "peak_source": "of measured (burst)" if peaks else "of fallback",
+                     "kernel": "sdpa_tc_kernel (prefill part)", "kernel_ms": round(by_name.get("prefill", split_ms), 5)},
+        "gpu_launches": launches, "clocks": sampler.summary(t0, t1),
+    }
+    if not args.no_parity:
+        sample = [[0, chunk // 2, chunk - 1] for _ in range(8)] + [[0] for _ in range(56)]
+        parity, _ = oracle_parity(spec, contexts, q_lens, case, out_split.float().cpu().numpy(), sample)
+        result["parity"] = parity
+    return result
+
+
 def measure_split_sequence(args, torch, context, rank, world, local, device, stream, torch_stream, steps,
                            partition=None, check_parity=True):
     """ONE long sequence whose pages are split in token order over the ranks. A step is: local split-KV map, local
@@ -818,11 +937,15 @@ def main():
     parser.add_argument("--kv-dtype", default="io", choices=["io", "fp8"],
                         help="element type of the K/V pages: the Q/output type (default) or FP8 E4M3FN")
     parser.add_argument("--context", type=int, default=0, help="workload c4: tokens of the one sequence")
+    parser.add_argument("--chunk", type=int, default=0, help="workload c5: tokens per prefill chunk (default 2048)")
     args = parser.parse_args()
     if args.impl == "reference":
         result = run_reference(args)
     elif args.workload == "c4":
         result = run_split_sequence(args)
+        finish_ranks()
+    elif args.workload == "c5":
+        result = run_mixed(args)
         finish_ranks()
     else:
         import torch

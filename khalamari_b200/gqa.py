@@ -291,6 +291,81 @@ class HostPipeline:
                 self.in_flight[slot] = False
 
 
+class MixedBatchAttention:
+    """A batch that mixes decode requests (one new token) with prefill / verify requests (several), as one call.
+
+    The reference selects ONE execution variant per batch (``Selector::select``, attn/gqa/sdpa.rs:278-380): in a
+    mixed batch the decode rows then ride the wide Q tiles chosen for the prefill rows (128-row tensor-memory tiles
+    with 8 valid rows). Here the two kinds are recorded back to back on the same stream as two selections - the
+    decode requests through the SlicedKv map + reduce, the others through the sliced-Q kernels - each writing its
+    own rows of the one output buffer: two kernels (pairs) in one recorded sequence rather than two task kinds in
+    one grid, because the tensor-memory kernel and the warp-level decode kernel want different block shapes,
+    register budgets and shared-memory layouts. The split needs the decode requests to form one contiguous run at
+    the start or the end of the batch (their Q rows and output rows are then one slice of the buffers); any other
+    order falls back to the reference's single selection."""
+
+    def __init__(self, device: Device, core: GQACore, io_dtype: Dtype, page_bytes: int,
+                 page_table_layout: GQAPageTableLayout, max_tokens: int, max_decode_tokens: int | None = None,
+                 policy: SelectorPolicy = SelectorPolicy.B200, kv_dtype: Dtype | None = None):
+        self.device = device
+        self._args = (core, io_dtype, page_bytes, page_table_layout)
+        self._policy = policy
+        self._kv_dtype = kv_dtype
+        self.max_tokens = max_tokens
+        self.max_decode_tokens = max_decode_tokens or min(max_tokens, 256)
+        self.core = core
+        self.io_dtype = io_dtype
+        self._parts = {}
+        self.plan = None  # list of (attention, first flat token, token count)
+
+    def _part(self, name: str, max_tokens: int) -> GQAAttention:
+        if name not in self._parts:
+            core, io_dtype, page_bytes, layout = self._args
+            self._parts[name] = GQAAttention(self.device, core, io_dtype, page_bytes, layout, max_tokens, self._policy,
+                                             kv_dtype=self._kv_dtype)
+        return self._parts[name]
+
+    def prepare(self, req_slots, token_indices, cu_tokens, stream: Stream | None = None) -> None:
+        n = len(req_slots)
+        q_lens = [int(cu_tokens[r + 1]) - int(cu_tokens[r]) for r in range(n)]
+        decode = [r for r in range(n) if q_lens[r] == 1]
+        split = None
+        if decode and len(decode) < n and len(decode) <= self.max_decode_tokens:
+            if decode == list(range(n - len(decode), n)):
+                split = n - len(decode)          # the others first, then the decode run
+                parts = [("wide", 0, split), ("decode", split, n)]
+            elif decode == list(range(len(decode))):
+                split = len(decode)
+                parts = [("decode", 0, split), ("wide", split, n)]
+        if split is None:
+            whole = self._part("whole", self.max_tokens)
+            whole.prepare(req_slots, token_indices, cu_tokens, int(cu_tokens[-1]), stream)
+            self.plan = [(whole, 0, int(cu_tokens[-1]))]
+            return
+        self.plan = []
+        for name, begin, end in parts:
+            part = self._part(name, self.max_decode_tokens if name == "decode" else self.max_tokens)
+            first = int(cu_tokens[begin])
+            # token capacity = the part's own token count: its Q and output rows are a slice of the caller's buffers
+            part.prepare(list(req_slots[begin:end]), list(token_indices[begin:end]),
+                         [int(c) - first for c in cu_tokens[begin:end + 1]], int(cu_tokens[end]) - first, stream)
+            self.plan.append((part, first, int(cu_tokens[end]) - first))
+
+    def record_sdpa(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer, output: Buffer,
+                    gqa_layer_index: int = 0, between=None) -> int:
+        """Enqueues every part of the plan on ``stream``; returns the kernels launched. ``between`` (a timing hook)
+        is called after each part."""
+        row = self.core.num_q_heads * self.core.head_dim * self.io_dtype.item_size()
+        launches = 0
+        for part, first, count in self.plan:
+            q_view = Buffer.wrap(self.device, q.ref.ptr + first * row, count * row)
+            out_view = Buffer.wrap(self.device, output.ref.ptr + first * row, count * row)
+            launches += part.record_sdpa(stream, q_view, kv_pages, page_ids, out_view, gqa_layer_index)
+            if between is not None:
+                between()
+        return launches
+
+
 def combine_partials(device: Device, stream: Stream, num_partials: int, num_rows: int, head_dim: int,
                      exp_sums: Buffer, max_logits: Buffer, partial_output: Buffer, out_dtype: Dtype, output: Buffer,
                      out_exp_sums: Buffer | None = None, out_max_logits: Buffer | None = None) -> None:

@@ -155,3 +155,46 @@ def test_config5_mix_with_short_chunks_in_full(device):
     case = _mixed_case(256, 3072)
     out = DeviceCase(device, case).run(fused=False)
     assert_within_contract(out, case.oracle_output(), "config 5 mix, 256-token chunks, every row")
+
+
+def _run_mixed(device, case):
+    """The batch through MixedBatchAttention (decode run and prefill run as two selections, back to back), on the
+    buffers a DeviceCase uploaded."""
+    from khalamari_b200.gqa import GQACore, MixedBatchAttention
+    run = DeviceCase(device, case)
+    mixed = MixedBatchAttention(device, GQACore(case.head_dim, case.num_q_heads, case.num_kv_heads, case.scale),
+                                run.dtype, case.page_bytes, run.layout, case.num_tokens, max_decode_tokens=64)
+    mixed.prepare(case.req_slots, case.token_indices, case.cu_tokens)
+    assert len(mixed.plan) == 2, "eight prefill requests then 56 decode requests split into two selections"
+    launches = mixed.record_sdpa(run.stream, run.q, run.kv_pages, run.page_ids, run.output, case.layer_index)
+    run.stream.synchronize()
+    assert device.check(run.stream) == 0
+    return run.read_output(), launches
+
+
+def test_config5_as_two_selections_in_one_call_sampled(device):
+    case = _mixed_case(2048, 30720)
+    out, launches = _run_mixed(device, case)
+    assert 2 <= launches <= 4
+    samples = [(r, [0, 1023, 2047]) for r in range(8)] + [(r, [0]) for r in range(8, 64)]
+    flat = [case.cu_tokens[r] + t for r, tokens in samples for t in tokens]
+    assert_within_contract(out[flat], _sampled_oracle(case, samples), "config 5 as two selections, sampled rows")
+
+
+def test_config5_as_two_selections_short_chunks_in_full(device):
+    case = _mixed_case(256, 3072)
+    out, _ = _run_mixed(device, case)
+    assert_within_contract(out, case.oracle_output(), "config 5 mix as two selections, every row")
+
+
+def test_mixed_batch_in_any_other_order_falls_back_to_one_selection(device):
+    from khalamari_b200.gqa import GQACore, MixedBatchAttention
+    case = make_case(5, "bf16", 64, 8, 128, [300, 40, 900, 77], [1, 24, 1, 19])
+    run = DeviceCase(device, case, max_tokens=64)
+    mixed = MixedBatchAttention(device, GQACore(128, 64, 8, case.scale), run.dtype, case.page_bytes, run.layout, 64)
+    mixed.prepare(case.req_slots, case.token_indices, case.cu_tokens)
+    assert len(mixed.plan) == 1
+    mixed.record_sdpa(run.stream, run.q, run.kv_pages, run.page_ids, run.output, case.layer_index)
+    run.stream.synchronize()
+    assert device.check(run.stream) == 0
+    assert_within_contract(run.read_output(), case.oracle_output(), "interleaved mix through one selection")
