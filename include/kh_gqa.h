@@ -603,6 +603,72 @@ KH_API kh_status kh_kv_page_write_invoke(kh_kv_page_write* compute, kh_stream* s
 KH_API uint8_t kh_fp8_e4m3_from_bf16(uint16_t bf16_bits);
 KH_API uint16_t kh_fp8_e4m3_to_bf16(uint8_t fp8_bits);
 
+/* ---- BiDi-block SDPA: BM/components/gqa/bidi_block_sdpa.rs, metal/gqa_bidi_block_sdpa.metal:10-88 -------------
+ * Dense bidirectional attention of every Q token over ALL tokens of its own request block (the proposal block a
+ * DFlash2 drafter works on; K/V of the block are contiguous [tokens][Hkv][D] rows, not yet in the paged cache),
+ * written as one more partial into the SplitKV partial-state layout: slot cu_sdpa_partial_outputs[range + 1] - 1 of
+ * the token's Q-token range, index ((slot * Hq + head) * max_q_tokens + token offset) (gqa_bidi_block_sdpa.metal:36,
+ * 64-66). The sliced-Q map kernel fills the range's other slots with (sliding-window) history partials and the
+ * sliced-Q reducer merges them all (BM/components/gqa/bidi_block_sdpa_test.rs:174-330 records map, block, reduce).
+ * Statistics as everywhere: exp sums relative to the maximum logit, maxima in the natural-log domain. Partial outputs
+ * are f32 here (the reference stores the io dtype). */
+/* bidi_block_sdpa::Config (bidi_block_sdpa.rs:56-64). head_dim must be a multiple of 32. */
+typedef struct kh_bidi_block_sdpa_config {
+    uint32_t block_size;
+    uint32_t max_q_tokens;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    float scale;
+    kh_dtype dtype; /* q / local_k / local_v element type: Bfloat16, Float16 or Float32 */
+} kh_bidi_block_sdpa_config;
+
+/* bidi_block_sdpa::Shape (bidi_block_sdpa.rs:141-145). num_total_tokens must hold complete request blocks. */
+typedef struct kh_bidi_block_sdpa_shape {
+    uint32_t num_total_tokens;
+    uint32_t num_total_q_token_ranges;
+    uint32_t num_total_partial_output_slots;
+} kh_bidi_block_sdpa_shape;
+
+/* bidi_block_sdpa::Buffers (bidi_block_sdpa.rs:177-186), binding order 0..7 of Invocation::record (:262-269). */
+typedef struct kh_bidi_block_sdpa_buffers {
+    kh_buffer_ref q;
+    kh_buffer_ref local_k;
+    kh_buffer_ref local_v;
+    kh_buffer_ref q_token_ranges;
+    kh_buffer_ref cu_sdpa_partial_outputs;
+    kh_buffer_ref partial_exp_sums;
+    kh_buffer_ref partial_max_logits;
+    kh_buffer_ref partial_output;
+} kh_bidi_block_sdpa_buffers;
+
+typedef struct kh_bidi_block_sdpa kh_bidi_block_sdpa;
+
+/* Compute::new (bidi_block_sdpa.rs:193-229). */
+KH_API kh_status kh_bidi_block_sdpa_create(kh_device* device, const kh_bidi_block_sdpa_config* config,
+                                           kh_bidi_block_sdpa** out);
+KH_API kh_status kh_bidi_block_sdpa_destroy(kh_bidi_block_sdpa* compute);
+/* Compute::invoke(shape, num_active_q_token_ranges, buffers).record (bidi_block_sdpa.rs:231-283, validation
+ * :286-330). With replay counts bound to the stream the active range count is read on the device (word 1). */
+KH_API kh_status kh_bidi_block_sdpa_invoke(kh_bidi_block_sdpa* compute, kh_stream* stream,
+                                           const kh_bidi_block_sdpa_shape* shape, uint32_t num_active_q_token_ranges,
+                                           const kh_bidi_block_sdpa_buffers* buffers);
+
+/* build_metal_metadata of the BiDi-block GQA owner (EM/attn/bidi_block_gqa/metadata.rs:176-339): the metadata of one
+ * proposal step. Tokens come in request blocks of `block_size` (request r owns flat tokens [r * block_size,
+ * (r + 1) * block_size)); token t sees cached history tokens [history_begins[t], history_ends[t]) of its request (a
+ * sliding window) plus its whole block. Per Q-token range (at most max_q_tokens tokens of one block): history map
+ * task templates over the union of its tokens' history ranges, cut on multiples of kv_tokens_per_iteration into as
+ * many splits as the template capacity allows (allocate_history_kv_splits, :341-367: longest range first, later
+ * ranges win ties), then ONE padded template (u32::MAX), whose index is the block partial's slot. The template count
+ * is padded to a power of two. Fills visible_kv_token_ranges, q_token_ranges, sdpa_map_task_templates,
+ * cu_sdpa_partial_outputs, and - when req_slots / token_positions are given - req_slots and flat_token_indices. */
+KH_API kh_status kh_bidi_block_metadata_build(const kh_metadata_arrays* arrays, const uint32_t* req_slots,
+                                              const uint32_t* token_positions, const uint32_t* history_begins,
+                                              const uint32_t* history_ends, uint32_t num_requests, uint32_t block_size,
+                                              uint32_t max_q_tokens, uint32_t kv_tokens_per_iteration,
+                                              uint32_t max_sdpa_map_task_templates, kh_replay_shape* out_shape);
+
 /* ---- device status word: the analogue of SubmissionCheck (BM/metal/stream/check.rs:8-13) ---- */
 /* Reads (after synchronising the stream) and clears the sticky status the kernels of `device`
  * write: 0 = clean; bit 0 = a bounded wait inside a kernel ran out; bit 1 = a page id addressed

@@ -3,7 +3,7 @@
 // Compiles the CUDA sources of libkhcuda_gqa for sm_100a with nvcc and links the crate against the result: the
 // same single nvcc command `khalamari_b200/build.py` runs for the Python harness.
 //
-//   KHCUDA_GQA_CSRC   directory holding host_sdpa.cpp, sdpa_api.cu, sdpa_fp8.cu, kv_page_write.cu and their
+//   KHCUDA_GQA_CSRC   directory holding host_sdpa.cpp, sdpa_api.cu, sdpa_fp8.cu, kv_page_write.cu, bidi_block_sdpa.cu and their
 //                     headers (default: ../khalamari_b200/csrc relative to this crate)
 //   KHCUDA_GQA_DIR    use a prebuilt libkhcuda_gqa.so from this directory instead of compiling
 //   NVCC              nvcc binary (default: nvcc on PATH, else /usr/local/cuda/bin/nvcc)
@@ -11,8 +11,8 @@ use std::env;
 use std::path::{Path, PathBuf};
 use std::process::Command;
 
-const SOURCES: [&str; 4] = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu"];
-const HEADERS: [&str; 6] = ["common.h", "cuda_objects.h", "host_sdpa.h", "map_instance.h", "sdpa_map.cuh", "sdpa_tc.cuh"];
+const SOURCES: [&str; 5] = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu", "bidi_block_sdpa.cu"];
+const HEADERS: [&str; 7] = ["common.h", "cuda_objects.h", "host_sdpa.h", "map_instance.h", "sdpa_map.cuh", "sdpa_tc.cuh", "sdpa_tm.cuh"];
 
 fn main() {
     println!("cargo:rerun-if-env-changed=KHCUDA_GQA_DIR");

@@ -85,6 +85,12 @@ pub struct KhKvPageWrite {
     _private: [u8; 0],
 }
 
+/// Opaque handle (`kh_bidi_block_sdpa`).
+#[repr(C)]
+pub struct KhBidiBlockSdpa {
+    _private: [u8; 0],
+}
+
 #[repr(C)]
 #[derive(Clone, Copy, Debug)]
 pub struct KhBufferRef {
@@ -363,6 +369,39 @@ pub struct KhKvPageWriteBuffers {
     pub req_slots: KhBufferRef,
     pub flat_token_indices: KhBufferRef,
     pub page_ids: KhBufferRef,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct KhBidiBlockSdpaConfig {
+    pub block_size: u32,
+    pub max_q_tokens: u32,
+    pub num_q_heads: u32,
+    pub num_kv_heads: u32,
+    pub head_dim: u32,
+    pub scale: f32,
+    pub dtype: u32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct KhBidiBlockSdpaShape {
+    pub num_total_tokens: u32,
+    pub num_total_q_token_ranges: u32,
+    pub num_total_partial_output_slots: u32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct KhBidiBlockSdpaBuffers {
+    pub q: KhBufferRef,
+    pub local_k: KhBufferRef,
+    pub local_v: KhBufferRef,
+    pub q_token_ranges: KhBufferRef,
+    pub cu_sdpa_partial_outputs: KhBufferRef,
+    pub partial_exp_sums: KhBufferRef,
+    pub partial_max_logits: KhBufferRef,
+    pub partial_output: KhBufferRef,
 }
 
 #[link(name = "khcuda_gqa")]
@@ -696,6 +735,32 @@ unsafe extern "C" {
     ) -> KhStatus;
     pub fn kh_fp8_e4m3_from_bf16(bf16_bits: u16) -> u8;
     pub fn kh_fp8_e4m3_to_bf16(fp8_bits: u8) -> u16;
+    pub fn kh_bidi_block_sdpa_create(
+        device: *mut KhDevice,
+        config: *const KhBidiBlockSdpaConfig,
+        out: *mut *mut KhBidiBlockSdpa,
+    ) -> KhStatus;
+    pub fn kh_bidi_block_sdpa_destroy(compute: *mut KhBidiBlockSdpa) -> KhStatus;
+    pub fn kh_bidi_block_sdpa_invoke(
+        compute: *mut KhBidiBlockSdpa,
+        stream: *mut KhStream,
+        shape: *const KhBidiBlockSdpaShape,
+        num_active_q_token_ranges: u32,
+        buffers: *const KhBidiBlockSdpaBuffers,
+    ) -> KhStatus;
+    pub fn kh_bidi_block_metadata_build(
+        arrays: *const KhMetadataArrays,
+        req_slots: *const u32,
+        token_positions: *const u32,
+        history_begins: *const u32,
+        history_ends: *const u32,
+        num_requests: u32,
+        block_size: u32,
+        max_q_tokens: u32,
+        kv_tokens_per_iteration: u32,
+        max_sdpa_map_task_templates: u32,
+        out_shape: *mut KhReplayShape,
+    ) -> KhStatus;
     pub fn kh_device_check(device: *mut KhDevice, stream: *mut KhStream, out_status_word: *mut u32) -> KhStatus;
     pub fn kh_device_set_wait_limit(device: *mut KhDevice, polls: u32) -> KhStatus;
     pub fn kh_combine_partials(

@@ -135,6 +135,21 @@ class SlicedKvStaticBuffersC(C.Structure):
 STATIC_PARTIALS_BYTES = 32 << 20  # KH_STATIC_PARTIALS_BYTES
 
 
+class BidiBlockSdpaConfigC(C.Structure):
+    _fields_ = [("block_size", C.c_uint32), ("max_q_tokens", C.c_uint32), ("num_q_heads", C.c_uint32),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("scale", C.c_float), ("dtype", C.c_uint32)]
+
+
+class BidiBlockSdpaShapeC(C.Structure):
+    _fields_ = [("num_total_tokens", C.c_uint32), ("num_total_q_token_ranges", C.c_uint32),
+                ("num_total_partial_output_slots", C.c_uint32)]
+
+
+class BidiBlockSdpaBuffersC(C.Structure):
+    _fields_ = [(name, BufferRef) for name in ("q", "local_k", "local_v", "q_token_ranges", "cu_sdpa_partial_outputs",
+                                               "partial_exp_sums", "partial_max_logits", "partial_output")]
+
+
 class SlicedKvSizesC(C.Structure):
     _fields_ = [("q_bytes", C.c_uint64), ("req_slots_bytes", C.c_uint64), ("page_ids_bytes", C.c_uint64),
                 ("sdpa_map_task_templates_bytes", C.c_uint64), ("cu_sdpa_partial_outputs_bytes", C.c_uint64),
@@ -263,6 +278,11 @@ PROTOTYPES = {
     "kh_kv_page_write_tokens_per_page": [P(KvPageWriteConfigC), P(C.c_uint32)],
     "kh_kv_page_write_invoke": [_vp, _vp, P(KvPageWriteShapeC), P(KvPageWriteBuffersC), _u32, _u32],
     "kh_combine_packed_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, _u32, BufferRef],
+    "kh_bidi_block_sdpa_create": [_vp, P(BidiBlockSdpaConfigC), P(_vp)],
+    "kh_bidi_block_sdpa_destroy": [_vp],
+    "kh_bidi_block_sdpa_invoke": [_vp, _vp, P(BidiBlockSdpaShapeC), _u32, P(BidiBlockSdpaBuffersC)],
+    "kh_bidi_block_metadata_build": [P(MetadataArraysC), P(_u32), P(_u32), P(_u32), P(_u32), _u32, _u32, _u32, _u32,
+                                     _u32, P(ReplayShapeC)],
 }
 _SPECIAL = {
     "kh_last_error": ([C.c_char_p, C.c_size_t], C.c_size_t),

@@ -1145,4 +1145,115 @@ kh_status kh_metadata_update(const kh_metadata_arrays* arrays, const uint32_t* r
     });
 }
 
+// build_metal_metadata + allocate_history_kv_splits of the BiDi-block GQA owner
+// (crates/inference-executor-metal/src/attn/bidi_block_gqa/metadata.rs:176-367).
+kh_status kh_bidi_block_metadata_build(const kh_metadata_arrays* arrays, const uint32_t* req_slots,
+                                       const uint32_t* token_positions, const uint32_t* history_begins,
+                                       const uint32_t* history_ends, uint32_t num_requests, uint32_t block_size,
+                                       uint32_t max_q_tokens, uint32_t kv_tokens_per_iteration,
+                                       uint32_t max_sdpa_map_task_templates, kh_replay_shape* out_shape) {
+    return guarded([&]() -> kh_status {
+        KH_REQUIRE(arrays && history_begins && history_ends, "null argument");
+        KH_REQUIRE(arrays->visible_kv_token_ranges && arrays->q_token_ranges && arrays->sdpa_map_task_templates &&
+                       arrays->cu_sdpa_partial_outputs,
+                   "metadata array is null");
+        KH_REQUIRE(num_requests > 0 && block_size > 0, "BiDiBlockGQA needs requests and a block size");
+        KH_REQUIRE(kv_tokens_per_iteration > 0, "BiDiBlockGQA KV-token iteration size must be positive");
+        KH_REQUIRE(max_q_tokens > 0, "BiDiBlockGQA Q-token range must contain tokens");
+        const uint64_t num_tokens64 = uint64_t(num_requests) * block_size;
+        KH_REQUIRE(num_tokens64 <= arrays->max_tokens, "BiDiBlockGQA tokens exceed the metadata capacity");
+        const uint32_t num_tokens = uint32_t(num_tokens64);
+        KH_REQUIRE(max_sdpa_map_task_templates <= arrays->max_map_task_templates,
+                   "BiDiBlockGQA TaskTemplate capacity exceeds the metadata capacity");
+        KH_REQUIRE((max_sdpa_map_task_templates & (max_sdpa_map_task_templates - 1)) == 0 &&
+                       max_sdpa_map_task_templates > 0,
+                   "BiDiBlockGQA TaskTemplate capacity must be a power of two");
+        for (uint32_t t = 0; t < num_tokens; ++t) {
+            arrays->visible_kv_token_ranges[2 * t] = history_begins[t];
+            arrays->visible_kv_token_ranges[2 * t + 1] = history_ends[t];
+            if (req_slots != nullptr && arrays->req_slots != nullptr) arrays->req_slots[t] = req_slots[t / block_size];
+            if (token_positions != nullptr && arrays->flat_token_indices != nullptr) {
+                arrays->flat_token_indices[t] = token_positions[t];
+            }
+        }
+        // Q-token ranges: runs of at most max_q_tokens tokens inside one request block
+        std::vector<std::pair<uint32_t, uint32_t>> ranges;
+        for (uint32_t r = 0; r < num_requests; ++r) {
+            const uint32_t request_end = (r + 1) * block_size;
+            for (uint32_t begin = r * block_size; begin < request_end;) {
+                const uint32_t end = std::min(begin + max_q_tokens, request_end);
+                ranges.emplace_back(begin, end);
+                begin = end;
+            }
+        }
+        KH_REQUIRE(uint64_t(max_sdpa_map_task_templates) >= uint64_t(ranges.size()) * 2,
+                   "BiDiBlockGQA needs at least two TaskTemplates per Q-token range");
+        // union of the history ranges of a Q-token range, and its KV iterations
+        std::vector<std::pair<uint32_t, uint32_t>> history(ranges.size());
+        std::vector<uint64_t> iterations(ranges.size());
+        for (size_t i = 0; i < ranges.size(); ++i) {
+            uint32_t begin = 0xffffffffu, end = 0;
+            for (uint32_t t = ranges[i].first; t < ranges[i].second; ++t) {
+                begin = std::min(begin, history_begins[t]);
+                end = std::max(end, history_ends[t]);
+            }
+            KH_REQUIRE(begin < end, "BiDiBlockGQA history range must not be empty");
+            history[i] = {begin, end};
+            iterations[i] = div_ceil64(end - begin, kv_tokens_per_iteration);
+            KH_REQUIRE(iterations[i] <= (0xffffffffull - begin) / kv_tokens_per_iteration,
+                       "BiDiBlockGQA padded history-token range must fit u32");
+        }
+        // allocate_history_kv_splits: one split each, then the remaining templates go, one at a time, to the range
+        // with the most iterations per split (later ranges win ties)
+        const uint64_t budget = max_sdpa_map_task_templates - ranges.size();
+        std::vector<uint64_t> splits(ranges.size(), 1);
+        if (ranges.size() == 1) {
+            splits[0] = std::min<uint64_t>(iterations[0], budget);
+        } else if (ranges.size() < budget) {
+            std::priority_queue<std::pair<uint64_t, size_t>> candidates;
+            for (size_t i = 0; i < ranges.size(); ++i) {
+                if (iterations[i] > 1) candidates.emplace(iterations[i], i);
+            }
+            for (uint64_t used = ranges.size(); used < budget && !candidates.empty(); ++used) {
+                const size_t index = candidates.top().second;
+                candidates.pop();
+                splits[index] += 1;
+                if (splits[index] < iterations[index]) {
+                    candidates.emplace(div_ceil64(iterations[index], splits[index]), index);
+                }
+            }
+        }
+        uint32_t templates = 0;
+        arrays->cu_sdpa_partial_outputs[0] = 0;
+        for (size_t i = 0; i < ranges.size(); ++i) {
+            arrays->q_token_ranges[2 * i] = ranges[i].first;
+            arrays->q_token_ranges[2 * i + 1] = ranges[i].second;
+            for (uint64_t k = 0; k < splits[i]; ++k) {
+                const uint64_t first = iterations[i] * k / splits[i], last = iterations[i] * (k + 1) / splits[i];
+                const uint32_t kv_begin = history[i].first + uint32_t(first) * kv_tokens_per_iteration;
+                const uint32_t kv_end =
+                    std::min<uint64_t>(history[i].second, uint64_t(history[i].first) + last * kv_tokens_per_iteration);
+                KH_REQUIRE(templates < max_sdpa_map_task_templates, "BiDiBlockGQA replay TaskTemplate count exceeds capacity");
+                arrays->sdpa_map_task_templates[3 * templates] = uint32_t(i);
+                arrays->sdpa_map_task_templates[3 * templates + 1] = kv_begin;
+                arrays->sdpa_map_task_templates[3 * templates + 2] = kv_end;
+                ++templates;
+            }
+            // the padded template whose index is the block partial's slot
+            KH_REQUIRE(templates < max_sdpa_map_task_templates, "BiDiBlockGQA replay TaskTemplate count exceeds capacity");
+            for (int f = 0; f < 3; ++f) arrays->sdpa_map_task_templates[3 * templates + f] = 0xffffffffu;
+            ++templates;
+            arrays->cu_sdpa_partial_outputs[i + 1] = templates;
+        }
+        const uint32_t total = next_pow2(templates);
+        KH_REQUIRE(total <= max_sdpa_map_task_templates, "BiDiBlockGQA replay TaskTemplate count exceeds capacity");
+        for (uint32_t i = templates * 3; i < total * 3; ++i) arrays->sdpa_map_task_templates[i] = 0xffffffffu;
+        if (out_shape != nullptr) {
+            *out_shape = make_replay_shape(num_tokens, num_tokens, uint32_t(ranges.size()), uint32_t(ranges.size()),
+                                           templates, total, true);
+        }
+        return KH_OK;
+    });
+}
+
 }  // extern "C"
