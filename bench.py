@@ -723,6 +723,28 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     step_ms, local_ms, eager_ms = stats.tolist()
+    # The same step with the exchange as ONE kernel over NVLink peer memory (local merge, rows stored into every
+    # rank's inbox, flags, bounded wait, final merge) instead of local merge + NCCL all-gather + merge.
+    nccl = {"ms_per_step": round(step_ms, 5), "eager_ms_per_step": round(eager_ms, 5), "gpu_launches_per_step": launches}
+    peer = None
+    if world > 1 and not args.no_peer_exchange:
+        out_nccl = case["out"].clone()
+        exchange = split_kv.PeerExchange(device, rank, world, hq, d)
+        exchange.connect()
+        decode_peer = split_kv.SplitKvDecode(device, attention, world, peer_exchange=exchange)
+        decode_peer.prepare(0, local_len, partition)
+        peer_ms, peer_eager_ms, _, peer_launches = measure(decode_peer, case, True)
+        device.check(stream)
+        peer_stats = torch.tensor([peer_ms, peer_eager_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(peer_stats, op=dist.ReduceOp.MAX)
+        peer_ms, peer_eager_ms = peer_stats.tolist()
+        peer = {"ms_per_step": round(peer_ms, 5), "eager_ms_per_step": round(peer_eager_ms, 5),
+                "gpu_launches_per_step": peer_launches,
+                "max_abs_difference_from_the_nccl_form": float((case["out"].float() - out_nccl.float()).abs().max().item())}
+        step_ms, eager_ms, launches = peer_ms, peer_eager_ms, peer_launches
+        dist.barrier()
+        del decode_peer
+        exchange.close()
 
     # ---- parity: every rank restates its own slice on the CPU as one partial (m, l, o) per head, rank 0 merges the
     # partials with the reducer's formula and compares the GPU result
@@ -774,6 +796,9 @@ def measure_split_sequence(args, torch, context, rank, world, local, device, str
     total_bytes = context * 2 * hkv * d * 2
     return {"context_tokens": context, "tokens_per_gpu": local_len, "ms_per_step": round(step_ms, 5),
             "form": "eager launches" if args.no_graph else "replayed CUDA graph", "eager_ms_per_step": round(eager_ms, 5),
+            "exchange": "none (one GPU)" if world == 1 else
+            ("one kernel over NVLink peer memory" if peer is not None else "NCCL all-gather between two merge kernels"),
+            "with_nccl_all_gather": nccl, "with_peer_memory_kernel": peer,
             "local_kernel_ms": round(local_ms, 5), "exchange_ms": round(step_ms - local_ms, 5),
             "kv_gbs_total": round(total_bytes / (step_ms * 1e-3) / 1e9, 1),
             "kv_gbs_per_gpu_local": round(local_len * 2 * hkv * d * 2 / (local_ms * 1e-3) / 1e9, 1),
@@ -924,6 +949,8 @@ def main():
     parser.add_argument("--no-parity", action="store_true", help="skip the oracle check of the bench's own output")
     parser.add_argument("--no-graph", action="store_true",
                         help="one long sequence: time eager launches only, not the step replayed as a CUDA graph")
+    parser.add_argument("--no-peer-exchange", action="store_true",
+                        help="one long sequence: exchange through NCCL only, not through the peer-memory kernel")
     parser.add_argument("--no-split-kv", action="store_true",
                         help="default workload: skip the one-long-sequence measurements that follow the headline")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling captures)")

@@ -705,6 +705,35 @@ KH_API kh_status kh_combine_packed_partials(kh_device* device, kh_stream* stream
                                             uint32_t num_rows, uint32_t head_dim, kh_buffer_ref packed,
                                             kh_dtype out_dtype, kh_buffer_ref output);
 
+/* ---- cross-GPU combine in one kernel over NVLink peer memory ---------------------------------------------------
+ * No counterpart in the reference (one device). For one long sequence whose pages are split over the GPUs of a
+ * node: every GPU runs its local split-KV map, then ONE launch of kh_peer_exchange_combine on every GPU merges
+ * this GPU's partials, stores the merged (max, sum, output) rows straight into every peer's inbox (plain peer
+ * stores through NVSwitch), flags them, waits - bounded - for the other ranks' rows and writes the final output on
+ * every GPU. It stands in for kh_combine_partials + an all-gather + kh_combine_packed_partials.
+ *  - Every rank allocates an inbox of kh_peer_exchange_inbox_bytes() with kh_buffer_alloc (zero filled: the step
+ *    counters start at zero), exports it (kh_ipc_export, a 64-byte CUDA IPC handle to hand to the other processes
+ *    by any host channel), imports the peers' (kh_ipc_import) and creates the exchange with the `world` inbox
+ *    pointers in rank order, its own entry being the local buffer.
+ *  - Every rank must call combine the same number of times: a call is step n on every rank. Calls of one rank are
+ *    ordered on its stream. The kernels of the ranks wait for one another, so every rank needs a GPU of its own.
+ *  - A peer that does not arrive within the device's wait limit (kh_device_set_wait_limit) sets bit 0 of the status
+ *    word; the output row is then not written and the kernel returns.
+ *  - num_partials may be 0 (a rank that holds no token of the sequence): it contributes empty rows. */
+typedef struct kh_peer_exchange kh_peer_exchange;
+KH_API kh_status kh_peer_exchange_inbox_bytes(uint32_t world, uint32_t num_rows, uint32_t head_dim, uint64_t* out);
+KH_API kh_status kh_ipc_export(kh_device* device, kh_buffer_ref buffer, uint8_t* handle64);
+KH_API kh_status kh_ipc_import(kh_device* device, const uint8_t* handle64, void** out);
+KH_API kh_status kh_ipc_close(kh_device* device, void* ptr);
+KH_API kh_status kh_peer_exchange_create(kh_device* device, uint32_t rank, uint32_t world, uint32_t num_rows,
+                                         uint32_t head_dim, void* const* inboxes, kh_peer_exchange** out);
+KH_API kh_status kh_peer_exchange_destroy(kh_peer_exchange* exchange);
+/* Local partials as kh_combine_partials takes them: exp_sums / max_logits f32 [num_partials][num_rows],
+ * partial_output f32 [num_partials][num_rows][head_dim]; output [num_rows][head_dim] in out_dtype. */
+KH_API kh_status kh_peer_exchange_combine(kh_peer_exchange* exchange, kh_stream* stream, uint32_t num_partials,
+                                          kh_buffer_ref exp_sums, kh_buffer_ref max_logits,
+                                          kh_buffer_ref partial_output, kh_dtype out_dtype, kh_buffer_ref output);
+
 #ifdef __cplusplus
 }
 #endif

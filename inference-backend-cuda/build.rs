@@ -11,7 +11,8 @@ use std::env;
 use std::path::{Path, PathBuf};
 use std::process::Command;
 
-const SOURCES: [&str; 5] = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu", "bidi_block_sdpa.cu"];
+const SOURCES: [&str; 6] =
+    ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu", "bidi_block_sdpa.cu", "peer_exchange.cu"];
 const HEADERS: [&str; 7] = ["common.h", "cuda_objects.h", "host_sdpa.h", "map_instance.h", "sdpa_map.cuh", "sdpa_tc.cuh", "sdpa_tm.cuh"];
 
 fn main() {

@@ -278,6 +278,13 @@ PROTOTYPES = {
     "kh_kv_page_write_tokens_per_page": [P(KvPageWriteConfigC), P(C.c_uint32)],
     "kh_kv_page_write_invoke": [_vp, _vp, P(KvPageWriteShapeC), P(KvPageWriteBuffersC), _u32, _u32],
     "kh_combine_packed_partials": [_vp, _vp, _u32, _u32, _u32, BufferRef, _u32, BufferRef],
+    "kh_peer_exchange_inbox_bytes": [_u32, _u32, _u32, P(C.c_uint64)],
+    "kh_ipc_export": [_vp, BufferRef, P(C.c_uint8)],
+    "kh_ipc_import": [_vp, P(C.c_uint8), P(_vp)],
+    "kh_ipc_close": [_vp, _vp],
+    "kh_peer_exchange_create": [_vp, _u32, _u32, _u32, _u32, P(_vp), P(_vp)],
+    "kh_peer_exchange_destroy": [_vp],
+    "kh_peer_exchange_combine": [_vp, _vp, _u32, BufferRef, BufferRef, BufferRef, _u32, BufferRef],
     "kh_bidi_block_sdpa_create": [_vp, P(BidiBlockSdpaConfigC), P(_vp)],
     "kh_bidi_block_sdpa_destroy": [_vp],
     "kh_bidi_block_sdpa_invoke": [_vp, _vp, P(BidiBlockSdpaShapeC), _u32, P(BidiBlockSdpaBuffersC)],

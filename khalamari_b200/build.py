@@ -16,7 +16,7 @@ LIBRARY = PACKAGE_DIR / "libkhcuda_gqa.so"
 # the same sources compiled with -DKH_GQA_MEASURE: the kernels honour KH_GQA_DEBUG (parts switched off so that the
 # others can be timed, and the switch the abort-path test uses). Never loaded unless KH_GQA_LIBRARY=measure.
 MEASURE_LIBRARY = PACKAGE_DIR / "libkhcuda_gqa_measure.so"
-SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu", "bidi_block_sdpa.cu"]
+SOURCES = ["host_sdpa.cpp", "sdpa_api.cu", "sdpa_fp8.cu", "kv_page_write.cu", "bidi_block_sdpa.cu", "peer_exchange.cu"]
 HEADERS = ["common.h", "cuda_objects.h", "host_sdpa.h", "map_instance.h", "sdpa_map.cuh", "sdpa_tc.cuh", "sdpa_tm.cuh", "../../include/kh_gqa.h"]
 
 

@@ -92,6 +92,75 @@ def gather_records(local_record, group=None):
     return gathered
 
 
+# -- exchange over peer memory ----------------------------------------------------------------------------
+class PeerExchange:
+    """One rank's end of the peer-memory exchange (``kh_peer_exchange_*``): an inbox every other rank of the node
+    writes its merged rows into, and the mapped inboxes of the others. ``combine`` is ONE kernel launch: local
+    merge of this rank's partials, rows stored into every inbox over NVLink, flags, a bounded wait for the other
+    ranks' rows, final merge into ``output``. Every rank must call it the same number of times.
+
+    ``connect`` exchanges the CUDA IPC handles of the inboxes through ``torch.distributed`` (host side, once)."""
+
+    def __init__(self, device: Device, rank: int, world: int, num_rows: int, head_dim: int):
+        import ctypes as C
+
+        self.device, self.rank, self.world, self.rows, self.head_dim = device, rank, world, num_rows, head_dim
+        size = C.c_uint64()
+        abi.call("kh_peer_exchange_inbox_bytes", world, num_rows, head_dim, C.byref(size))
+        self.inbox = Buffer.new_zeroed(device, size.value)
+        self.handle = None
+        self._imported = []
+
+    def export_handle(self) -> bytes:
+        import ctypes as C
+        raw = (C.c_uint8 * 64)()
+        abi.call("kh_ipc_export", self.device.handle, self.inbox.ref, raw)
+        return bytes(raw)
+
+    def attach(self, inbox_pointers) -> None:
+        """``inbox_pointers[r]``: device address of rank r's inbox as this process sees it (own entry: the local
+        buffer)."""
+        import ctypes as C
+        pointers = (C.c_void_p * self.world)(*[C.c_void_p(int(ptr)) for ptr in inbox_pointers])
+        handle = C.c_void_p()
+        abi.call("kh_peer_exchange_create", self.device.handle, self.rank, self.world, self.rows, self.head_dim, pointers,
+                 C.byref(handle))
+        self.handle = handle
+
+    def connect(self, group=None) -> None:
+        import ctypes as C
+
+        import torch.distributed as dist
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.export_handle(), group=group)
+        pointers = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                pointers.append(self.inbox.ref.ptr)
+                continue
+            mapped = C.c_void_p()
+            abi.call("kh_ipc_import", self.device.handle, (C.c_uint8 * 64).from_buffer_copy(raw), C.byref(mapped))
+            self._imported.append(mapped)
+            pointers.append(mapped.value)
+        self.attach(pointers)
+        dist.barrier(group=group)  # every rank has mapped every inbox before the first kernel writes into one
+
+    def combine(self, stream: Stream, num_partials: int, exp_sums: Buffer, max_logits: Buffer, partial_output: Buffer,
+                out_dtype: Dtype, output: Buffer) -> None:
+        null = abi.BufferRef()
+        abi.call("kh_peer_exchange_combine", self.handle, stream.handle, num_partials,
+                 exp_sums.ref if num_partials else null, max_logits.ref if num_partials else null,
+                 partial_output.ref if num_partials else null, int(out_dtype), output.ref)
+
+    def close(self) -> None:
+        if self.handle:
+            abi.call("kh_peer_exchange_destroy", self.handle)
+            self.handle = None
+        for mapped in self._imported:
+            abi.call("kh_ipc_close", self.device.handle, mapped)
+        self._imported = []
+
+
 # -- one long sequence over several GPUs ----------------------------------------------------------------
 class SplitKvDecode:
     """Decode attention of ONE sequence whose KV pages are split in token order over the ranks of ``group``.
@@ -101,9 +170,12 @@ class SplitKvDecode:
     rank's record, all-gather of the records, merge of the gathered records into ``output`` (every rank ends
     with the full result). All launches and the collective go to torch's current stream."""
 
-    def __init__(self, device: Device, attention, world: int, group=None):
+    def __init__(self, device: Device, attention, world: int, group=None, peer_exchange: "PeerExchange | None" = None):
+        """``peer_exchange``: when given, ``record_step`` is the local map plus ONE exchange-and-merge kernel over
+        peer memory; otherwise local merge, NCCL all-gather of the records and a merge of the gathered records."""
         import torch
 
+        self.peer_exchange = peer_exchange
         self.torch = torch
         self.device = device
         self.attention = attention
@@ -168,6 +240,8 @@ class SplitKvDecode:
                     gqa_layer_index: int = 0) -> int:
         import torch.distributed as dist
 
+        if self.peer_exchange is not None:
+            return self._record_step_over_peer_memory(stream, q, kv_pages, page_ids, output, gqa_layer_index)
         launches = self.record_local(stream, q, kv_pages, page_ids, gqa_layer_index)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.local_record, group=self.group)
@@ -176,3 +250,26 @@ class SplitKvDecode:
         abi.call("kh_combine_packed_partials", self.device.handle, stream.handle, self.world, self.rows,
                  self.head_dim, self._gathered.ref, int(self.attention.io_dtype), output.ref)
         return launches + 1
+
+    def _record_step_over_peer_memory(self, stream: Stream, q: Buffer, kv_pages: Buffer, page_ids: Buffer,
+                                      output: Buffer, gqa_layer_index: int) -> int:
+        from . import sdpa, sliced_kv
+
+        attention = self.attention
+        if self.local_len == 0:
+            self.peer_exchange.combine(stream, 0, attention.partial_exp_sums, attention.partial_max_logits,
+                                       attention.partial_output, attention.io_dtype, output)
+            return 1
+        meta = attention.metadata
+        shape = meta.replay_shape()
+        execution = meta.variant()
+        if execution.kind != sdpa.MapKernelKind.SlicedKv:
+            raise abi.InvalidArgument(1, "split-KV decode runs the SlicedKv map")
+        compute = attention._sliced_kv(shape, execution)
+        compute.invoke_map(stream, sliced_kv.MapBuffers(
+            q, kv_pages, meta.req_slots(), page_ids, meta.sdpa_map_task_templates(), attention.partial_exp_sums,
+            attention.partial_max_logits, attention.partial_output), gqa_layer_index, shape.num_tokens,
+            shape.num_sdpa_map_task_templates)
+        self.peer_exchange.combine(stream, shape.num_sdpa_map_task_templates, attention.partial_exp_sums,
+                                   attention.partial_max_logits, attention.partial_output, attention.io_dtype, output)
+        return 2
