@@ -8,8 +8,8 @@
 //               (8 token rows) of each of the stage's four pages, the only uniform stride 16-token pages offer.
 //   P           eight softmax warps in two groups that take alternate stages, one thread per row: tcgen05.ld brings
 //               the thread its row's 64 scores, so the row maximum and sum need no shuffles. P goes back to
-//               tensor memory as packed 16-bit pairs (rounded part and rounding remainder, as in the warp-level
-//               kernel).
+//               tensor memory as packed 16-bit pairs of the Q/output type (A and B operands of one MMA must share
+//               their type); bf16 probabilities are followed by their rounding remainder, as in the warp-level kernel.
 //   O += P V    A = P from tensor memory, B = the V rows in shared memory, MN-major (V is stored
 //               [token][head dim], the head dim being the contiguous N dimension), N = 128, K = 16.
 // The running maximum is updated lazily: O (in tensor memory) is rescaled only when a row's maximum grows by more
@@ -133,6 +133,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     constexpr int TQ = G::kTaskSlots;
     constexpr int NSW = G::kSoftmaxWarps;
     constexpr float kRescaleLog2 = 8.0f;  // O is rescaled only when a row maximum grows by more than 2^8
+    // bf16 probabilities carry their rounding remainder in a second MMA; f16 probabilities (11 significant bits) do not
+    constexpr bool kRemainder = std::is_same<T, __nv_bfloat16>::value;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -214,8 +216,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
-    const bool balanced =
-        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+    // Tasks are dealt round-robin (task i to CTA i mod grid), not in contiguous runs: the CTAs then work on
+    // neighbouring tasks at any moment - Q tiles of the same sequence over the same K/V rows - so the rows one CTA
+    // pulls from HBM are L2 hits for the others. A chunked-prefill batch streams every sequence's K/V once per Q tile
+    // (tens of GB per step through L2); contiguous runs spread the CTAs over all sequences at once and the working
+    // set (hundreds of MB) no longer fits the 126 MB L2. There are tens of tasks per CTA, so the deal balances.
+    const bool balanced = false;
+    (void)task_range;
 
     ProducerContext producer{};
     producer.ring = ring;
@@ -236,6 +243,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     producer.active = active;
     producer.lane = lane;
 
+    // Registers follow the work: the softmax warps (two warpgroups) hold a row's 64 scores and grow to 208 registers,
+    // the warpgroup of the two issuing threads, the stream warp and the task warp shrinks to 80.
+    if (warp >= NSW) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
     if (warp == NSW + 2) {
         run_task_warp<G, P>(p, q_map, producer);
     } else if (warp == NSW + 1) {
@@ -296,7 +307,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // ------------------------------ P V issue (one thread) ---------------------------------
         if (lane == 0) {
             constexpr uint32_t kFormat = umma_format<T>();
-            // D f32; A (P, tensor memory) and B 16-bit; M = 128, N = D; B (V) MN-major
+            // D f32; A (P, tensor memory) and B 16-bit of the same type (an f16 A operand beside a bf16 B operand is
+            // not a legal descriptor: it raised an illegal-instruction error); M = 128, N = D; B (V) MN-major
             const uint32_t idesc_pv =
                 (1u << 4) | (kFormat << 7) | (kFormat << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t v_desc0 = umma_smem_desc(0, G::kBoxBytes, G::kCopyBytes);
@@ -325,7 +337,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
                         const uint64_t v = v_desc + uint64_t(((2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024) >> 4);
                         umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
-                        if (!(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
+                        // bf16 probabilities (8 significant bits) are followed by their rounding remainder; f16
+                        // probabilities (11 bits) need none
+                        if (kRemainder && !(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
                     }
                     umma_commit(empty_bar + 8 * slot);  // K and V of the stage are consumed (its Q K^T completed
                                                         // before the probabilities could be computed)
@@ -340,7 +354,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 if (mbar_try_wait(drain_bar + 8, 0)) break;
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // ------------------------------ softmax and epilogue warps -----------------------------
         // Two groups of four warps; both cover the tile's 128 rows (a warp reaches the tensor-memory lanes of
         // quadrant warp % 4) and take alternate stages: group w handles the stages whose running number has
@@ -482,7 +498,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 tmem_fence_after();
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    uint32_t packed_hi[16], packed_lo[16];  // rounded pairs and their rounding remainders
+                    uint32_t packed_hi[16], packed_lo[kRemainder ? 16 : 1];  // rounded pairs and their rounding remainders
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int c = 32 * half + 2 * j;
@@ -490,11 +506,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c + 1]), p.scale_log2e, shift));
                         l_run += p0 + p1;
                         packed_hi[j] = pack2<T>(p0, p1);
-                        const float2 r = unpack2<T>(packed_hi[j]);
-                        packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
+                        if constexpr (kRemainder) {
+                            const float2 r = unpack2<T>(packed_hi[j]);
+                            packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
+                        }
                     }
                     tmem_st16(tmem_p + 64 * sb + 16 * half + lane_base, packed_hi);
-                    tmem_st16(tmem_p + 64 * sb + 32 + 16 * half + lane_base, packed_lo);
+                    if constexpr (kRemainder) tmem_st16(tmem_p + 64 * sb + 32 + 16 * half + lane_base, packed_lo);
                 }
                 tmem_st_wait();
                 if (tile_tok + ST > t_kv_end) {
