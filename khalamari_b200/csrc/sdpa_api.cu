@@ -78,7 +78,7 @@ template <typename T>
 __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const ReduceParams p) {
     __shared__ float4 shared_acc[kReduceMaxThreads];
     __shared__ float2 shared_stat[kReduceMaxThreads];
-    const uint32_t range = blockIdx.y;
+    const uint32_t range = blockIdx.x;  // ranges on x: no 65,535 limit
     uint32_t num_active_ranges = p.num_active_ranges, num_active_tokens = p.num_active_tokens;
     if (p.active != nullptr) {
         num_active_ranges = min(p.active[p.active_range_word], num_active_ranges);
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
         // head; no shared memory, no second wave of blocks.
         const uint32_t D = p.head_dim;
         const uint32_t slots = D / 4;
-        const uint32_t head = blockIdx.x * p.heads_per_block + threadIdx.x / slots;
+        const uint32_t head = blockIdx.y * p.heads_per_block + threadIdx.x / slots;
         const uint32_t d = (threadIdx.x % slots) * 4;
         if (head >= p.num_q_heads || threadIdx.x / slots >= p.heads_per_block) return;
         const uint32_t tok = p.q_ranges != nullptr ? p.q_ranges[range * 2] : range;
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const Re
         }
         return;
     }
-    const uint32_t head = blockIdx.x;
+    const uint32_t head = blockIdx.y;
     uint32_t tok_begin = range, tok_end = range + 1;
     if (p.q_ranges != nullptr) {
         tok_begin = p.q_ranges[range * 2];
@@ -311,11 +311,23 @@ struct ComputeCommon {
     std::vector<PoolMap> pool_maps;
     std::vector<PoolMap> q_maps;
 
+    // Encoded tensor maps are kept per (address, byte length), least recently used first: a hit moves the entry to
+    // the back, a miss with the cache full drops the front. 64 entries cover a caller that rotates its Q and pool
+    // buffers (one Q buffer per in-flight step and per replay bucket); beyond that a call re-encodes on the host.
+    static constexpr size_t kTensorMapCacheEntries = 64;
+    static const CUtensorMap* find_map(std::vector<PoolMap>& maps, kh_buffer_ref buffer) {
+        for (size_t i = maps.size(); i-- > 0;) {
+            if (maps[i].ptr == buffer.ptr && maps[i].bytes == buffer.bytes) {
+                if (i + 1 != maps.size()) std::rotate(maps.begin() + i, maps.begin() + i + 1, maps.end());
+                return &maps.back().map;
+            }
+        }
+        return nullptr;
+    }
+
     // Tensor map over Q [tokens * Hq rows][head_dim], one box = the Q heads of one task for one token.
     const CUtensorMap& q_map(kh_buffer_ref q) {
-        for (const auto& entry : q_maps) {
-            if (entry.ptr == q.ptr && entry.bytes == q.bytes) return entry.map;
-        }
+        if (const CUtensorMap* hit = find_map(q_maps, q)) return *hit;
         KH_REQUIRE((reinterpret_cast<uintptr_t>(q.ptr) & 127) == 0, "q must be 128-byte aligned");
         const uint64_t rows = q.bytes / (uint64_t(head_dim) * 2);
         KH_REQUIRE(rows > 0 && rows <= 0x7fffffffull, "q holds an unsupported number of rows");
@@ -332,15 +344,13 @@ struct ComputeCommon {
                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rc != CUDA_SUCCESS) raise(KH_INTERNAL, "cuTensorMapEncodeTiled (q) failed with code %d", int(rc));
-        if (q_maps.size() >= 8) q_maps.erase(q_maps.begin());
+        if (q_maps.size() >= kTensorMapCacheEntries) q_maps.erase(q_maps.begin());
         q_maps.push_back(entry);
         return q_maps.back().map;
     }
 
     const CUtensorMap& pool_map(kh_buffer_ref pages) {
-        for (const auto& entry : pool_maps) {
-            if (entry.ptr == pages.ptr && entry.bytes == pages.bytes) return entry.map;
-        }
+        if (const CUtensorMap* hit = find_map(pool_maps, pages)) return *hit;
         KH_REQUIRE((reinterpret_cast<uintptr_t>(pages.ptr) & 127) == 0, "kv_pages must be 128-byte aligned");
         const uint64_t pool_pages = pages.bytes / page_bytes;
         KH_REQUIRE(pool_pages > 0, "kv_pages holds no complete page");
@@ -370,7 +380,7 @@ struct ComputeCommon {
                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rc != CUDA_SUCCESS) raise(KH_INTERNAL, "cuTensorMapEncodeTiled failed with code %d", int(rc));
-        if (pool_maps.size() >= 8) pool_maps.erase(pool_maps.begin());
+        if (pool_maps.size() >= kTensorMapCacheEntries) pool_maps.erase(pool_maps.begin());
         pool_maps.push_back(entry);
         return pool_maps.back().map;
     }
@@ -448,21 +458,21 @@ static void launch_map(ComputeCommon& c, kh_stream* stream, MapParams& p, kh_buf
 template <typename T>
 static void launch_reduce_typed(const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {
     ReduceParams params = p;
-    dim3 grid(p.num_q_heads, num_ranges, 1);
+    dim3 grid(num_ranges, p.num_q_heads, 1);
     // a fixed, long partial list per row (the cross-slice and cross-GPU merges) gets the widest block
     uint32_t threads = (p.cu == nullptr && p.fixed_partials > 32) ? kReduceMaxThreads : 128;
     params.heads_per_block = 1;
     const uint32_t slots = p.head_dim / 4;
     if (p.max_q_tokens == 1 && threads == 128 && slots <= 64 && 128 % slots == 0) {
         params.heads_per_block = 128 / slots;
-        grid.x = (p.num_q_heads + params.heads_per_block - 1) / params.heads_per_block;
+        grid.y = (p.num_q_heads + params.heads_per_block - 1) / params.heads_per_block;
     }
     sdpa_reduce_kernel<T><<<grid, threads, 0, stream>>>(params);
 }
 
 static void launch_reduce(kh_dtype dtype, const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {
     KH_REQUIRE(p.head_dim % 4 == 0, "head_dim must be a multiple of 4");
-    KH_REQUIRE(num_ranges <= 65535, "reduce supports at most 65535 Q-token ranges per launch");
+    KH_REQUIRE(p.num_q_heads <= 65535, "reduce supports at most 65535 Q heads");
     if (num_ranges == 0) return;
     if (dtype == KH_DTYPE_BFLOAT16) launch_reduce_typed<__nv_bfloat16>(p, num_ranges, stream);
     else if (dtype == KH_DTYPE_FLOAT16) launch_reduce_typed<__half>(p, num_ranges, stream);
