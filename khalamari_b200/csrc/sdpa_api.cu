@@ -208,23 +208,25 @@ static MapInstance make_tc_instance() {
 
 // Token-major instance over 16-bit pages (sdpa_tm.cuh): the KV tokens on the M side of the tiles, warp pairs that
 // split the head dimension.
-template <typename T, int D, int P, int NQ, int CW, int DS>
+template <typename T, int D, int P, int NQ, int CW, int DS, bool TS = false, int NR = 1>
 static MapInstance make_tm_instance() {
-    using G = TmGeometry<D, P, NQ, CW, DS, 2>;
-    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, DS, 2>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
-                       G::kStages};
+    using G = TmGeometry<D, P, NQ, CW, DS, 2, TS, NR>;
+    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, DS, 2, TS, NR>, G::kThreads, G::kSmemBytes, G::kStageTokens,
+                       G::kBoxRows, G::kStages};
 }
 
 template <typename T, int D, int P>
 static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     constexpr int PS = 1;
-    // Verify tiles of 17-32 rows (four tokens x six or eight heads): token-major, every K/V fragment loaded once
-    // for all rows. `tensor_memory` is false for the one-launch map + reduce form, which this kernel does not have.
+    // Verify tiles of 17-32 rows (four tokens x six or eight heads): token-major. `tensor_memory` is false for the
+    // one-launch map + reduce form, which this kernel does not have.
     if constexpr (P == 16) {
-        // (head_dim 256: six consumer warps, because eight warps per block leave a thread 255 registers, ten only 168)
-        if (tensor_memory && rows > 16 && rows <= 24) return make_tm_instance<T, D, P, 3, D == 256 ? 6 : 8, 2>();
+        // 17-24 rows: three groups of three warps, each warp of a group taking one n-tile of 8 rows over the whole
+        // head dimension (nine consumer warps at 168 registers). On the verify workload (four tokens x six heads,
+        // head_dim 256) this form and warp pairs that split a 32-token stage by tokens measured the same.
+        if (tensor_memory && rows > 16 && rows <= 24) return make_tm_instance<T, D, P, 3, 9, 1, false, 3>();
         if constexpr (D == 128) {
-            if (tensor_memory && rows > 24 && rows <= 32) return make_tm_instance<T, D, P, 4, 6, 2>();
+            if (tensor_memory && rows > 24 && rows <= 32) return make_tm_instance<T, D, P, 4, 6, 2, true>();
         }
     }
     if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();

@@ -8,10 +8,19 @@
 // With the tokens on M a decode task (8 rows) costs one MMA per 16 tokens x 16 head-dim elements instead of two
 // half-empty ones, every K/V fragment is loaded (and, for one-byte pages, converted) once for all Q rows of the
 // task, and a thread's accumulator is D/16 x (rows/8) x 4 registers, small enough for eight consumer warps per SM.
-// Tasks whose accumulator would still be too wide (24-32 rows, or head_dim 256 with more than 8 rows) are run by
-// warp PAIRS that split the head dimension (DS = 2): each warp of a pair contracts K Q^T over its half of the head
-// dimension, the two exchange their partial scores through shared memory, both run the (cheap) softmax on the full
-// scores and each accumulates its half of the output columns.
+// Tasks whose accumulator would still be too wide (24-32 rows, or head_dim 256 with more than 8 rows) share a stage
+// among several warps. Row split (NR > 1): the NR warps of a group each take NQ / NR n-tiles of Q rows over the
+// whole head dimension; they load the same K/V fragments (shared-memory bandwidth is not the limit here), exchange
+// nothing, and release the stage together. Or warp PAIRS (DS = 2) that split the output columns, in two forms:
+//  - TS (token split): a stage holds two 16-token tiles. Each warp of the pair computes K Q^T and the softmax for
+//    ONE of the tiles over the whole head dimension, hands its packed probabilities to the partner through shared
+//    memory, and accumulates V^T P^T of BOTH tiles for its half of the output columns. Nothing is computed twice.
+//    The running reference of a row is an integer in the log2 domain that both warps hold identically and raise
+//    lazily (only when a score exceeds it by more than 2^8): a warp that raises it says so beside its
+//    probabilities, and the partner brings its own accumulators and the received probabilities to the common
+//    reference - all factors are exact powers of two.
+//  - otherwise (head-dim split): each warp contracts K Q^T over its half of the head dimension, the two exchange
+//    their partial scores through shared memory and both run the softmax on the full scores.
 //
 // K/V pages of FP8 E4M3FN elements (KVB = 1; the reference's cache format: one byte per stored element, one unit
 // scale; components/gqa/sdpa/sliced_kv.rs:113-125, decoded on load by metal/gqa_fp8.metal:1-25). At the HBM rate a
@@ -41,15 +50,19 @@
 namespace kh {
 
 // D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps. DS: warps that
-// share a stage by splitting the head dimension (1 or 2). KVB: bytes of a stored K/V element.
-template <int D, int P, int NQ, int CW, int DS, int KVB>
+// share a stage by splitting the head dimension (1 or 2). KVB: bytes of a stored K/V element. TS: the pair splits
+// a stage's tokens for K Q^T and the softmax. NR: warps that share a stage by splitting the n-tiles of Q rows.
+template <int D, int P, int NQ, int CW, int DS, int KVB, bool TS = false, int NR = 1>
 struct TmGeometry {
     static_assert(P == 16, "the token-major kernel is built for 16-token pages (one page = one 16-token MMA tile)");
     static_assert(D == 128 || D == 256, "head_dim 128 or 256");
     static_assert(KVB == 1 || KVB == 2, "K/V elements are stored in one or two bytes");
     static_assert(DS == 1 || DS == 2, "a stage is shared by at most two warps");
     static_assert(CW % DS == 0, "consumer warps come in groups of DS");
-    static constexpr int kStageTokens = (D == 128) ? 32 : 16;
+    static_assert(!TS || DS == 2, "the token split is a form of the warp pair");
+    static_assert(NR >= 1 && NQ % NR == 0 && (NR == 1 || DS == 1), "a row split divides the n-tiles among single warps");
+    static_assert(CW % (DS * NR) == 0, "consumer warps come in groups of DS * NR");
+    static constexpr int kStageTokens = (D == 128 || TS) ? 32 : 16;
     static constexpr int kBoxRows = P;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;   // pages per stage
     static constexpr int kLineElems = 128 / KVB;                      // stored elements of a 128-byte line
@@ -63,19 +76,25 @@ struct TmGeometry {
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;
     static constexpr int kConsumerWarps = CW;
-    static constexpr int kGroups = CW / DS;                           // warp groups; a stage goes to one group
+    static constexpr int kGroups = CW / (DS * NR);                    // warp groups; a stage goes to one group
     static constexpr int kThreads = (CW + 2) * 32;                    // + stream warp + task warp
     static constexpr int kRowStride = D + 4;                          // floats; makes the parking stores conflict free
-    static constexpr int kParkFloats = kQRows * kRowStride + 4 * kQRows;  // O rows, then two sets of (max, sum) per row
+    // O rows, then two sets of (max, sum) per row and, for the token split, the second warp's share of each sum
+    static constexpr int kParkFloats = kQRows * kRowStride + 6 * kQRows;
     // Task-end merge of the groups' states through shared memory: one parking slot per group, or - where that would
     // take the stage ring's memory - half as many slots in two rounds (the second half of the groups folds its
     // state into the slots the first half parked)
-    static constexpr bool kTwoRounds = kGroups >= 3 && kGroups * kParkFloats * 4 > 64 * 1024;
+    static constexpr bool kTwoRounds = kGroups >= 2 && kGroups * kParkFloats * 4 > 48 * 1024;
     static constexpr int kSlots = kTwoRounds ? (kGroups + 1) / 2 : kGroups;
     static constexpr int kMergeBytes = kSlots * kParkFloats * 4;
     static constexpr int kScoreFloats = (kStageTokens / 16) * NQ * 4;    // a thread's scores of one stage
     // partial scores a warp hands its partner: [stage parity][warp of the pair][score][lane]
-    static constexpr int kExchangeBytes = (DS == 2) ? kGroups * 2 * 2 * kScoreFloats * 32 * 4 : 0;
+    // token split: packed probabilities (and their rounding remainders) [stage parity][warp of the pair][word][lane],
+    // then the references a warp raised [stage parity][warp][row], then [stage parity][warp] "raised" flags
+    static constexpr int kPairWords = NQ * 4;
+    static constexpr int kPairGroupBytes = 2 * 2 * kPairWords * 32 * 4 + 2 * 2 * kQRows * 4 + 32;
+    static constexpr int kExchangeBytes =
+        (DS != 2) ? 0 : TS ? kGroups * kPairGroupBytes : kGroups * 2 * 2 * kScoreFloats * 32 * 4;
     static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
     static constexpr int kFixedBytes =
@@ -83,12 +102,19 @@ struct TmGeometry {
     static constexpr int kSmemLimit = 227 * 1024 - 1024;
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
     static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
-    static constexpr int kStages = kStagesCapped / kGroups * kGroups;  // a ring slot always belongs to the same group
+    // (any depth: a ring slot may pass from group to group, see the two waits before a stage is read)
+    static constexpr int kStages = kStagesCapped;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
-    // Q fragments of a task stay in registers for the whole task (each warp holds those of its head-dim share)
-    static constexpr int kQFragmentRegs = NQ * (D / 16 / DS) * 2;
+    // Q fragments of a task stay in registers for the whole task: each warp holds those of its head-dim share, or
+    // (token split: a warp contracts over the whole head dimension) as many 16-element steps as 48-64 registers hold;
+    // the remaining steps are read from the Q tile in shared memory stage after stage (16-bit pages only)
+    static constexpr int kQStepsAll = TS ? D / 16 : D / 16 / DS;
+    static constexpr int kQStepsFit = (((KVB == 2 && D == 256) ? 48 : 64) / (NQ / NR * 2)) / 2 * 2;
+    static constexpr int kQRegSteps = kQStepsAll < kQStepsFit ? kQStepsAll : kQStepsFit;
+    static constexpr int kQFragmentRegs = NQ / NR * kQRegSteps * 2;
     static_assert(kStages >= kGroups && kStages >= 4, "shared memory ring too small");
-    static_assert(kQFragmentRegs <= 48, "the task's Q fragments must fit registers");
+    static_assert(TS || kQRegSteps == kQStepsAll, "the task's Q fragments must fit registers");
+    static_assert(KVB == 2 || kQRegSteps == kQStepsAll, "one-byte pages: all Q fragments in registers");
     static_assert(NQ >= 1 && NQ <= 4, "a task holds at most 32 Q rows here");
 };
 
@@ -127,10 +153,11 @@ __device__ __forceinline__ uint32_t q_pair_to_f16x2<__nv_bfloat16>(uint32_t pack
     return pack_f16x2(lo, hi);
 }
 
-template <typename T, int D, int P, int NQ, int CW, int DS, int KVB>
-__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW, DS, KVB>::kThreads, 1)
+template <typename T, int D, int P, int NQ, int CW, int DS, int KVB, bool TS = false, int NR = 1>
+__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW, DS, KVB, TS, NR>::kThreads, 1)
 sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
-    using G = TmGeometry<D, P, NQ, CW, DS, KVB>;
+    using G = TmGeometry<D, P, NQ, CW, DS, KVB, TS, NR>;
+    constexpr int NQW = NQ / NR;      // n-tiles of Q rows a warp works on
     // the element type the MMAs run in: f16 over one-byte pages, the Q/output type over 16-bit pages
     using M = std::conditional_t<KVB == 1, __half, T>;
     constexpr bool kRemainder = KVB == 2 && std::is_same<T, __nv_bfloat16>::value;  // P V carries P's rounding remainder
@@ -140,7 +167,11 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     constexpr int NG = G::kGroups;
     constexpr int MTK = ST / 16;      // 16-token tiles (pages) per stage
     constexpr int DK = D / 16;        // contraction steps of K Q^T = 16-element m-tiles of O^T
-    constexpr int DKW = DK / DS;      // ... of which a warp takes this many
+    constexpr int DKW = DK / DS;      // ... of which a warp takes this many (of O^T; token split: K Q^T takes all)
+    constexpr int QS = G::kQStepsAll; // contraction steps of K Q^T this warp runs
+    constexpr int QR = G::kQRegSteps; // ... of which the Q fragments of the first QR stay in registers
+    constexpr float kNoReference = -1.0e30f;  // token split: a row that has seen no visible token yet
+    constexpr float kLazyRaise = 8.0f;        // token split: the reference follows only beyond 2^8
     constexpr int RS = G::kRowStride;
     constexpr int SF = G::kScoreFloats;
     static_assert(DKW % 2 == 0, "a warp takes an even number of 16-element steps");
@@ -173,7 +204,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, DS);
+            mbar_init(empty_bar + 8 * s, DS * NR);
         }
         for (int s = 0; s < TQ; ++s) {
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
@@ -226,8 +257,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // ------------------------------ consumer warps ----------------------------------------
         const int g = lane >> 2;   // fragment row group
         const int tq = lane & 3;   // thread in quad
-        const int group = warp / DS;   // which stages this warp works on
-        const int half = warp % DS;    // which share of the head dimension
+        const int group = warp / (DS * NR);   // which stages this warp works on
+        const int half = warp % DS;           // which share of the head dimension (output columns)
+        const int n0 = ((warp / DS) % NR) * NQW;  // row split: the first n-tile of Q rows this warp works on
         // One-byte pages: row r (0-7) of a 16-token MMA tile is token 4 * (r / 2) + r % 2 of its page, row r + 8 is
         // that token + 2: a thread's accumulator pair (rows g, g + 8) then holds tokens t and t + 2, and after the
         // transposition of the packed probabilities thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of Q row g - the
@@ -248,15 +280,15 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         const uint32_t v_lane = v_tok * 128u;
         const uint32_t v_y4 = ((KVB == 1 ? uint32_t(lane) >> 4 : (k_mat & 1)) ^ (v_tok & 7)) << 4;
 
-        float o[DKW][NQ][4];
-        float m_run[NQ][2], l_run[NQ][2];
+        float o[DKW][NQW][4];
+        float m_run[NQW][2], l_run[NQW][2];
 #pragma unroll
         for (int c = 0; c < DKW; ++c)
 #pragma unroll
-            for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
+            for (int n = 0; n < NQW; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
-        for (int n = 0; n < NQ; ++n) {
-            m_run[n][0] = m_run[n][1] = -INFINITY;
+        for (int n = 0; n < NQW; ++n) {
+            m_run[n][0] = m_run[n][1] = TS ? kNoReference : -INFINITY;
             l_run[n][0] = l_run[n][1] = 0.0f;
         }
         uint32_t stage_counter = 0;
@@ -267,7 +299,8 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         const int merge_round = G::kTwoRounds ? group / NSLOT : 0;  // which merge round this warp writes in
         float* const my_park = merge + (group % NSLOT) * G::kParkFloats;
         float* const my_stats = my_park + G::kQRows * RS + merge_round * 2 * G::kQRows;
-        float* const my_exchange = exchange + group * (2 * 2 * SF * 32);
+        float* const my_sums_b = my_park + G::kQRows * RS + 4 * G::kQRows;  // [round][row]: second warp's sums
+        float* const my_exchange = exchange + group * (TS ? G::kPairGroupBytes / 4 : 2 * 2 * SF * 32);
 
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
@@ -282,12 +315,12 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             const bool write_final = p.direct != 0;
 
             // ---- per-thread row bounds: Q rows 8 n + 2 tq + j of the task
-            uint32_t lo[NQ][2], hi[NQ][2];
+            uint32_t lo[NQW][2], hi[NQW][2];
 #pragma unroll
-            for (int n = 0; n < NQ; ++n) {
+            for (int n = 0; n < NQW; ++n) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const uint32_t row = 8 * n + 2 * tq + j;
+                    const uint32_t row = 8 * (n0 + n) + 2 * tq + j;
                     const uint32_t row_tok = row / p.heads_per_task;
                     const uint32_t row_head = row % p.heads_per_task;
                     lo[n][j] = 0;
@@ -308,10 +341,10 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < DKW; ++c)
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
+                    for (int n = 0; n < NQW; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
-                for (int n = 0; n < NQ; ++n) {
-                    m_run[n][0] = m_run[n][1] = -INFINITY;
+                for (int n = 0; n < NQW; ++n) {
+                    m_run[n][0] = m_run[n][1] = TS ? kNoReference : -INFINITY;
                     l_run[n][0] = l_run[n][1] = 0.0f;
                 }
             }
@@ -320,13 +353,13 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             // permutation, thread (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g as two f16 pairs.
             // 16-bit pages: the natural fragment, elements 16 kk + 2 tq, + 1 and 16 kk + 8 + 2 tq, + 1.
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes);
-            uint32_t qb[NQ][DKW][2];
+            uint32_t qb[NQW][QR][2];
 #pragma unroll
-            for (int n = 0; n < NQ; ++n) {
-                const uint32_t row = 8 * n + g;
+            for (int n = 0; n < NQW; ++n) {
+                const uint32_t row = 8 * (n0 + n) + g;
 #pragma unroll
-                for (int k = 0; k < DKW; ++k) {
-                    const int kk = half * DKW + k;
+                for (int k = 0; k < QR; ++k) {
+                    const int kk = TS ? k : half * DKW + k;
                     const uint32_t row_addr = q_tile + (kk >> 2) * (G::kQRows * 128) + row * 128;
                     if constexpr (KVB == 1) {
                         const uint32_t chunk = (2 * (kk & 3) + (tq >> 1)) ^ (row & 7);
@@ -343,6 +376,10 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     }
                 }
             }
+            // Token split, steps QR and up: the Q fragments of two steps of one n-tile per ldmatrix .x4 (matrix bit 0
+            // picks the upper 8 elements of a step, bit 1 the second step), straight from the swizzled Q tile.
+            const uint32_t q_lane = q_tile + (lane & 7) * 128u;
+            const uint32_t q_y4 = ((((lane >> 4) << 1) | ((lane >> 3) & 1)) ^ (lane & 7)) << 4;
 
             for (; my_stage < stage_counter + t_num_tiles; my_stage += NG) {
                 const uint32_t tile = my_stage - stage_counter;
@@ -355,6 +392,13 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 }
                 const uint32_t exchange_phase = my_stages_done & 1;
                 ++my_stages_done;
+                // The ring depth need not be a multiple of the group count, so the slot's previous stage may have been
+                // another group's. A parity wait tells "this phase" from "the phase before" only: waiting for this
+                // stage's copy while the previous stage's copy is still in flight would return at once. So first
+                // wait until the previous stage of the slot has been RELEASED (its phase of the empty barrier: that
+                // phase cannot be followed by another one before this warp itself releases the slot), which
+                // implies that its copy has landed; then wait for this stage's copy.
+                if (my_stage >= uint32_t(NS) && !mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p)) continue;
                 if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p)) continue;
                 if (debug_bits(p) & 1) {
                     __syncwarp();
@@ -380,174 +424,470 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     __syncwarp();
                 }
 
-                // ---- S^T = K Q^T (raw dot products; the softmax scale is folded into the exponent below)
-                float s[MTK][NQ][4];
+                if constexpr (TS) {
+                    // ================= token split: this warp owns tile `half` of the stage =================
+                    const uint32_t own_tok = tile_tok + 16 * half;
+                    const float c2 = p.scale_log2e;
+                    float (&r_ref)[NQW][2] = m_run;  // the rows' references: log2 domain, integer valued
+                    // ---- S^T = K Q^T over the whole head dimension
+                    // (two accumulator sets, for even and odd steps: half as long a chain of dependent MMAs)
+                    float s[NQW][4], s_odd[NQW][4];
 #pragma unroll
-                for (int mt = 0; mt < MTK; ++mt)
+                    for (int n = 0; n < NQW; ++n) {
+                        s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+                        s_odd[n][0] = s_odd[n][1] = s_odd[n][2] = s_odd[n][3] = 0.0f;
+                    }
+                    {
+                        const uint32_t k_base = stage_base + half * G::kCopyBytes + k_lane;
+                        if constexpr (KVB == 1) {
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n) s[mt][n][0] = s[mt][n][1] = s[mt][n][2] = s[mt][n][3] = 0.0f;
+                            for (int k = 0; k < QS; k += 2) {
+                                uint32_t r[4];
+                                ldmatrix_x4(r, k_base + (k >> 3) * G::kBoxBytes + (k_y4 ^ ((k & 7) << 4)));
 #pragma unroll
-                for (int mt = 0; mt < MTK; ++mt) {
-                    const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
-                    if constexpr (KVB == 1) {
+                                for (int h = 0; h < 2; ++h) {
+                                    uint32_t a[4];
+                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
 #pragma unroll
-                        for (int k = 0; k < DKW; k += 2) {
-                            const int kk = half * DKW + k;  // 16-byte chunk kk of the row = elements 16 kk .. + 15
-                            uint32_t r[4];
-                            ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
+                                    for (int n = 0; n < NQW; ++n)
+                                        mma_16816<M>(h ? s_odd[n] : s[n], a, qb[n][k + h][0], qb[n][k + h][1]);
+                                }
+                            }
+                        } else {
 #pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                uint32_t a[4];
-                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                            for (int k = 0; k < QS; k += 2) {
+                                uint32_t qf[NQW][4];
+                                if (k >= QR) {
 #pragma unroll
-                                for (int n = 0; n < NQ; ++n) mma_16816<M>(s[mt][n], a, qb[n][k + h][0], qb[n][k + h][1]);
+                                    for (int n = 0; n < NQW; ++n)
+                                        ldmatrix_x4(qf[n], q_lane + (k >> 2) * (G::kQRows * 128) + n * 1024 +
+                                                               (q_y4 ^ ((2 * (k & 3)) << 4)));
+                                }
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const int kk = k + h;
+                                    uint32_t a[4];
+                                    ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
+#pragma unroll
+                                    for (int n = 0; n < NQW; ++n) {
+                                        if (k < QR) mma_16816<M>(h ? s_odd[n] : s[n], a, qb[n][kk < QR ? kk : 0][0], qb[n][kk < QR ? kk : 0][1]);
+                                        else mma_16816<M>(h ? s_odd[n] : s[n], a, qf[n][2 * h], qf[n][2 * h + 1]);
+                                    }
+                                }
                             }
                         }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < DKW; ++k) {
-                            const int kk = half * DKW + k;  // elements 16 kk .. + 15 = 16-byte chunks 2 kk, 2 kk + 1
-                            uint32_t a[4];
-                            ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
-#pragma unroll
-                            for (int n = 0; n < NQ; ++n) mma_16816<M>(s[mt][n], a, qb[n][k][0], qb[n][k][1]);
-                        }
                     }
-                }
-                if constexpr (DS == 2) {
-                    // hand the partial scores to the partner and add the partner's (addition commutes: both warps
-                    // end with the same bits)
-                    float* mine = my_exchange + (exchange_phase * 2 + half) * (SF * 32);
-                    const float* theirs = my_exchange + (exchange_phase * 2 + (half ^ 1)) * (SF * 32);
 #pragma unroll
-                    for (int mt = 0; mt < MTK; ++mt)
+                    for (int n = 0; n < NQW; ++n)
 #pragma unroll
-                        for (int n = 0; n < NQ; ++n)
+                        for (int e = 0; e < 4; ++e) s[n][e] += s_odd[n][e];
+                    // ---- mask (only where a row's visible range cuts this tile)
+                    bool cut = false;
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) mine[((mt * NQ + n) * 4 + e) * 32 + lane] = s[mt][n][e];
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
-                    if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
+                    for (int n = 0; n < NQW; ++n)
 #pragma unroll
-                    for (int mt = 0; mt < MTK; ++mt)
+                        for (int j = 0; j < 2; ++j) cut = cut || own_tok < lo[n][j] || own_tok + 16 > hi[n][j];
+                    if (__any_sync(0xffffffffu, cut)) {
 #pragma unroll
-                        for (int n = 0; n < NQ; ++n)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) s[mt][n][e] += theirs[((mt * NQ + n) * 4 + e) * 32 + lane];
-                }
-
-                // ---- mask (only where a row's visible range cuts the stage) and running maximum
-                bool cut = false;
-#pragma unroll
-                for (int n = 0; n < NQ; ++n)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) cut = cut || tile_tok < lo[n][j] || tile_tok + ST > hi[n][j];
-                if (__any_sync(0xffffffffu, cut)) {
-#pragma unroll
-                    for (int mt = 0; mt < MTK; ++mt)
-#pragma unroll
-                        for (int n = 0; n < NQ; ++n)
+                        for (int n = 0; n < NQW; ++n)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const uint32_t tok = tile_tok + 16 * mt + sig + kUpperRow * (e >> 1);
-                                if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
+                                const uint32_t tok = own_tok + sig + kUpperRow * (e >> 1);
+                                if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[n][e] = -INFINITY;
                             }
-                }
-                float alpha[NQ][2], shift[NQ][2];
-                bool rescale = false;
-#pragma unroll
-                for (int n = 0; n < NQ; ++n) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        float tile_max = fmaxf(s[0][n][j], s[0][n][j + 2]);
-#pragma unroll
-                        for (int mt = 1; mt < MTK; ++mt) tile_max = fmaxf(tile_max, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
-                        // the row's tokens are spread over the eight row groups of the warp
-                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
-                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
-                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
-                        const float m_new = fmaxf(m_run[n][j], tile_max);
-                        const float base = m_new == -INFINITY ? 0.0f : m_new;
-                        alpha[n][j] = m_run[n][j] == -INFINITY ? 1.0f : fast_exp2((m_run[n][j] - base) * p.scale_log2e);
-                        shift[n][j] = -base * p.scale_log2e;
-                        m_run[n][j] = m_new;
-                        rescale = rescale || alpha[n][j] != 1.0f;
                     }
-                }
-                if (__any_sync(0xffffffffu, rescale)) {
+                    // ---- exponent arguments against the rows' references; raise a reference only when a score
+                    // is more than 2^8 above it (or the row has none yet)
+                    float arg[NQW][4];
+                    bool exceed = false;
 #pragma unroll
-                    for (int c = 0; c < DKW; ++c)
+                    for (int n = 0; n < NQW; ++n)
 #pragma unroll
-                        for (int n = 0; n < NQ; ++n)
+                        for (int e = 0; e < 4; ++e) {
+                            arg[n][e] = fmaf(s[n][e], c2, -r_ref[n][e & 1]);
+                            exceed = exceed || arg[n][e] > kLazyRaise;
+                        }
+                    const bool raised = __any_sync(0xffffffffu, exceed);
+                    float r_before[NQW][2];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
+                    for (int n = 0; n < NQW; ++n) r_before[n][0] = r_ref[n][0], r_before[n][1] = r_ref[n][1];
+                    if (raised) {
+                        float alpha[NQW][2];
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n) {
-                        l_run[n][0] *= alpha[n][0];
-                        l_run[n][1] *= alpha[n][1];
+                        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                float tile_max = fmaxf(s[n][j], s[n][j + 2]);
+                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+                                float r_new = r_ref[n][j];
+                                if (tile_max > -INFINITY) r_new = fmaxf(r_new, ceilf(tile_max * c2));
+                                alpha[n][j] = fast_exp2(r_ref[n][j] - r_new);  // a power of two, or 0 for a first reference
+                                r_ref[n][j] = r_new;
+                                l_run[n][j] *= alpha[n][j];
+                            }
+#pragma unroll
+                        for (int c = 0; c < DKW; ++c)
+#pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
+#pragma unroll
+                        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) arg[n][e] = fmaf(s[n][e], c2, -r_ref[n][e & 1]);
                     }
-                }
-
-                // ---- P^T as the B operand of V^T P^T: exponentials, packed 16-bit pairs (rows 2 tq, 2 tq + 1 of one
-                // token), transposed across the warp so that thread (g, tq) holds its four tokens of Q row g
-                uint32_t pb[MTK][NQ][2], pr[kRemainder ? MTK : 1][kRemainder ? NQ : 1][2];
+                    // ---- probabilities of this warp's tile as the B operand of V^T P^T, and to the partner
+                    constexpr int RW = kRemainder ? 2 : 1;
+                    uint32_t own[RW][NQW][2];
 #pragma unroll
-                for (int mt = 0; mt < MTK; ++mt) {
-#pragma unroll
-                    for (int n = 0; n < NQ; ++n) {
+                    for (int n = 0; n < NQW; ++n) {
                         float pv[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
+                        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(arg[n][e]);
                         l_run[n][0] += pv[0] + pv[2];
                         l_run[n][1] += pv[1] + pv[3];
                         const uint32_t x0 = pack2<M>(pv[0], pv[1]), x1 = pack2<M>(pv[2], pv[3]);
-                        pb[mt][n][0] = movmatrix_trans(x0);
-                        pb[mt][n][1] = movmatrix_trans(x1);
+                        own[0][n][0] = movmatrix_trans(x0);
+                        own[0][n][1] = movmatrix_trans(x1);
                         if constexpr (kRemainder) {
                             const float2 r0 = unpack2<M>(x0), r1 = unpack2<M>(x1);
-                            pr[mt][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
-                            pr[mt][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
+                            own[RW - 1][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
+                            own[RW - 1][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
                         }
                     }
-                }
+                    uint32_t* const pair_words = reinterpret_cast<uint32_t*>(my_exchange);
+                    float* const pair_refs = my_exchange + 2 * 2 * G::kPairWords * 32;
+                    volatile uint32_t* const pair_flags = reinterpret_cast<volatile uint32_t*>(pair_refs + 2 * 2 * G::kQRows);
+                    {
+                        uint32_t* mine = pair_words + (exchange_phase * 2 + half) * (G::kPairWords * 32);
+#pragma unroll
+                        for (int w = 0; w < RW; ++w)
+#pragma unroll
+                            for (int n = 0; n < NQW; ++n) {
+                                mine[((w * NQW + n) * 2 + 0) * 32 + lane] = own[w][n][0];
+                                mine[((w * NQW + n) * 2 + 1) * 32 + lane] = own[w][n][1];
+                            }
+                        if (raised && g == 0) {
+#pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                                for (int j = 0; j < 2; ++j)
+                                    pair_refs[(exchange_phase * 2 + half) * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = r_ref[n][j];
+                        }
+                        if (lane == 0) pair_flags[exchange_phase * 2 + half] = raised ? 1u : 0u;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
 
-                // ---- O^T += V^T P^T over this warp's output columns
+                    // ---- O^T += V^T P^T of one tile over this warp's output columns
+                    auto accumulate_tile = [&](uint32_t mt, const uint32_t (&pb)[RW][NQW][2]) {
+                        const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
+                        if constexpr (KVB == 1) {
 #pragma unroll
-                for (int mt = 0; mt < MTK; ++mt) {
-                    const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
-                    if constexpr (KVB == 1) {
+                            for (int k = 0; k < DKW; k += 2) {
+                                const int c = half * DKW + k;
+                                uint32_t r[4];
+                                ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
 #pragma unroll
-                        for (int k = 0; k < DKW; k += 2) {
-                            const int c = half * DKW + k;  // 16-byte chunk c = output columns 16 c .. + 15
-                            uint32_t r[4];
-                            ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
+                                for (int h = 0; h < 2; ++h) {
+                                    uint32_t a[4];
+                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
 #pragma unroll
-                            for (int h = 0; h < 2; ++h) {
+                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k + h][n], a, pb[0][n][0], pb[0][n][1]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < DKW; ++k) {
+                                const int c = half * DKW + k;
                                 uint32_t a[4];
-                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                                ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
 #pragma unroll
-                                for (int n = 0; n < NQ; ++n) mma_16816<M>(o[k + h][n], a, pb[mt][n][0], pb[mt][n][1]);
+                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[0][n][0], pb[0][n][1]);
+                            }
+                            if constexpr (kRemainder) {
+                                // the remainders in a pass of their own (V fragments loaded again): an MMA right
+                                // behind the one that wrote its accumulator would wait for it
+#pragma unroll
+                                for (int k = 0; k < DKW; ++k) {
+                                    const int c = half * DKW + k;
+                                    uint32_t a[4];
+                                    ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
+#pragma unroll
+                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[RW - 1][n][0], pb[RW - 1][n][1]);
+                                }
+                            }
+                        }
+                    };
+                    accumulate_tile(uint32_t(half), own);  // while the partner's probabilities arrive
+
+                    // ---- the partner's tile
+                    if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
+                    uint32_t other[RW][NQW][2];
+                    {
+                        const uint32_t* theirs = pair_words + (exchange_phase * 2 + (half ^ 1)) * (G::kPairWords * 32);
+#pragma unroll
+                        for (int w = 0; w < RW; ++w)
+#pragma unroll
+                            for (int n = 0; n < NQW; ++n) {
+                                other[w][n][0] = theirs[((w * NQW + n) * 2 + 0) * 32 + lane];
+                                other[w][n][1] = theirs[((w * NQW + n) * 2 + 1) * 32 + lane];
+                            }
+                    }
+                    const bool partner_raised = pair_flags[exchange_phase * 2 + (half ^ 1)] != 0u;
+                    if (raised || partner_raised) {
+                        // bring both sides to the larger reference of every row
+                        bool shrink = false;
+                        float f_me[NQW][2], f_partner[NQW][2];
+#pragma unroll
+                        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const float r_partner =
+                                    partner_raised ? pair_refs[(exchange_phase * 2 + (half ^ 1)) * G::kQRows + 8 * (n0 + n) + 2 * tq + j]
+                                                   : r_before[n][j];
+                                const float common = fmaxf(r_ref[n][j], r_partner);
+                                f_me[n][j] = fast_exp2(r_ref[n][j] - common);
+                                f_partner[n][j] = fast_exp2(r_partner - common);
+                                shrink = shrink || f_me[n][j] != 1.0f;
+                                r_ref[n][j] = common;
+                                l_run[n][j] *= f_me[n][j];
+                            }
+                        if (__any_sync(0xffffffffu, shrink)) {
+#pragma unroll
+                            for (int c = 0; c < DKW; ++c)
+#pragma unroll
+                                for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) o[c][n][e] *= f_me[n][e & 1];
+                        }
+                        // the received words hold Q row 8 n + g; its factor sits in the threads with tq = g / 2
+#pragma unroll
+                        for (int n = 0; n < NQW; ++n) {
+                            const float f0 = __shfl_sync(0xffffffffu, f_partner[n][0], g >> 1);
+                            const float f1 = __shfl_sync(0xffffffffu, f_partner[n][1], g >> 1);
+                            const float f = (g & 1) ? f1 : f0;
+#pragma unroll
+                            for (int w = 0; w < RW; ++w)
+#pragma unroll
+                                for (int i = 0; i < 2; ++i) {
+                                    const float2 v = unpack2<M>(other[w][n][i]);
+                                    other[w][n][i] = pack2<M>(v.x * f, v.y * f);
+                                }
+                        }
+                    }
+                    accumulate_tile(uint32_t(half ^ 1), other);
+                } else {
+                    // ---- S^T = K Q^T (raw dot products; the softmax scale is folded into the exponent below).
+                    // A dependent MMA waits for the one before it, so the contraction steps go round KS accumulator
+                    // sets: with the tiles and n-tiles of the stage that gives at least four independent chains.
+                    constexpr int KS = MTK * NQW >= 4 ? 1 : MTK * NQW >= 2 ? 2 : 4;
+                    float s_set[KS][MTK][NQW][4];
+    #pragma unroll
+                    for (int ks = 0; ks < KS; ++ks)
+    #pragma unroll
+                        for (int mt = 0; mt < MTK; ++mt)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+                                s_set[ks][mt][n][0] = s_set[ks][mt][n][1] = s_set[ks][mt][n][2] = s_set[ks][mt][n][3] = 0.0f;
+                    if (debug_bits(p) & 2) {
+                        // measurement build only: no K Q^T
+                    } else if constexpr (KVB == 1) {
+    #pragma unroll
+                        for (int k = 0; k < DKW; k += 2) {
+                            const int kk = half * DKW + k;  // 16-byte chunk kk of the row = elements 16 kk .. + 15
+    #pragma unroll
+                            for (int mt = 0; mt < MTK; ++mt) {
+                                const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+                                uint32_t r[4];
+                                ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
+    #pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    uint32_t a[4];
+                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+    #pragma unroll
+                                    for (int n = 0; n < NQW; ++n)
+                                        mma_16816<M>(s_set[(k + h) % KS][mt][n], a, qb[n][k + h][0], qb[n][k + h][1]);
+                                }
                             }
                         }
                     } else {
-#pragma unroll
+    #pragma unroll
                         for (int k = 0; k < DKW; ++k) {
-                            const int c = half * DKW + k;  // output columns 16 c .. + 15 = 16-byte chunks 2 c, 2 c + 1
-                            uint32_t a[4];
-                            ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
-#pragma unroll
-                            for (int n = 0; n < NQ; ++n) {
-                                mma_16816<M>(o[k][n], a, pb[mt][n][0], pb[mt][n][1]);
-                                if constexpr (kRemainder) mma_16816<M>(o[k][n], a, pr[mt][n][0], pr[mt][n][1]);
+                            const int kk = half * DKW + k;  // elements 16 kk .. + 15 = 16-byte chunks 2 kk, 2 kk + 1
+    #pragma unroll
+                            for (int mt = 0; mt < MTK; ++mt) {
+                                const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+                                uint32_t a[4];
+                                ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
+    #pragma unroll
+                                for (int n = 0; n < NQW; ++n) mma_16816<M>(s_set[k % KS][mt][n], a, qb[n][k][0], qb[n][k][1]);
                             }
                         }
                     }
+                    float (&s)[MTK][NQW][4] = s_set[0];
+    #pragma unroll
+                    for (int ks = 1; ks < KS; ++ks)
+    #pragma unroll
+                        for (int mt = 0; mt < MTK; ++mt)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) s[mt][n][e] += s_set[ks][mt][n][e];
+                    if constexpr (DS == 2) {
+                        // hand the partial scores to the partner and add the partner's (addition commutes: both warps
+                        // end with the same bits)
+                        float* mine = my_exchange + (exchange_phase * 2 + half) * (SF * 32);
+                        const float* theirs = my_exchange + (exchange_phase * 2 + (half ^ 1)) * (SF * 32);
+    #pragma unroll
+                        for (int mt = 0; mt < MTK; ++mt)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) mine[((mt * NQW + n) * 4 + e) * 32 + lane] = s[mt][n][e];
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
+                        if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
+    #pragma unroll
+                        for (int mt = 0; mt < MTK; ++mt)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) s[mt][n][e] += theirs[((mt * NQW + n) * 4 + e) * 32 + lane];
+                    }
+
+                    // ---- mask (only where a row's visible range cuts the stage) and running maximum
+                    bool cut = false;
+    #pragma unroll
+                    for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                        for (int j = 0; j < 2; ++j) cut = cut || tile_tok < lo[n][j] || tile_tok + ST > hi[n][j];
+                    if (__any_sync(0xffffffffu, cut)) {
+    #pragma unroll
+                        for (int mt = 0; mt < MTK; ++mt)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const uint32_t tok = tile_tok + 16 * mt + sig + kUpperRow * (e >> 1);
+                                    if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
+                                }
+                    }
+                    float alpha[NQW][2], shift[NQW][2];
+                    bool rescale = false;
+    #pragma unroll
+                    for (int n = 0; n < NQW; ++n) {
+    #pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            float tile_max = fmaxf(s[0][n][j], s[0][n][j + 2]);
+    #pragma unroll
+                            for (int mt = 1; mt < MTK; ++mt) tile_max = fmaxf(tile_max, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
+                            // the row's tokens are spread over the eight row groups of the warp
+                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+                            const float m_new = fmaxf(m_run[n][j], tile_max);
+                            const float base = m_new == -INFINITY ? 0.0f : m_new;
+                            alpha[n][j] = m_run[n][j] == -INFINITY ? 1.0f : fast_exp2((m_run[n][j] - base) * p.scale_log2e);
+                            shift[n][j] = -base * p.scale_log2e;
+                            m_run[n][j] = m_new;
+                            rescale = rescale || alpha[n][j] != 1.0f;
+                        }
+                    }
+                    if (__any_sync(0xffffffffu, rescale)) {
+    #pragma unroll
+                        for (int c = 0; c < DKW; ++c)
+    #pragma unroll
+                            for (int n = 0; n < NQW; ++n)
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
+    #pragma unroll
+                        for (int n = 0; n < NQW; ++n) {
+                            l_run[n][0] *= alpha[n][0];
+                            l_run[n][1] *= alpha[n][1];
+                        }
+                    }
+
+                    // ---- P^T as the B operand of V^T P^T: exponentials, packed 16-bit pairs (rows 2 tq, 2 tq + 1 of one
+                    // token), transposed across the warp so that thread (g, tq) holds its four tokens of Q row g
+                    uint32_t pb[MTK][NQW][2], pr[kRemainder ? MTK : 1][kRemainder ? NQW : 1][2];
+    #pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt) {
+    #pragma unroll
+                        for (int n = 0; n < NQW; ++n) {
+                            float pv[4];
+    #pragma unroll
+                            for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
+                            l_run[n][0] += pv[0] + pv[2];
+                            l_run[n][1] += pv[1] + pv[3];
+                            const uint32_t x0 = pack2<M>(pv[0], pv[1]), x1 = pack2<M>(pv[2], pv[3]);
+                            pb[mt][n][0] = movmatrix_trans(x0);
+                            pb[mt][n][1] = movmatrix_trans(x1);
+                            if constexpr (kRemainder) {
+                                const float2 r0 = unpack2<M>(x0), r1 = unpack2<M>(x1);
+                                pr[mt][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
+                                pr[mt][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
+                            }
+                        }
+                    }
+
+                    // ---- O^T += V^T P^T over this warp's output columns
+    #pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt) {
+                        if (debug_bits(p) & 16) break;  // measurement build only: no V^T P^T
+                        const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
+                        if constexpr (KVB == 1) {
+    #pragma unroll
+                            for (int k = 0; k < DKW; k += 2) {
+                                const int c = half * DKW + k;  // 16-byte chunk c = output columns 16 c .. + 15
+                                uint32_t r[4];
+                                ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
+    #pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    uint32_t a[4];
+                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+    #pragma unroll
+                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k + h][n], a, pb[mt][n][0], pb[mt][n][1]);
+                                }
+                            }
+                        } else {
+    #pragma unroll
+                            for (int k = 0; k < DKW; ++k) {
+                                const int c = half * DKW + k;  // output columns 16 c .. + 15 = 16-byte chunks 2 c, 2 c + 1
+                                uint32_t a[4];
+                                ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
+    #pragma unroll
+                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[mt][n][0], pb[mt][n][1]);
+                            }
+                            if constexpr (kRemainder) {
+                                // the remainders in a pass of their own (V fragments loaded again): an MMA right
+                                // behind the one that wrote its accumulator would wait for it
+    #pragma unroll
+                                for (int k = 0; k < DKW; ++k) {
+                                    const int c = half * DKW + k;
+                                    uint32_t a[4];
+                                    ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
+    #pragma unroll
+                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pr[mt][n][0], pr[mt][n][1]);
+                                }
+                            }
+                        }
+                    }
+
                 }
 
                 // ---- release the stage
@@ -560,12 +900,12 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             if (t_carry & 2u) {
                 // The next task of this CTA continues these rows: nothing is merged or published now. This task's
                 // template still gets a partial, an empty one (weight zero in every merge).
-                if (warp == 0 && g == 0) {
+                if (group == 0 && half == 0 && g == 0) {
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n) {
+                    for (int n = 0; n < NQW; ++n) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const uint32_t row = 8 * n + 2 * tq + j;
+                            const uint32_t row = 8 * (n0 + n) + 2 * tq + j;
                             const uint32_t row_tok = row / p.heads_per_task;
                             const uint32_t row_head = row % p.heads_per_task;
                             if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
@@ -583,9 +923,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 
             // ---- task end: every warp parks its share of (max, sum, O^T), then every thread merges and publishes a
             // slice of the rows. Row sums first: a row's tokens are spread over the row groups.
-            float l_row[NQ][2];
+            float l_row[NQW][2];
 #pragma unroll
-            for (int n = 0; n < NQ; ++n) {
+            for (int n = 0; n < NQW; ++n) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     float l = l_run[n][j];
@@ -595,35 +935,53 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     l_row[n][j] = l;
                 }
             }
+            // The statistics every merge below works on: the running maximum as a raw dot product, or (token split)
+            // the reference in the log2 domain; a row without any visible token carries -inf.
+            constexpr bool kLog2Stats = TS;
+            float m_pub[NQW][2];
+#pragma unroll
+            for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) m_pub[n][j] = (TS && m_run[n][j] <= 0.5f * kNoReference) ? -INFINITY : m_run[n][j];
             bool merge_ok = true;
             if (merges > 0) merge_ok = mbar_wait(merged_bar, (merges - 1) & 1, abort_flag, p);  // parked states are free
             auto weight_of = [&](float m, float base) {
-                return m == -INFINITY ? 0.0f : fast_exp2((m - base) * p.scale_log2e);
+                return m == -INFINITY ? 0.0f : fast_exp2((m - base) * (kLog2Stats ? 1.0f : p.scale_log2e));
             };
             if (merge_ok) {
                 if (merge_round == 0) {
 #pragma unroll
                     for (int c = 0; c < DKW; ++c)
 #pragma unroll
-                        for (int n = 0; n < NQ; ++n)
+                        for (int n = 0; n < NQW; ++n)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                my_park[(8 * n + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1)] = o[c][n][e];
+                                my_park[(8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1)] = o[c][n][e];
                             }
                 }
                 if (g == 0 && half == 0) {
 #pragma unroll
-                    for (int n = 0; n < NQ; ++n)
+                    for (int n = 0; n < NQW; ++n)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            my_stats[8 * n + 2 * tq + j] = m_run[n][j];
-                            my_stats[G::kQRows + 8 * n + 2 * tq + j] = l_row[n][j];
+                            my_stats[8 * (n0 + n) + 2 * tq + j] = m_pub[n][j];
+                            my_stats[G::kQRows + 8 * (n0 + n) + 2 * tq + j] = l_row[n][j];
                             if (G::kTwoRounds && merge_round == 0 && group + NSLOT >= NG) {
                                 // no second-round group folds into this slot: its second statistics are empty
-                                my_stats[2 * G::kQRows + 8 * n + 2 * tq + j] = -INFINITY;
-                                my_stats[3 * G::kQRows + 8 * n + 2 * tq + j] = 0.0f;
+                                my_stats[2 * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = -INFINITY;
+                                my_stats[3 * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = 0.0f;
+                                if constexpr (TS) my_sums_b[G::kQRows + 8 * (n0 + n) + 2 * tq + j] = 0.0f;
                             }
                         }
+                }
+                if constexpr (TS) {
+                    // the second warp of a pair summed the probabilities of its own tokens
+                    if (g == 0 && half == 1) {
+#pragma unroll
+                        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) my_sums_b[merge_round * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = l_row[n][j];
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(parked_bar);
@@ -635,24 +993,24 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         // fold this warp's state into the slot a first-round group parked: both become relative to
                         // the larger of the two maxima (the statistics of the two rounds stay side by side)
                         const float* first = my_park + G::kQRows * RS;
-                        float w_slot[NQ][2], w_mine[NQ][2];
+                        float w_slot[NQW][2], w_mine[NQW][2];
 #pragma unroll
-                        for (int n = 0; n < NQ; ++n)
+                        for (int n = 0; n < NQW; ++n)
 #pragma unroll
                             for (int j = 0; j < 2; ++j) {
-                                const float m_first = first[8 * n + 2 * tq + j];
-                                const float m_new = fmaxf(m_first, m_run[n][j]);
+                                const float m_first = first[8 * (n0 + n) + 2 * tq + j];
+                                const float m_new = fmaxf(m_first, m_pub[n][j]);
                                 const float base = m_new == -INFINITY ? 0.0f : m_new;
                                 w_slot[n][j] = weight_of(m_first, base);
-                                w_mine[n][j] = weight_of(m_run[n][j], base);
+                                w_mine[n][j] = weight_of(m_pub[n][j], base);
                             }
 #pragma unroll
                         for (int c = 0; c < DKW; ++c)
 #pragma unroll
-                            for (int n = 0; n < NQ; ++n)
+                            for (int n = 0; n < NQW; ++n)
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    float* at = my_park + (8 * n + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1);
+                                    float* at = my_park + (8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1);
                                     *at = *at * w_slot[n][e & 1] + o[c][n][e] * w_mine[n][e & 1];
                                 }
                     }
@@ -677,12 +1035,14 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         const float* stats = merge + w * G::kParkFloats + G::kQRows * RS;
                         m_slot[w] = stats[row];
                         l_slot[w] = stats[G::kQRows + row];
+                        if constexpr (TS) l_slot[w] += stats[4 * G::kQRows + row];
                         if constexpr (G::kTwoRounds) {
                             const float m_second = stats[2 * G::kQRows + row];
                             const float m_new = fmaxf(m_slot[w], m_second);
                             const float base = m_new == -INFINITY ? 0.0f : m_new;
-                            l_slot[w] = l_slot[w] * weight_of(m_slot[w], base) +
-                                        stats[3 * G::kQRows + row] * weight_of(m_second, base);
+                            float l_second = stats[3 * G::kQRows + row];
+                            if constexpr (TS) l_second += stats[5 * G::kQRows + row];
+                            l_slot[w] = l_slot[w] * weight_of(m_slot[w], base) + l_second * weight_of(m_second, base);
                             m_slot[w] = m_new;
                         }
                         m_max = fmaxf(m_max, m_slot[w]);
@@ -714,8 +1074,10 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         *reinterpret_cast<float4*>(p.partial_out + index * D + d) = acc;
                         if (d == 0) {
                             p.partial_sum[index] = l_sum;
-                            // the running maximum is a raw dot product; publish the natural-log-domain logit
-                            p.partial_max[index] = l_sum > 0.0f ? m_max * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
+                            // the statistic is a raw dot product or a log2-domain reference; publish the
+                            // natural-log-domain logit
+                            p.partial_max[index] = l_sum > 0.0f ? m_max * ((kLog2Stats ? 1.0f : p.scale_log2e) * 0.6931471805599453f)
+                                                                : -INFINITY;
                         }
                     }
                 }
