@@ -206,13 +206,13 @@ static MapInstance make_tc_instance() {
     return MapInstance{sdpa_tc_kernel<T, D, P>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows, G::kStages};
 }
 
-// Token-major instance over 16-bit pages (sdpa_tm.cuh): the KV tokens on the M side of the tiles, warp pairs that
-// split the head dimension.
-template <typename T, int D, int P, int NQ, int CW, int DS, bool TS = false, int NR = 1>
+// Token-major instance over 16-bit pages (sdpa_tm.cuh): the KV tokens on the M side of the tiles, groups of NR
+// warps that take the n-tiles of Q rows between them.
+template <typename T, int D, int P, int NQ, int CW, int NR>
 static MapInstance make_tm_instance() {
-    using G = TmGeometry<D, P, NQ, CW, DS, 2, TS, NR>;
-    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, DS, 2, TS, NR>, G::kThreads, G::kSmemBytes, G::kStageTokens,
-                       G::kBoxRows, G::kStages};
+    using G = TmGeometry<D, P, NQ, CW, 2, NR>;
+    return MapInstance{sdpa_tm_kernel<T, D, P, NQ, CW, 2, NR>, G::kThreads, G::kSmemBytes, G::kStageTokens, G::kBoxRows,
+                       G::kStages};
 }
 
 template <typename T, int D, int P>
@@ -222,11 +222,10 @@ static MapInstance pick_rows(uint32_t rows, bool tensor_memory) {
     // one-launch map + reduce form, which this kernel does not have.
     if constexpr (P == 16) {
         // 17-24 rows: three groups of three warps, each warp of a group taking one n-tile of 8 rows over the whole
-        // head dimension (nine consumer warps at 168 registers). On the verify workload (four tokens x six heads,
-        // head_dim 256) this form and warp pairs that split a 32-token stage by tokens measured the same.
-        if (tensor_memory && rows > 16 && rows <= 24) return make_tm_instance<T, D, P, 3, 9, 1, false, 3>();
+        // head dimension (nine consumer warps at 168 registers); 25-32 rows at head_dim 128: two groups of four
+        if (tensor_memory && rows > 16 && rows <= 24) return make_tm_instance<T, D, P, 3, 9, 3>();
         if constexpr (D == 128) {
-            if (tensor_memory && rows > 24 && rows <= 32) return make_tm_instance<T, D, P, 4, 6, 2, true>();
+            if (tensor_memory && rows > 24 && rows <= 32) return make_tm_instance<T, D, P, 4, 8, 4>();
         }
     }
     if (rows <= 8) return make_instance<T, D, P, 1, 4, PS, true>();

@@ -8,19 +8,13 @@
 // With the tokens on M a decode task (8 rows) costs one MMA per 16 tokens x 16 head-dim elements instead of two
 // half-empty ones, every K/V fragment is loaded (and, for one-byte pages, converted) once for all Q rows of the
 // task, and a thread's accumulator is D/16 x (rows/8) x 4 registers, small enough for eight consumer warps per SM.
-// Tasks whose accumulator would still be too wide (24-32 rows, or head_dim 256 with more than 8 rows) share a stage
-// among several warps. Row split (NR > 1): the NR warps of a group each take NQ / NR n-tiles of Q rows over the
-// whole head dimension; they load the same K/V fragments (shared-memory bandwidth is not the limit here), exchange
-// nothing, and release the stage together. Or warp PAIRS (DS = 2) that split the output columns, in two forms:
-//  - TS (token split): a stage holds two 16-token tiles. Each warp of the pair computes K Q^T and the softmax for
-//    ONE of the tiles over the whole head dimension, hands its packed probabilities to the partner through shared
-//    memory, and accumulates V^T P^T of BOTH tiles for its half of the output columns. Nothing is computed twice.
-//    The running reference of a row is an integer in the log2 domain that both warps hold identically and raise
-//    lazily (only when a score exceeds it by more than 2^8): a warp that raises it says so beside its
-//    probabilities, and the partner brings its own accumulators and the received probabilities to the common
-//    reference - all factors are exact powers of two.
-//  - otherwise (head-dim split): each warp contracts K Q^T over its half of the head dimension, the two exchange
-//    their partial scores through shared memory and both run the softmax on the full scores.
+// Tasks whose accumulator would still be too wide (17-32 rows, or head_dim 256 with more than 8 rows) share a stage
+// among the NR warps of a group (row split): each warp takes NQ / NR n-tiles of Q rows over the whole head
+// dimension. The warps of a group load the same K/V fragments (shared-memory bandwidth is not the limit here),
+// exchange nothing, and release the stage together. Measured on the verify workload (24 rows, head_dim 256)
+// against warp pairs that split the head dimension and exchange partial scores (every warp then repeats the
+// softmax: 0.55 ms against 0.49 ms) and against pairs that split a 32-token stage by tokens and exchange packed
+// probabilities (the same 0.49 ms, with far more machinery): the row split is what is kept.
 //
 // K/V pages of FP8 E4M3FN elements (KVB = 1; the reference's cache format: one byte per stored element, one unit
 // scale; components/gqa/sdpa/sliced_kv.rs:113-125, decoded on load by metal/gqa_fp8.metal:1-25). At the HBM rate a
@@ -49,20 +43,16 @@
 
 namespace kh {
 
-// D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps. DS: warps that
-// share a stage by splitting the head dimension (1 or 2). KVB: bytes of a stored K/V element. TS: the pair splits
-// a stage's tokens for K Q^T and the softmax. NR: warps that share a stage by splitting the n-tiles of Q rows.
-template <int D, int P, int NQ, int CW, int DS, int KVB, bool TS = false, int NR = 1>
+// D: head dimension. P: tokens per page. NQ: n-tiles of 8 Q rows per task. CW: consumer warps. KVB: bytes of a
+// stored K/V element. NR: warps that share a stage by splitting the n-tiles of Q rows between them.
+template <int D, int P, int NQ, int CW, int KVB, int NR = 1>
 struct TmGeometry {
     static_assert(P == 16, "the token-major kernel is built for 16-token pages (one page = one 16-token MMA tile)");
     static_assert(D == 128 || D == 256, "head_dim 128 or 256");
     static_assert(KVB == 1 || KVB == 2, "K/V elements are stored in one or two bytes");
-    static_assert(DS == 1 || DS == 2, "a stage is shared by at most two warps");
-    static_assert(CW % DS == 0, "consumer warps come in groups of DS");
-    static_assert(!TS || DS == 2, "the token split is a form of the warp pair");
-    static_assert(NR >= 1 && NQ % NR == 0 && (NR == 1 || DS == 1), "a row split divides the n-tiles among single warps");
-    static_assert(CW % (DS * NR) == 0, "consumer warps come in groups of DS * NR");
-    static constexpr int kStageTokens = (D == 128 || TS) ? 32 : 16;
+    static_assert(NR >= 1 && NQ % NR == 0, "a row split divides the n-tiles among the warps of a group");
+    static_assert(CW % NR == 0, "consumer warps come in groups of NR");
+    static constexpr int kStageTokens = (D == 128) ? 32 : 16;
     static constexpr int kBoxRows = P;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;   // pages per stage
     static constexpr int kLineElems = 128 / KVB;                      // stored elements of a 128-byte line
@@ -76,45 +66,28 @@ struct TmGeometry {
     static constexpr int kQBytes = kQRows * D * 2;
     static constexpr int kTaskSlots = 2;
     static constexpr int kConsumerWarps = CW;
-    static constexpr int kGroups = CW / (DS * NR);                    // warp groups; a stage goes to one group
+    static constexpr int kGroups = CW / NR;                           // warp groups; a stage goes to one group
     static constexpr int kThreads = (CW + 2) * 32;                    // + stream warp + task warp
     static constexpr int kRowStride = D + 4;                          // floats; makes the parking stores conflict free
-    // O rows, then two sets of (max, sum) per row and, for the token split, the second warp's share of each sum
-    static constexpr int kParkFloats = kQRows * kRowStride + 6 * kQRows;
+    static constexpr int kParkFloats = kQRows * kRowStride + 4 * kQRows;  // O rows, then two sets of (max, sum) per row
     // Task-end merge of the groups' states through shared memory: one parking slot per group, or - where that would
     // take the stage ring's memory - half as many slots in two rounds (the second half of the groups folds its
     // state into the slots the first half parked)
     static constexpr bool kTwoRounds = kGroups >= 2 && kGroups * kParkFloats * 4 > 48 * 1024;
     static constexpr int kSlots = kTwoRounds ? (kGroups + 1) / 2 : kGroups;
     static constexpr int kMergeBytes = kSlots * kParkFloats * 4;
-    static constexpr int kScoreFloats = (kStageTokens / 16) * NQ * 4;    // a thread's scores of one stage
-    // partial scores a warp hands its partner: [stage parity][warp of the pair][score][lane]
-    // token split: packed probabilities (and their rounding remainders) [stage parity][warp of the pair][word][lane],
-    // then the references a warp raised [stage parity][warp][row], then [stage parity][warp] "raised" flags
-    static constexpr int kPairWords = NQ * 4;
-    static constexpr int kPairGroupBytes = 2 * 2 * kPairWords * 32 * 4 + 2 * 2 * kQRows * 4 + 32;
-    static constexpr int kExchangeBytes =
-        (DS != 2) ? 0 : TS ? kGroups * kPairGroupBytes : kGroups * 2 * 2 * kScoreFloats * 32 * 4;
     static constexpr int kPidBytes = kTaskSlots * kMaxPidsPerSegment * 4;
     static constexpr int kTaskBytes = kTaskSlots * static_cast<int>(sizeof(TaskSlot));
-    static constexpr int kFixedBytes =
-        kTaskSlots * kQBytes + kMergeBytes + kExchangeBytes + kPidBytes + kTaskBytes + 1024;
+    static constexpr int kFixedBytes = kTaskSlots * kQBytes + kMergeBytes + kPidBytes + kTaskBytes + 1024;
     static constexpr int kSmemLimit = 227 * 1024 - 1024;
     static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
-    static constexpr int kStagesCapped = kStagesFit > 24 ? 24 : kStagesFit;
     // (any depth: a ring slot may pass from group to group, see the two waits before a stage is read)
-    static constexpr int kStages = kStagesCapped;
+    static constexpr int kStages = kStagesFit > 24 ? 24 : kStagesFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes + 1024;
-    // Q fragments of a task stay in registers for the whole task: each warp holds those of its head-dim share, or
-    // (token split: a warp contracts over the whole head dimension) as many 16-element steps as 48-64 registers hold;
-    // the remaining steps are read from the Q tile in shared memory stage after stage (16-bit pages only)
-    static constexpr int kQStepsAll = TS ? D / 16 : D / 16 / DS;
-    static constexpr int kQStepsFit = (((KVB == 2 && D == 256) ? 48 : 64) / (NQ / NR * 2)) / 2 * 2;
-    static constexpr int kQRegSteps = kQStepsAll < kQStepsFit ? kQStepsAll : kQStepsFit;
-    static constexpr int kQFragmentRegs = NQ / NR * kQRegSteps * 2;
+    // Q fragments of a task stay in registers for the whole task
+    static constexpr int kQFragmentRegs = NQ / NR * (D / 16) * 2;
     static_assert(kStages >= kGroups && kStages >= 4, "shared memory ring too small");
-    static_assert(TS || kQRegSteps == kQStepsAll, "the task's Q fragments must fit registers");
-    static_assert(KVB == 2 || kQRegSteps == kQStepsAll, "one-byte pages: all Q fragments in registers");
+    static_assert(kQFragmentRegs <= 64, "the task's Q fragments must fit registers");
     static_assert(NQ >= 1 && NQ <= 4, "a task holds at most 32 Q rows here");
 };
 
@@ -153,10 +126,10 @@ __device__ __forceinline__ uint32_t q_pair_to_f16x2<__nv_bfloat16>(uint32_t pack
     return pack_f16x2(lo, hi);
 }
 
-template <typename T, int D, int P, int NQ, int CW, int DS, int KVB, bool TS = false, int NR = 1>
-__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW, DS, KVB, TS, NR>::kThreads, 1)
+template <typename T, int D, int P, int NQ, int CW, int KVB, int NR = 1>
+__global__ void __launch_bounds__(TmGeometry<D, P, NQ, CW, KVB, NR>::kThreads, 1)
 sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
-    using G = TmGeometry<D, P, NQ, CW, DS, KVB, TS, NR>;
+    using G = TmGeometry<D, P, NQ, CW, KVB, NR>;
     constexpr int NQW = NQ / NR;      // n-tiles of Q rows a warp works on
     // the element type the MMAs run in: f16 over one-byte pages, the Q/output type over 16-bit pages
     using M = std::conditional_t<KVB == 1, __half, T>;
@@ -167,25 +140,17 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     constexpr int NG = G::kGroups;
     constexpr int MTK = ST / 16;      // 16-token tiles (pages) per stage
     constexpr int DK = D / 16;        // contraction steps of K Q^T = 16-element m-tiles of O^T
-    constexpr int DKW = DK / DS;      // ... of which a warp takes this many (of O^T; token split: K Q^T takes all)
-    constexpr int QS = G::kQStepsAll; // contraction steps of K Q^T this warp runs
-    constexpr int QR = G::kQRegSteps; // ... of which the Q fragments of the first QR stay in registers
-    constexpr float kNoReference = -1.0e30f;  // token split: a row that has seen no visible token yet
-    constexpr float kLazyRaise = 8.0f;        // token split: the reference follows only beyond 2^8
     constexpr int RS = G::kRowStride;
-    constexpr int SF = G::kScoreFloats;
-    static_assert(DKW % 2 == 0, "a warp takes an even number of 16-element steps");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
     uint8_t* q_ring = ring + NS * G::kStageBytes;
     float* merge = reinterpret_cast<float*>(q_ring + TQ * G::kQBytes);
-    float* exchange = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
-    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(exchange) + G::kExchangeBytes);
+    uint32_t* pid_smem = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(merge) + G::kMergeBytes);
     TaskSlot* task_ring = reinterpret_cast<TaskSlot*>(reinterpret_cast<uint8_t*>(pid_smem) + G::kPidBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
-    constexpr int kNumBars = 2 * NS + 3 * TQ + 3 + NG;
+    constexpr int kNumBars = 2 * NS + 3 * TQ + 3;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
     uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 2;
 
@@ -199,12 +164,11 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t parked_bar = smem_addr(bars + 2 * NS + 3 * TQ);      // every consumer warp parked its state
     const uint32_t merged_bar = smem_addr(bars + 2 * NS + 3 * TQ + 1);  // every consumer warp read the parked states
     const uint32_t folded_bar = smem_addr(bars + 2 * NS + 3 * TQ + 2);  // second merge round: every warp folded its state
-    const uint32_t exchange_bar = smem_addr(bars + 2 * NS + 3 * TQ + 3);  // [NG] both warps of a pair wrote their scores
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, DS * NR);
+            mbar_init(empty_bar + 8 * s, NR);  // every warp of the group releases the stage
         }
         for (int s = 0; s < TQ; ++s) {
             mbar_init(task_full_bar + 8 * s, p.visible != nullptr ? 33 : 1);
@@ -214,7 +178,6 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         mbar_init(parked_bar, CW);
         mbar_init(merged_bar, CW);
         mbar_init(folded_bar, CW);
-        for (int s = 0; s < NG; ++s) mbar_init(exchange_bar + 8 * s, DS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -257,9 +220,8 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // ------------------------------ consumer warps ----------------------------------------
         const int g = lane >> 2;   // fragment row group
         const int tq = lane & 3;   // thread in quad
-        const int group = warp / (DS * NR);   // which stages this warp works on
-        const int half = warp % DS;           // which share of the head dimension (output columns)
-        const int n0 = ((warp / DS) % NR) * NQW;  // row split: the first n-tile of Q rows this warp works on
+        const int group = warp / NR;          // which stages this warp works on
+        const int n0 = (warp % NR) * NQW;     // row split: the first n-tile of Q rows this warp works on
         // One-byte pages: row r (0-7) of a 16-token MMA tile is token 4 * (r / 2) + r % 2 of its page, row r + 8 is
         // that token + 2: a thread's accumulator pair (rows g, g + 8) then holds tokens t and t + 2, and after the
         // transposition of the packed probabilities thread (g, tq) holds tokens 4 tq .. 4 tq + 3 of Q row g - the
@@ -280,27 +242,24 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         const uint32_t v_lane = v_tok * 128u;
         const uint32_t v_y4 = ((KVB == 1 ? uint32_t(lane) >> 4 : (k_mat & 1)) ^ (v_tok & 7)) << 4;
 
-        float o[DKW][NQW][4];
+        float o[DK][NQW][4];
         float m_run[NQW][2], l_run[NQW][2];
 #pragma unroll
-        for (int c = 0; c < DKW; ++c)
+        for (int c = 0; c < DK; ++c)
 #pragma unroll
             for (int n = 0; n < NQW; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
         for (int n = 0; n < NQW; ++n) {
-            m_run[n][0] = m_run[n][1] = TS ? kNoReference : -INFINITY;
+            m_run[n][0] = m_run[n][1] = -INFINITY;
             l_run[n][0] = l_run[n][1] = 0.0f;
         }
         uint32_t stage_counter = 0;
         uint32_t my_stage = group, my_slot = group, my_parity = 0;
-        uint32_t my_stages_done = 0;  // stages this group has worked on (phase of its exchange barrier)
         uint32_t merges = 0;          // merges this CTA has run (phase of the two merge barriers)
         constexpr int NSLOT = G::kSlots;
         const int merge_round = G::kTwoRounds ? group / NSLOT : 0;  // which merge round this warp writes in
         float* const my_park = merge + (group % NSLOT) * G::kParkFloats;
         float* const my_stats = my_park + G::kQRows * RS + merge_round * 2 * G::kQRows;
-        float* const my_sums_b = my_park + G::kQRows * RS + 4 * G::kQRows;  // [round][row]: second warp's sums
-        float* const my_exchange = exchange + group * (TS ? G::kPairGroupBytes / 4 : 2 * 2 * SF * 32);
 
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
@@ -339,12 +298,12 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             }
             if (!(t_carry & 1u)) {
 #pragma unroll
-                for (int c = 0; c < DKW; ++c)
+                for (int c = 0; c < DK; ++c)
 #pragma unroll
                     for (int n = 0; n < NQW; ++n) o[c][n][0] = o[c][n][1] = o[c][n][2] = o[c][n][3] = 0.0f;
 #pragma unroll
                 for (int n = 0; n < NQW; ++n) {
-                    m_run[n][0] = m_run[n][1] = TS ? kNoReference : -INFINITY;
+                    m_run[n][0] = m_run[n][1] = -INFINITY;
                     l_run[n][0] = l_run[n][1] = 0.0f;
                 }
             }
@@ -353,13 +312,12 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             // permutation, thread (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g as two f16 pairs.
             // 16-bit pages: the natural fragment, elements 16 kk + 2 tq, + 1 and 16 kk + 8 + 2 tq, + 1.
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes);
-            uint32_t qb[NQW][QR][2];
+            uint32_t qb[NQW][DK][2];
 #pragma unroll
             for (int n = 0; n < NQW; ++n) {
                 const uint32_t row = 8 * (n0 + n) + g;
 #pragma unroll
-                for (int k = 0; k < QR; ++k) {
-                    const int kk = TS ? k : half * DKW + k;
+                for (int kk = 0; kk < DK; ++kk) {
                     const uint32_t row_addr = q_tile + (kk >> 2) * (G::kQRows * 128) + row * 128;
                     if constexpr (KVB == 1) {
                         const uint32_t chunk = (2 * (kk & 3) + (tq >> 1)) ^ (row & 7);
@@ -367,20 +325,15 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
                                      : "=r"(w0), "=r"(w1)
                                      : "r"(row_addr + (chunk << 4) + 8 * (tq & 1)));
-                        qb[n][k][0] = q_pair_to_f16x2<T>(w0);
-                        qb[n][k][1] = q_pair_to_f16x2<T>(w1);
+                        qb[n][kk][0] = q_pair_to_f16x2<T>(w0);
+                        qb[n][kk][1] = q_pair_to_f16x2<T>(w1);
                     } else {
                         const uint32_t c0 = (2 * (kk & 3)) ^ (row & 7), c1 = (2 * (kk & 3) + 1) ^ (row & 7);
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][k][0]) : "r"(row_addr + (c0 << 4) + 4 * tq));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][k][1]) : "r"(row_addr + (c1 << 4) + 4 * tq));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][kk][0]) : "r"(row_addr + (c0 << 4) + 4 * tq));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qb[n][kk][1]) : "r"(row_addr + (c1 << 4) + 4 * tq));
                     }
                 }
             }
-            // Token split, steps QR and up: the Q fragments of two steps of one n-tile per ldmatrix .x4 (matrix bit 0
-            // picks the upper 8 elements of a step, bit 1 the second step), straight from the swizzled Q tile.
-            const uint32_t q_lane = q_tile + (lane & 7) * 128u;
-            const uint32_t q_y4 = ((((lane >> 4) << 1) | ((lane >> 3) & 1)) ^ (lane & 7)) << 4;
-
             for (; my_stage < stage_counter + t_num_tiles; my_stage += NG) {
                 const uint32_t tile = my_stage - stage_counter;
                 const uint32_t slot = my_slot;
@@ -390,8 +343,6 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     my_slot -= NS;
                     my_parity ^= 1;
                 }
-                const uint32_t exchange_phase = my_stages_done & 1;
-                ++my_stages_done;
                 // The ring depth need not be a multiple of the group count, so the slot's previous stage may have been
                 // another group's. A parity wait tells "this phase" from "the phase before" only: waiting for this
                 // stage's copy while the previous stage's copy is still in flight would return at once. So first
@@ -413,9 +364,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 // produce NaN.
                 if (tile_tok + ST > t_kv_end) {
                     const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0u;
-                    constexpr uint32_t kChunksPerRow = D * KVB / 16 / DS;  // 16-byte chunks of this warp's columns
+                    constexpr uint32_t kChunksPerRow = D * KVB / 16;  // 16-byte chunks of a row
                     for (uint32_t idx = first_bad * kChunksPerRow + lane; idx < uint32_t(ST) * kChunksPerRow; idx += 32) {
-                        const uint32_t r = idx / kChunksPerRow, c = half * kChunksPerRow + idx % kChunksPerRow;
+                        const uint32_t r = idx / kChunksPerRow, c = idx % kChunksPerRow;
                         // (chunk c of row r sits at position c ^ (r & 7) of its 128-byte line)
                         const uint32_t addr = stage_base + (r / 16) * G::kCopyBytes + G::kPlaneBoxBytes +
                                               (c >> 3) * G::kBoxBytes + (r % 16) * 128 + (((c & 7) ^ (r & 7)) << 4);
@@ -424,471 +375,186 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     __syncwarp();
                 }
 
-                if constexpr (TS) {
-                    // ================= token split: this warp owns tile `half` of the stage =================
-                    const uint32_t own_tok = tile_tok + 16 * half;
-                    const float c2 = p.scale_log2e;
-                    float (&r_ref)[NQW][2] = m_run;  // the rows' references: log2 domain, integer valued
-                    // ---- S^T = K Q^T over the whole head dimension
-                    // (two accumulator sets, for even and odd steps: half as long a chain of dependent MMAs)
-                    float s[NQW][4], s_odd[NQW][4];
+                // ---- S^T = K Q^T (raw dot products; the softmax scale is folded into the exponent below).
+                // A dependent MMA waits for the one before it, so the contraction steps go round KS accumulator
+                // sets: with the tiles and n-tiles of the stage that gives at least four independent chains.
+                constexpr int KS = MTK * NQW >= 4 ? 1 : MTK * NQW >= 2 ? 2 : 4;
+                float s_set[KS][MTK][NQW][4];
 #pragma unroll
-                    for (int n = 0; n < NQW; ++n) {
-                        s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
-                        s_odd[n][0] = s_odd[n][1] = s_odd[n][2] = s_odd[n][3] = 0.0f;
-                    }
-                    {
-                        const uint32_t k_base = stage_base + half * G::kCopyBytes + k_lane;
-                        if constexpr (KVB == 1) {
+                for (int ks = 0; ks < KS; ++ks)
 #pragma unroll
-                            for (int k = 0; k < QS; k += 2) {
-                                uint32_t r[4];
-                                ldmatrix_x4(r, k_base + (k >> 3) * G::kBoxBytes + (k_y4 ^ ((k & 7) << 4)));
+                    for (int mt = 0; mt < MTK; ++mt)
 #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    uint32_t a[4];
-                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                        for (int n = 0; n < NQW; ++n)
+                            s_set[ks][mt][n][0] = s_set[ks][mt][n][1] = s_set[ks][mt][n][2] = s_set[ks][mt][n][3] = 0.0f;
+                if (debug_bits(p) & 2) {
+                    // measurement build only: no K Q^T
+                } else if constexpr (KVB == 1) {
 #pragma unroll
-                                    for (int n = 0; n < NQW; ++n)
-                                        mma_16816<M>(h ? s_odd[n] : s[n], a, qb[n][k + h][0], qb[n][k + h][1]);
-                                }
-                            }
-                        } else {
+                    for (int k = 0; k < DK; k += 2) {
+                        const int kk = k;  // 16-byte chunk kk of the row = elements 16 kk .. + 15
 #pragma unroll
-                            for (int k = 0; k < QS; k += 2) {
-                                uint32_t qf[NQW][4];
-                                if (k >= QR) {
+                        for (int mt = 0; mt < MTK; ++mt) {
+                            const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+                            uint32_t r[4];
+                            ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
 #pragma unroll
-                                    for (int n = 0; n < NQW; ++n)
-                                        ldmatrix_x4(qf[n], q_lane + (k >> 2) * (G::kQRows * 128) + n * 1024 +
-                                                               (q_y4 ^ ((2 * (k & 3)) << 4)));
-                                }
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t a[4];
+                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
 #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    const int kk = k + h;
-                                    uint32_t a[4];
-                                    ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
-#pragma unroll
-                                    for (int n = 0; n < NQW; ++n) {
-                                        if (k < QR) mma_16816<M>(h ? s_odd[n] : s[n], a, qb[n][kk < QR ? kk : 0][0], qb[n][kk < QR ? kk : 0][1]);
-                                        else mma_16816<M>(h ? s_odd[n] : s[n], a, qf[n][2 * h], qf[n][2 * h + 1]);
-                                    }
-                                }
+                                for (int n = 0; n < NQW; ++n)
+                                    mma_16816<M>(s_set[(k + h) % KS][mt][n], a, qb[n][k + h][0], qb[n][k + h][1]);
                             }
                         }
                     }
+                } else {
 #pragma unroll
-                    for (int n = 0; n < NQW; ++n)
+                    for (int k = 0; k < DK; ++k) {
+                        const int kk = k;  // elements 16 kk .. + 15 = 16-byte chunks 2 kk, 2 kk + 1
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) s[n][e] += s_odd[n][e];
-                    // ---- mask (only where a row's visible range cuts this tile)
-                    bool cut = false;
+                        for (int mt = 0; mt < MTK; ++mt) {
+                            const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
+                            uint32_t a[4];
+                            ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
 #pragma unroll
-                    for (int n = 0; n < NQW; ++n)
+                            for (int n = 0; n < NQW; ++n) mma_16816<M>(s_set[k % KS][mt][n], a, qb[n][k][0], qb[n][k][1]);
+                        }
+                    }
+                }
+                float (&s)[MTK][NQW][4] = s_set[0];
 #pragma unroll
-                        for (int j = 0; j < 2; ++j) cut = cut || own_tok < lo[n][j] || own_tok + 16 > hi[n][j];
-                    if (__any_sync(0xffffffffu, cut)) {
+                for (int ks = 1; ks < KS; ++ks)
+#pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt)
+#pragma unroll
+                        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) s[mt][n][e] += s_set[ks][mt][n][e];
+                // ---- mask (only where a row's visible range cuts the stage) and running maximum
+                bool cut = false;
+#pragma unroll
+                for (int n = 0; n < NQW; ++n)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) cut = cut || tile_tok < lo[n][j] || tile_tok + ST > hi[n][j];
+                if (__any_sync(0xffffffffu, cut)) {
+#pragma unroll
+                    for (int mt = 0; mt < MTK; ++mt)
 #pragma unroll
                         for (int n = 0; n < NQW; ++n)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const uint32_t tok = own_tok + sig + kUpperRow * (e >> 1);
-                                if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[n][e] = -INFINITY;
+                                const uint32_t tok = tile_tok + 16 * mt + sig + kUpperRow * (e >> 1);
+                                if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
                             }
+                }
+                float alpha[NQW][2], shift[NQW][2];
+                bool rescale = false;
+#pragma unroll
+                for (int n = 0; n < NQW; ++n) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float tile_max = fmaxf(s[0][n][j], s[0][n][j + 2]);
+#pragma unroll
+                        for (int mt = 1; mt < MTK; ++mt) tile_max = fmaxf(tile_max, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
+                        // the row's tokens are spread over the eight row groups of the warp
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+                        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+                        const float m_new = fmaxf(m_run[n][j], tile_max);
+                        const float base = m_new == -INFINITY ? 0.0f : m_new;
+                        alpha[n][j] = m_run[n][j] == -INFINITY ? 1.0f : fast_exp2((m_run[n][j] - base) * p.scale_log2e);
+                        shift[n][j] = -base * p.scale_log2e;
+                        m_run[n][j] = m_new;
+                        rescale = rescale || alpha[n][j] != 1.0f;
                     }
-                    // ---- exponent arguments against the rows' references; raise a reference only when a score
-                    // is more than 2^8 above it (or the row has none yet)
-                    float arg[NQW][4];
-                    bool exceed = false;
+                }
+                if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-                    for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            arg[n][e] = fmaf(s[n][e], c2, -r_ref[n][e & 1]);
-                            exceed = exceed || arg[n][e] > kLazyRaise;
-                        }
-                    const bool raised = __any_sync(0xffffffffu, exceed);
-                    float r_before[NQW][2];
-#pragma unroll
-                    for (int n = 0; n < NQW; ++n) r_before[n][0] = r_ref[n][0], r_before[n][1] = r_ref[n][1];
-                    if (raised) {
-                        float alpha[NQW][2];
+                    for (int c = 0; c < DK; ++c)
 #pragma unroll
                         for (int n = 0; n < NQW; ++n)
 #pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                float tile_max = fmaxf(s[n][j], s[n][j + 2]);
-                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
-                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
-                                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
-                                float r_new = r_ref[n][j];
-                                if (tile_max > -INFINITY) r_new = fmaxf(r_new, ceilf(tile_max * c2));
-                                alpha[n][j] = fast_exp2(r_ref[n][j] - r_new);  // a power of two, or 0 for a first reference
-                                r_ref[n][j] = r_new;
-                                l_run[n][j] *= alpha[n][j];
-                            }
+                            for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
 #pragma unroll
-                        for (int c = 0; c < DKW; ++c)
-#pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
-#pragma unroll
-                        for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) arg[n][e] = fmaf(s[n][e], c2, -r_ref[n][e & 1]);
+                    for (int n = 0; n < NQW; ++n) {
+                        l_run[n][0] *= alpha[n][0];
+                        l_run[n][1] *= alpha[n][1];
                     }
-                    // ---- probabilities of this warp's tile as the B operand of V^T P^T, and to the partner
-                    constexpr int RW = kRemainder ? 2 : 1;
-                    uint32_t own[RW][NQW][2];
+                }
+
+                // ---- P^T as the B operand of V^T P^T: exponentials, packed 16-bit pairs (rows 2 tq, 2 tq + 1 of one
+                // token), transposed across the warp so that thread (g, tq) holds its four tokens of Q row g
+                uint32_t pb[MTK][NQW][2], pr[kRemainder ? MTK : 1][kRemainder ? NQW : 1][2];
+#pragma unroll
+                for (int mt = 0; mt < MTK; ++mt) {
 #pragma unroll
                     for (int n = 0; n < NQW; ++n) {
                         float pv[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(arg[n][e]);
+                        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
                         l_run[n][0] += pv[0] + pv[2];
                         l_run[n][1] += pv[1] + pv[3];
                         const uint32_t x0 = pack2<M>(pv[0], pv[1]), x1 = pack2<M>(pv[2], pv[3]);
-                        own[0][n][0] = movmatrix_trans(x0);
-                        own[0][n][1] = movmatrix_trans(x1);
+                        pb[mt][n][0] = movmatrix_trans(x0);
+                        pb[mt][n][1] = movmatrix_trans(x1);
                         if constexpr (kRemainder) {
                             const float2 r0 = unpack2<M>(x0), r1 = unpack2<M>(x1);
-                            own[RW - 1][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
-                            own[RW - 1][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
+                            pr[mt][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
+                            pr[mt][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
                         }
                     }
-                    uint32_t* const pair_words = reinterpret_cast<uint32_t*>(my_exchange);
-                    float* const pair_refs = my_exchange + 2 * 2 * G::kPairWords * 32;
-                    volatile uint32_t* const pair_flags = reinterpret_cast<volatile uint32_t*>(pair_refs + 2 * 2 * G::kQRows);
-                    {
-                        uint32_t* mine = pair_words + (exchange_phase * 2 + half) * (G::kPairWords * 32);
-#pragma unroll
-                        for (int w = 0; w < RW; ++w)
-#pragma unroll
-                            for (int n = 0; n < NQW; ++n) {
-                                mine[((w * NQW + n) * 2 + 0) * 32 + lane] = own[w][n][0];
-                                mine[((w * NQW + n) * 2 + 1) * 32 + lane] = own[w][n][1];
-                            }
-                        if (raised && g == 0) {
-#pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                                for (int j = 0; j < 2; ++j)
-                                    pair_refs[(exchange_phase * 2 + half) * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = r_ref[n][j];
-                        }
-                        if (lane == 0) pair_flags[exchange_phase * 2 + half] = raised ? 1u : 0u;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
+                }
 
-                    // ---- O^T += V^T P^T of one tile over this warp's output columns
-                    auto accumulate_tile = [&](uint32_t mt, const uint32_t (&pb)[RW][NQW][2]) {
-                        const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
-                        if constexpr (KVB == 1) {
+                // ---- O^T += V^T P^T over this warp's output columns
 #pragma unroll
-                            for (int k = 0; k < DKW; k += 2) {
-                                const int c = half * DKW + k;
-                                uint32_t r[4];
-                                ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
+                for (int mt = 0; mt < MTK; ++mt) {
+                    if (debug_bits(p) & 16) break;  // measurement build only: no V^T P^T
+                    const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
+                    if constexpr (KVB == 1) {
 #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    uint32_t a[4];
-                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
+                        for (int k = 0; k < DK; k += 2) {
+                            const int c = k;  // 16-byte chunk c = output columns 16 c .. + 15
+                            uint32_t r[4];
+                            ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
 #pragma unroll
-                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k + h][n], a, pb[0][n][0], pb[0][n][1]);
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < DKW; ++k) {
-                                const int c = half * DKW + k;
+                            for (int h = 0; h < 2; ++h) {
                                 uint32_t a[4];
-                                ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
+                                a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
+                                a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
+                                a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
+                                a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
 #pragma unroll
-                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[0][n][0], pb[0][n][1]);
-                            }
-                            if constexpr (kRemainder) {
-                                // the remainders in a pass of their own (V fragments loaded again): an MMA right
-                                // behind the one that wrote its accumulator would wait for it
-#pragma unroll
-                                for (int k = 0; k < DKW; ++k) {
-                                    const int c = half * DKW + k;
-                                    uint32_t a[4];
-                                    ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
-#pragma unroll
-                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[RW - 1][n][0], pb[RW - 1][n][1]);
-                                }
-                            }
-                        }
-                    };
-                    accumulate_tile(uint32_t(half), own);  // while the partner's probabilities arrive
-
-                    // ---- the partner's tile
-                    if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
-                    uint32_t other[RW][NQW][2];
-                    {
-                        const uint32_t* theirs = pair_words + (exchange_phase * 2 + (half ^ 1)) * (G::kPairWords * 32);
-#pragma unroll
-                        for (int w = 0; w < RW; ++w)
-#pragma unroll
-                            for (int n = 0; n < NQW; ++n) {
-                                other[w][n][0] = theirs[((w * NQW + n) * 2 + 0) * 32 + lane];
-                                other[w][n][1] = theirs[((w * NQW + n) * 2 + 1) * 32 + lane];
-                            }
-                    }
-                    const bool partner_raised = pair_flags[exchange_phase * 2 + (half ^ 1)] != 0u;
-                    if (raised || partner_raised) {
-                        // bring both sides to the larger reference of every row
-                        bool shrink = false;
-                        float f_me[NQW][2], f_partner[NQW][2];
-#pragma unroll
-                        for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                const float r_partner =
-                                    partner_raised ? pair_refs[(exchange_phase * 2 + (half ^ 1)) * G::kQRows + 8 * (n0 + n) + 2 * tq + j]
-                                                   : r_before[n][j];
-                                const float common = fmaxf(r_ref[n][j], r_partner);
-                                f_me[n][j] = fast_exp2(r_ref[n][j] - common);
-                                f_partner[n][j] = fast_exp2(r_partner - common);
-                                shrink = shrink || f_me[n][j] != 1.0f;
-                                r_ref[n][j] = common;
-                                l_run[n][j] *= f_me[n][j];
-                            }
-                        if (__any_sync(0xffffffffu, shrink)) {
-#pragma unroll
-                            for (int c = 0; c < DKW; ++c)
-#pragma unroll
-                                for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) o[c][n][e] *= f_me[n][e & 1];
-                        }
-                        // the received words hold Q row 8 n + g; its factor sits in the threads with tq = g / 2
-#pragma unroll
-                        for (int n = 0; n < NQW; ++n) {
-                            const float f0 = __shfl_sync(0xffffffffu, f_partner[n][0], g >> 1);
-                            const float f1 = __shfl_sync(0xffffffffu, f_partner[n][1], g >> 1);
-                            const float f = (g & 1) ? f1 : f0;
-#pragma unroll
-                            for (int w = 0; w < RW; ++w)
-#pragma unroll
-                                for (int i = 0; i < 2; ++i) {
-                                    const float2 v = unpack2<M>(other[w][n][i]);
-                                    other[w][n][i] = pack2<M>(v.x * f, v.y * f);
-                                }
-                        }
-                    }
-                    accumulate_tile(uint32_t(half ^ 1), other);
-                } else {
-                    // ---- S^T = K Q^T (raw dot products; the softmax scale is folded into the exponent below).
-                    // A dependent MMA waits for the one before it, so the contraction steps go round KS accumulator
-                    // sets: with the tiles and n-tiles of the stage that gives at least four independent chains.
-                    constexpr int KS = MTK * NQW >= 4 ? 1 : MTK * NQW >= 2 ? 2 : 4;
-                    float s_set[KS][MTK][NQW][4];
-    #pragma unroll
-                    for (int ks = 0; ks < KS; ++ks)
-    #pragma unroll
-                        for (int mt = 0; mt < MTK; ++mt)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-                                s_set[ks][mt][n][0] = s_set[ks][mt][n][1] = s_set[ks][mt][n][2] = s_set[ks][mt][n][3] = 0.0f;
-                    if (debug_bits(p) & 2) {
-                        // measurement build only: no K Q^T
-                    } else if constexpr (KVB == 1) {
-    #pragma unroll
-                        for (int k = 0; k < DKW; k += 2) {
-                            const int kk = half * DKW + k;  // 16-byte chunk kk of the row = elements 16 kk .. + 15
-    #pragma unroll
-                            for (int mt = 0; mt < MTK; ++mt) {
-                                const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
-                                uint32_t r[4];
-                                ldmatrix_x4(r, k_base + (kk >> 3) * G::kBoxBytes + (k_y4 ^ ((kk & 7) << 4)));
-    #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    uint32_t a[4];
-                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
-    #pragma unroll
-                                    for (int n = 0; n < NQW; ++n)
-                                        mma_16816<M>(s_set[(k + h) % KS][mt][n], a, qb[n][k + h][0], qb[n][k + h][1]);
-                                }
+                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k + h][n], a, pb[mt][n][0], pb[mt][n][1]);
                             }
                         }
                     } else {
-    #pragma unroll
-                        for (int k = 0; k < DKW; ++k) {
-                            const int kk = half * DKW + k;  // elements 16 kk .. + 15 = 16-byte chunks 2 kk, 2 kk + 1
-    #pragma unroll
-                            for (int mt = 0; mt < MTK; ++mt) {
-                                const uint32_t k_base = stage_base + mt * G::kCopyBytes + k_lane;
-                                uint32_t a[4];
-                                ldmatrix_x4(a, k_base + ((2 * kk) >> 3) * G::kBoxBytes + (k_y4 ^ (((2 * kk) & 7) << 4)));
-    #pragma unroll
-                                for (int n = 0; n < NQW; ++n) mma_16816<M>(s_set[k % KS][mt][n], a, qb[n][k][0], qb[n][k][1]);
-                            }
+#pragma unroll
+                        for (int k = 0; k < DK; ++k) {
+                            const int c = k;  // output columns 16 c .. + 15 = 16-byte chunks 2 c, 2 c + 1
+                            uint32_t a[4];
+                            ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
+#pragma unroll
+                            for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[mt][n][0], pb[mt][n][1]);
                         }
-                    }
-                    float (&s)[MTK][NQW][4] = s_set[0];
-    #pragma unroll
-                    for (int ks = 1; ks < KS; ++ks)
-    #pragma unroll
-                        for (int mt = 0; mt < MTK; ++mt)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) s[mt][n][e] += s_set[ks][mt][n][e];
-                    if constexpr (DS == 2) {
-                        // hand the partial scores to the partner and add the partner's (addition commutes: both warps
-                        // end with the same bits)
-                        float* mine = my_exchange + (exchange_phase * 2 + half) * (SF * 32);
-                        const float* theirs = my_exchange + (exchange_phase * 2 + (half ^ 1)) * (SF * 32);
-    #pragma unroll
-                        for (int mt = 0; mt < MTK; ++mt)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) mine[((mt * NQW + n) * 4 + e) * 32 + lane] = s[mt][n][e];
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(exchange_bar + 8 * group);
-                        if (!mbar_wait(exchange_bar + 8 * group, exchange_phase, abort_flag, p)) continue;
-    #pragma unroll
-                        for (int mt = 0; mt < MTK; ++mt)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) s[mt][n][e] += theirs[((mt * NQW + n) * 4 + e) * 32 + lane];
-                    }
-
-                    // ---- mask (only where a row's visible range cuts the stage) and running maximum
-                    bool cut = false;
-    #pragma unroll
-                    for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                        for (int j = 0; j < 2; ++j) cut = cut || tile_tok < lo[n][j] || tile_tok + ST > hi[n][j];
-                    if (__any_sync(0xffffffffu, cut)) {
-    #pragma unroll
-                        for (int mt = 0; mt < MTK; ++mt)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const uint32_t tok = tile_tok + 16 * mt + sig + kUpperRow * (e >> 1);
-                                    if (!(tok >= lo[n][e & 1] && tok < hi[n][e & 1])) s[mt][n][e] = -INFINITY;
-                                }
-                    }
-                    float alpha[NQW][2], shift[NQW][2];
-                    bool rescale = false;
-    #pragma unroll
-                    for (int n = 0; n < NQW; ++n) {
-    #pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            float tile_max = fmaxf(s[0][n][j], s[0][n][j + 2]);
-    #pragma unroll
-                            for (int mt = 1; mt < MTK; ++mt) tile_max = fmaxf(tile_max, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
-                            // the row's tokens are spread over the eight row groups of the warp
-                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
-                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
-                            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
-                            const float m_new = fmaxf(m_run[n][j], tile_max);
-                            const float base = m_new == -INFINITY ? 0.0f : m_new;
-                            alpha[n][j] = m_run[n][j] == -INFINITY ? 1.0f : fast_exp2((m_run[n][j] - base) * p.scale_log2e);
-                            shift[n][j] = -base * p.scale_log2e;
-                            m_run[n][j] = m_new;
-                            rescale = rescale || alpha[n][j] != 1.0f;
-                        }
-                    }
-                    if (__any_sync(0xffffffffu, rescale)) {
-    #pragma unroll
-                        for (int c = 0; c < DKW; ++c)
-    #pragma unroll
-                            for (int n = 0; n < NQW; ++n)
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) o[c][n][e] *= alpha[n][e & 1];
-    #pragma unroll
-                        for (int n = 0; n < NQW; ++n) {
-                            l_run[n][0] *= alpha[n][0];
-                            l_run[n][1] *= alpha[n][1];
-                        }
-                    }
-
-                    // ---- P^T as the B operand of V^T P^T: exponentials, packed 16-bit pairs (rows 2 tq, 2 tq + 1 of one
-                    // token), transposed across the warp so that thread (g, tq) holds its four tokens of Q row g
-                    uint32_t pb[MTK][NQW][2], pr[kRemainder ? MTK : 1][kRemainder ? NQW : 1][2];
-    #pragma unroll
-                    for (int mt = 0; mt < MTK; ++mt) {
-    #pragma unroll
-                        for (int n = 0; n < NQW; ++n) {
-                            float pv[4];
-    #pragma unroll
-                            for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s[mt][n][e], p.scale_log2e, shift[n][e & 1]));
-                            l_run[n][0] += pv[0] + pv[2];
-                            l_run[n][1] += pv[1] + pv[3];
-                            const uint32_t x0 = pack2<M>(pv[0], pv[1]), x1 = pack2<M>(pv[2], pv[3]);
-                            pb[mt][n][0] = movmatrix_trans(x0);
-                            pb[mt][n][1] = movmatrix_trans(x1);
-                            if constexpr (kRemainder) {
-                                const float2 r0 = unpack2<M>(x0), r1 = unpack2<M>(x1);
-                                pr[mt][n][0] = movmatrix_trans(pack2<M>(pv[0] - r0.x, pv[1] - r0.y));
-                                pr[mt][n][1] = movmatrix_trans(pack2<M>(pv[2] - r1.x, pv[3] - r1.y));
-                            }
-                        }
-                    }
-
-                    // ---- O^T += V^T P^T over this warp's output columns
-    #pragma unroll
-                    for (int mt = 0; mt < MTK; ++mt) {
-                        if (debug_bits(p) & 16) break;  // measurement build only: no V^T P^T
-                        const uint32_t v_base = stage_base + mt * G::kCopyBytes + G::kPlaneBoxBytes + v_lane;
-                        if constexpr (KVB == 1) {
-    #pragma unroll
-                            for (int k = 0; k < DKW; k += 2) {
-                                const int c = half * DKW + k;  // 16-byte chunk c = output columns 16 c .. + 15
-                                uint32_t r[4];
-                                ldmatrix_m16n16_x2_trans_b8(r, v_base + (c >> 3) * G::kBoxBytes + (v_y4 ^ ((c & 7) << 4)));
-    #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    uint32_t a[4];
-                                    a[0] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] & 0xffffu));
-                                    a[1] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] & 0xffffu));
-                                    a[2] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h] >> 16));
-                                    a[3] = cvt_e4m3x2_to_f16x2(uint16_t(r[2 * h + 1] >> 16));
-    #pragma unroll
-                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k + h][n], a, pb[mt][n][0], pb[mt][n][1]);
-                                }
-                            }
-                        } else {
-    #pragma unroll
-                            for (int k = 0; k < DKW; ++k) {
-                                const int c = half * DKW + k;  // output columns 16 c .. + 15 = 16-byte chunks 2 c, 2 c + 1
+                        if constexpr (kRemainder) {
+                            // the remainders in a pass of their own (V fragments loaded again): an MMA right
+                            // behind the one that wrote its accumulator would wait for it
+#pragma unroll
+                            for (int k = 0; k < DK; ++k) {
+                                const int c = k;
                                 uint32_t a[4];
                                 ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
-    #pragma unroll
-                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pb[mt][n][0], pb[mt][n][1]);
-                            }
-                            if constexpr (kRemainder) {
-                                // the remainders in a pass of their own (V fragments loaded again): an MMA right
-                                // behind the one that wrote its accumulator would wait for it
-    #pragma unroll
-                                for (int k = 0; k < DKW; ++k) {
-                                    const int c = half * DKW + k;
-                                    uint32_t a[4];
-                                    ldmatrix_x4_trans(a, v_base + ((2 * c) >> 3) * G::kBoxBytes + (v_y4 ^ (((2 * c) & 7) << 4)));
-    #pragma unroll
-                                    for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pr[mt][n][0], pr[mt][n][1]);
-                                }
+#pragma unroll
+                                for (int n = 0; n < NQW; ++n) mma_16816<M>(o[k][n], a, pr[mt][n][0], pr[mt][n][1]);
                             }
                         }
                     }
-
                 }
+
 
                 // ---- release the stage
                 if (tile_tok + ST > t_kv_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -900,7 +566,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             if (t_carry & 2u) {
                 // The next task of this CTA continues these rows: nothing is merged or published now. This task's
                 // template still gets a partial, an empty one (weight zero in every merge).
-                if (group == 0 && half == 0 && g == 0) {
+                if (group == 0 && g == 0) {
 #pragma unroll
                     for (int n = 0; n < NQW; ++n) {
 #pragma unroll
@@ -935,53 +601,35 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     l_row[n][j] = l;
                 }
             }
-            // The statistics every merge below works on: the running maximum as a raw dot product, or (token split)
-            // the reference in the log2 domain; a row without any visible token carries -inf.
-            constexpr bool kLog2Stats = TS;
-            float m_pub[NQW][2];
-#pragma unroll
-            for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) m_pub[n][j] = (TS && m_run[n][j] <= 0.5f * kNoReference) ? -INFINITY : m_run[n][j];
             bool merge_ok = true;
             if (merges > 0) merge_ok = mbar_wait(merged_bar, (merges - 1) & 1, abort_flag, p);  // parked states are free
             auto weight_of = [&](float m, float base) {
-                return m == -INFINITY ? 0.0f : fast_exp2((m - base) * (kLog2Stats ? 1.0f : p.scale_log2e));
+                return m == -INFINITY ? 0.0f : fast_exp2((m - base) * p.scale_log2e);
             };
             if (merge_ok) {
                 if (merge_round == 0) {
 #pragma unroll
-                    for (int c = 0; c < DKW; ++c)
+                    for (int c = 0; c < DK; ++c)
 #pragma unroll
                         for (int n = 0; n < NQW; ++n)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                my_park[(8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1)] = o[c][n][e];
+                                my_park[(8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * c + g + 8 * (e >> 1)] = o[c][n][e];
                             }
                 }
-                if (g == 0 && half == 0) {
+                if (g == 0) {
 #pragma unroll
                     for (int n = 0; n < NQW; ++n)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            my_stats[8 * (n0 + n) + 2 * tq + j] = m_pub[n][j];
+                            my_stats[8 * (n0 + n) + 2 * tq + j] = m_run[n][j];
                             my_stats[G::kQRows + 8 * (n0 + n) + 2 * tq + j] = l_row[n][j];
                             if (G::kTwoRounds && merge_round == 0 && group + NSLOT >= NG) {
                                 // no second-round group folds into this slot: its second statistics are empty
                                 my_stats[2 * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = -INFINITY;
                                 my_stats[3 * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = 0.0f;
-                                if constexpr (TS) my_sums_b[G::kQRows + 8 * (n0 + n) + 2 * tq + j] = 0.0f;
                             }
                         }
-                }
-                if constexpr (TS) {
-                    // the second warp of a pair summed the probabilities of its own tokens
-                    if (g == 0 && half == 1) {
-#pragma unroll
-                        for (int n = 0; n < NQW; ++n)
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) my_sums_b[merge_round * G::kQRows + 8 * (n0 + n) + 2 * tq + j] = l_row[n][j];
-                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(parked_bar);
@@ -999,18 +647,18 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 #pragma unroll
                             for (int j = 0; j < 2; ++j) {
                                 const float m_first = first[8 * (n0 + n) + 2 * tq + j];
-                                const float m_new = fmaxf(m_first, m_pub[n][j]);
+                                const float m_new = fmaxf(m_first, m_run[n][j]);
                                 const float base = m_new == -INFINITY ? 0.0f : m_new;
                                 w_slot[n][j] = weight_of(m_first, base);
-                                w_mine[n][j] = weight_of(m_pub[n][j], base);
+                                w_mine[n][j] = weight_of(m_run[n][j], base);
                             }
 #pragma unroll
-                        for (int c = 0; c < DKW; ++c)
+                        for (int c = 0; c < DK; ++c)
 #pragma unroll
                             for (int n = 0; n < NQW; ++n)
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    float* at = my_park + (8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * (half * DKW + c) + g + 8 * (e >> 1);
+                                    float* at = my_park + (8 * (n0 + n) + 2 * tq + (e & 1)) * RS + 16 * c + g + 8 * (e >> 1);
                                     *at = *at * w_slot[n][e & 1] + o[c][n][e] * w_mine[n][e & 1];
                                 }
                     }
@@ -1035,14 +683,12 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         const float* stats = merge + w * G::kParkFloats + G::kQRows * RS;
                         m_slot[w] = stats[row];
                         l_slot[w] = stats[G::kQRows + row];
-                        if constexpr (TS) l_slot[w] += stats[4 * G::kQRows + row];
                         if constexpr (G::kTwoRounds) {
                             const float m_second = stats[2 * G::kQRows + row];
                             const float m_new = fmaxf(m_slot[w], m_second);
                             const float base = m_new == -INFINITY ? 0.0f : m_new;
-                            float l_second = stats[3 * G::kQRows + row];
-                            if constexpr (TS) l_second += stats[5 * G::kQRows + row];
-                            l_slot[w] = l_slot[w] * weight_of(m_slot[w], base) + l_second * weight_of(m_second, base);
+                            l_slot[w] = l_slot[w] * weight_of(m_slot[w], base) +
+                                        stats[3 * G::kQRows + row] * weight_of(m_second, base);
                             m_slot[w] = m_new;
                         }
                         m_max = fmaxf(m_max, m_slot[w]);
@@ -1074,10 +720,8 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         *reinterpret_cast<float4*>(p.partial_out + index * D + d) = acc;
                         if (d == 0) {
                             p.partial_sum[index] = l_sum;
-                            // the statistic is a raw dot product or a log2-domain reference; publish the
-                            // natural-log-domain logit
-                            p.partial_max[index] = l_sum > 0.0f ? m_max * ((kLog2Stats ? 1.0f : p.scale_log2e) * 0.6931471805599453f)
-                                                                : -INFINITY;
+                            // the running maximum is a raw dot product; publish the natural-log-domain logit
+                            p.partial_max[index] = l_sum > 0.0f ? m_max * (p.scale_log2e * 0.6931471805599453f) : -INFINITY;
                         }
                     }
                 }
