@@ -261,6 +261,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         float* const my_park = merge + (group % NSLOT) * G::kParkFloats;
         float* const my_stats = my_park + G::kQRows * RS + merge_round * 2 * G::kQRows;
 
+        uint32_t qb[NQW][DK][2] = {};  // the task's Q rows as the B operand of K Q^T
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
             if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
@@ -311,10 +312,11 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             // ---- Q as the B operand of K Q^T for this warp's contraction steps. One-byte pages: under K's head-dim
             // permutation, thread (g, tq) holds elements 16 kk + 4 tq .. + 3 of Q row 8 n + g as two f16 pairs.
             // 16-bit pages: the natural fragment, elements 16 kk + 2 tq, + 1 and 16 kk + 8 + 2 tq, + 1.
+            // A task that continues the previous task's running state has the same Q rows: the fragments stay.
             const uint32_t q_tile = smem_addr(q_ring + tslot * G::kQBytes);
-            uint32_t qb[NQW][DK][2];
 #pragma unroll
             for (int n = 0; n < NQW; ++n) {
+                if (t_carry & 1u) break;
                 const uint32_t row = 8 * (n0 + n) + g;
 #pragma unroll
                 for (int kk = 0; kk < DK; ++kk) {
