@@ -64,12 +64,24 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_map_kernel launch over its algorithmic K/V bytes, from
+# dram__bytes_read.sum + dram__bytes_write.sum of one map-kernel launch over its algorithmic K/V bytes, from
 # profiler captures of the decode workload at a reduced batch (315.70 MB moved for 309.67 MB of 16-bit pages;
-# 308.63 MB for 301.35 MB of FP8 pages); traffic grows with the tokens processed, so the ratio carries to the
+# 307.75 MB for 301.35 MB of FP8 pages); traffic grows with the tokens processed, so the ratio carries to the
 # full batch.
 MAP_TRAFFIC_PER_KV_BYTE = 315.70 / 309.67
-MAP_TRAFFIC_PER_FP8_KV_BYTE = 308.63 / 301.35
+MAP_TRAFFIC_PER_FP8_KV_BYTE = 307.75 / 301.35
+
+
+def map_kernel_name(spec):
+    """Which kernel the library picks for the workload's map tasks (rows per task = Q tokens x heads per group):
+    the token-major kernel for FP8 pages and for 17-32-row tasks, the row-major warp-level kernel otherwise."""
+    rows = spec.get("q_len", 1) * (spec["hq"] // spec["hkv"])
+    widest = 32 if spec["d"] == 128 else 24
+    if spec.get("kv_elem", 2) == 1 and rows <= widest:
+        return "sdpa_tm_kernel"
+    if 16 < rows <= widest:
+        return "sdpa_tm_kernel"
+    return "sdpa_map_kernel"
 
 
 def traffic_estimate(spec, kv_bytes):
@@ -480,7 +492,7 @@ def run_ours(args):
             "hbm_frac": round(value / world / peak, 4),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": traffic_estimate(spec, kv_bytes), "peak_source": f"of {peak_kind}",
-                         "kernel": "sdpa_map_kernel", "kernel_ms": round(map_ms_mean, 5)},
+                         "kernel": map_kernel_name(spec), "kernel_ms": round(map_ms_mean, 5)},
             "e2e": {"value": round(total_kv_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 5),
                     "tokens_per_s": round(total_tokens / (e2e_ms * 1e-3), 1),

@@ -630,6 +630,7 @@ struct ProducerContext {
     uint32_t task_base, task_step, task_limit;
     bool balanced;             // the CTA owns one contiguous run of tasks
     bool allow_carry;          // consumers can continue a running state across tasks
+    bool cell_major;           // round-robin dealing walks the tasks cell by cell (all templates of a KV head first)
     ActiveCounts active;
     int lane;
 };
@@ -663,7 +664,13 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     const uint32_t run_r0 = by_cell ? task_base / cells : 0, run_c0 = by_cell ? task_base % cells : 0;
     const uint32_t run_r1 = by_cell ? (task_limit - 1) / cells : 0, run_c1 = by_cell ? (task_limit - 1) % cells + 1 : 0;
     auto visit_to_task = [&](uint64_t visit) -> uint64_t {
-        if (!by_cell) return task_base + visit * task_step;
+        if (!by_cell) {
+            const uint64_t dealt = task_base + visit * task_step;
+            if (!c.cell_major || dealt >= task_limit || c.active.templates == 0) return dealt;
+            // the dealt index counts cell-major: the CTAs of the grid then work on the same KV head's rows at the
+            // same time (task ids stay template-major)
+            return (dealt % c.active.templates) * cells + dealt / c.active.templates;
+        }
         if (visit >= task_limit - task_base) return task_limit;
         uint32_t before = 0;
         for (uint32_t c = 0; c < cells; ++c) {

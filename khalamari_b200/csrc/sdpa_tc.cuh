@@ -221,11 +221,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     // pulls from HBM are L2 hits for the others. A chunked-prefill batch streams every sequence's K/V once per Q tile
     // (tens of GB per step through L2); contiguous runs spread the CTAs over all sequences at once and the working
     // set (hundreds of MB) no longer fits the 126 MB L2. There are tens of tasks per CTA, so the deal balances.
+    // The deal walks the tasks KV head by KV head (cell-major): at any moment the grid reads one or two K/V streams.
     const bool balanced = false;
     (void)task_range;
 
     ProducerContext producer{};
     producer.ring = ring;
+    producer.cell_major = true;
     producer.q_ring = q_ring;
     producer.pid_smem = pid_smem;
     producer.task_ring = task_ring;
