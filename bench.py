@@ -100,11 +100,23 @@ def attention_flops(spec, contexts):
     return 4.0 * spec["hq"] * spec["d"] * pairs
 
 
-def contexts_for(spec, rank):
+def contexts_for(spec, rank, world=1):
+    """Context lengths of the requests rank ``rank`` of ``world`` owns. One GPU: the workload's batch. Several: the
+    job's requests (``batch`` per GPU, every GPU's share drawn with its own seed) are binned over the ranks
+    longest-first by context length (`split_kv.assign_requests`), so that every rank streams about the same bytes;
+    no rank needs another rank's data, there is no collective on the data path."""
     if "contexts" in spec:
         return list(spec["contexts"])
-    rng = np.random.default_rng(spec["seed"] + 1000 * rank)
-    return rng.integers(spec["lo"], spec["hi"] + 1, size=spec["batch"]).tolist()
+
+    def draw(r):
+        rng = np.random.default_rng(spec["seed"] + 1000 * r)
+        return rng.integers(spec["lo"], spec["hi"] + 1, size=spec["batch"]).tolist()
+
+    if world <= 1:
+        return draw(rank)
+    from khalamari_b200.split_kv import assign_requests
+    job = [ctx for r in range(world) for ctx in draw(r)]
+    return [job[i] for i in assign_requests(job, world)[rank]]
 
 
 def workload_config(spec, contexts, world):
@@ -355,7 +367,7 @@ def run_ours(args):
         spec["kv_elem"] = 1
         spec["label"] += " [K/V pages of FP8 E4M3FN]"
     kv_elem = spec.get("kv_elem", 2)
-    contexts = contexts_for(spec, rank)
+    contexts = contexts_for(spec, rank, world)
     q_len = spec["q_len"]
     q_lens = [q_len] * len(contexts)
     device = Device(local)
@@ -923,7 +935,7 @@ def run_reference(args):
     if rank != 0:
         return None
     spec = dict(WORKLOADS[args.workload])
-    contexts = contexts_for(spec, 0)
+    contexts = contexts_for(spec, 0, int(os.environ.get("WORLD_SIZE", "1")))
     threads = host_threads()
     warmup = max(args.warmup, 0)
     sample = bounded_sample(spec, contexts, threads, args.steps + warmup)

@@ -64,7 +64,7 @@ struct TmGeometry {
     static constexpr int kColumnHalves = D / 64;                      // Q tile: 64-element column halves (16-bit)
     static constexpr int kQRows = NQ * 8;
     static constexpr int kQBytes = kQRows * D * 2;
-    static constexpr int kTaskSlots = 2;
+    static constexpr int kTaskSlots = 2;  // (four slots measured the same on the FP8 decode bench)
     static constexpr int kConsumerWarps = CW;
     static constexpr int kGroups = CW / NR;                           // warp groups; a stage goes to one group
     static constexpr int kThreads = (CW + 2) * 32;                    // + stream warp + task warp
@@ -262,6 +262,16 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         float* const my_stats = my_park + G::kQRows * RS + merge_round * 2 * G::kQRows;
 
         uint32_t qb[NQW][DK][2] = {};  // the task's Q rows as the B operand of K Q^T
+        // Q rows 8 n + 2 tq + j of a task (this thread's score columns): which Q token and which head of the task
+        uint32_t row_tok_of[NQW][2], row_head_of[NQW][2];
+#pragma unroll
+        for (int n = 0; n < NQW; ++n)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t row = 8 * (n0 + n) + 2 * tq + j;
+                row_tok_of[n][j] = row / p.heads_per_task;
+                row_head_of[n][j] = row % p.heads_per_task;
+            }
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
             if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
@@ -280,9 +290,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             for (int n = 0; n < NQW; ++n) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const uint32_t row = 8 * (n0 + n) + 2 * tq + j;
-                    const uint32_t row_tok = row / p.heads_per_task;
-                    const uint32_t row_head = row % p.heads_per_task;
+                    const uint32_t row_tok = row_tok_of[n][j], row_head = row_head_of[n][j];
                     lo[n][j] = 0;
                     hi[n][j] = 0xffffffffu;  // rows that hold nothing are never published: left unmasked
                     if (row_tok < t_num_toks && row_head < t_num_heads) {
@@ -573,9 +581,7 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     for (int n = 0; n < NQW; ++n) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const uint32_t row = 8 * (n0 + n) + 2 * tq + j;
-                            const uint32_t row_tok = row / p.heads_per_task;
-                            const uint32_t row_head = row % p.heads_per_task;
+                            const uint32_t row_tok = row_tok_of[n][j], row_head = row_head_of[n][j];
                             if (!(row_tok < t_num_toks && row_head < t_num_heads)) continue;
                             const uint64_t index =
                                 (uint64_t(t_tmpl) * p.num_q_heads + t_head_begin + row_head) * p.max_q_tokens + row_tok;

@@ -36,3 +36,17 @@ def test_other_ranks_of_the_reference_arm_exit_quietly():
                           "--warmup", "0"], capture_output=True, text=True, timeout=120, cwd=ROOT,
                          env={**os.environ, **env})
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_several_gpus_share_the_job_by_longest_first_binning():
+    """At N GPUs the bench bins the job's requests (64 per GPU) over the ranks with ``split_kv.assign_requests``:
+    every request lands on exactly one rank and the ranks' byte loads differ by less than one request."""
+    import bench
+    spec = bench.WORKLOADS["c2"]
+    for world in (2, 4, 8):
+        shares = [bench.contexts_for(spec, rank, world) for rank in range(world)]
+        job = sorted(ctx for rank in range(world) for ctx in bench.contexts_for(spec, rank))
+        assert sorted(ctx for share in shares for ctx in share) == job
+        loads = [sum(share) for share in shares]
+        assert max(loads) - min(loads) <= spec["hi"]
+    assert bench.contexts_for(spec, 0, 1) == bench.contexts_for(spec, 0)
