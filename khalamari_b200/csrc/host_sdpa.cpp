@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cstring>
 #include <memory>
+#include <cstdlib>
 #include <queue>
 #include <tuple>
 
@@ -427,7 +428,13 @@ Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* request
     // measured: decode (one Q token per task) runs best with about 4 tasks per SM (2,048-token slices on the decode
     // bench and on 1M tokens); Q-tile tasks, fewer and costlier, balance better with about 8
     constexpr uint32_t kTasksPerSm = 8;
-    constexpr uint32_t kDecodeTasksPerSm = 4;
+    uint32_t kDecodeTasksPerSm = 4;
+    uint32_t min_slice = 256;
+#ifdef KH_GQA_MEASURE
+    // measurement build only: try other decode slice policies without rebuilding
+    if (const char* v = std::getenv("KH_GQA_DECODE_TASKS_PER_SM")) kDecodeTasksPerSm = uint32_t(std::atoi(v));
+    if (const char* v = std::getenv("KH_GQA_MIN_SLICE")) min_slice = uint32_t(std::atoi(v));
+#endif
     uint32_t max_q = 0, end = 0;
     unsigned __int128 visible = 0;
     for (uint32_t r = 0; r < num_requests; ++r) {
@@ -466,7 +473,7 @@ Route lookup_route_b200(const kh_sdpa_config& c, const kh_request_shape* request
             // one task per tile writes the output directly, no partials and no reduce (chunked prefill)
             slice = end;
         } else {
-            slice = decode_slice(end, work * head_groups, 256, 2048,
+            slice = decode_slice(end, work * head_groups, min_slice, 2048,
                                  (unsigned __int128)sm_count * (sliced_q ? kTasksPerSm : kDecodeTasksPerSm));
             // A small batch cut at 256 tokens leaves most SMs without a task (four short decode requests with two
             // KV heads: 32 tasks on 148 SMs, and the batch sits in L2, so the step is pure latency). When the tasks

@@ -217,8 +217,9 @@ class HostPipeline:
 
     A step is what a host-side caller issues per batch: copy Q from page-locked host memory, plan the batch
     (selector + metadata, on the host, while the copy runs), run map + reduce over the resident KV pages, copy
-    the output back. ``submit`` enqueues one step and returns without waiting; the output copy of a step runs on a
-    second stream while the kernels of the next step run on the first (``ReplaySubmission`` handles in the
+    the output back. ``submit`` enqueues one step and returns without waiting; the Q copy of a step and the output
+    copy of the step before run on two copy streams while kernels run on the compute stream (``ReplaySubmission``
+    handles in the
     reference, metal/stream/submission.rs:41-101: a caller may hold several submissions and wait for each). Two
     slots of device Q / output buffers and batch metadata alternate; ``submit`` first waits for the step that used
     the slot two submissions ago, so at most two steps are in flight. ``wait(ticket)`` blocks until that step's
@@ -231,7 +232,8 @@ class HostPipeline:
 
         self.attention = attention
         self.compute = compute_stream
-        self.copy = Stream(attention.device)
+        self.copy = Stream(attention.device)      # device -> host: outputs
+        self.copy_in = Stream(attention.device)   # host -> device: Q rows of the next step, beside this step's kernels
         core = attention.core
         limits = attention.limits
         row = core.num_q_heads * core.head_dim * attention.io_dtype.item_size()
@@ -242,6 +244,7 @@ class HostPipeline:
         self.metadata = [attention.metadata] + [
             GQAMetadataBuffers(attention.device, limits.max_tokens, limits.max_map_task_templates)
             for _ in range(self.SLOTS - 1)]
+        self.q_ready = [Event(attention.device) for _ in range(self.SLOTS)]
         self.kernels_done = [Event(attention.device) for _ in range(self.SLOTS)]
         self.copied = [Event(attention.device) for _ in range(self.SLOTS)]
         self.in_flight = [False] * self.SLOTS
@@ -259,7 +262,8 @@ class HostPipeline:
             self.copied[slot].synchronize()  # the slot's buffers and its metadata host block are free again
         num_tokens = int(cu_tokens[-1])
         nbytes = num_tokens * self.row_bytes
-        self.compute.write(self.q[slot], 0, q_host.ptr, nbytes)  # runs while the host plans the batch
+        self.copy_in.write(self.q[slot], 0, q_host.ptr, nbytes)  # runs while the host plans the batch
+        self.copy_in.record_event(self.q_ready[slot])
         attention.metadata = self.metadata[slot]
         selection = None
         if partition:
@@ -267,6 +271,7 @@ class HostPipeline:
                            if v.kind == 0 and v.thread_block.max_q_tokens == 1)
             selection = attention.select_partitioned(variant, partition, False, token_indices, cu_tokens, num_tokens)
         attention.prepare(req_slots, token_indices, cu_tokens, num_tokens, self.compute, selection)
+        self.compute.wait_event(self.q_ready[slot])
         launches = attention.record_sdpa(self.compute, self.q[slot], kv_pages, page_ids, self.out[slot],
                                          gqa_layer_index)
         self.compute.record_event(self.kernels_done[slot])
