@@ -55,6 +55,12 @@ pub struct KhEvent {
     _private: [u8; 0],
 }
 
+/// Opaque handle (`kh_peer_exchange`).
+#[repr(C)]
+pub struct KhPeerExchange {
+    _private: [u8; 0],
+}
+
 /// Opaque handle (`kh_selector`).
 #[repr(C)]
 pub struct KhSelector {
@@ -784,6 +790,31 @@ unsafe extern "C" {
         num_rows: u32,
         head_dim: u32,
         packed: KhBufferRef,
+        out_dtype: u32,
+        output: KhBufferRef,
+    ) -> KhStatus;
+    // ---- cross-GPU combine in one kernel over NVLink peer memory (no counterpart in the reference)
+    pub fn kh_peer_exchange_inbox_bytes(world: u32, num_rows: u32, head_dim: u32, out: *mut u64) -> KhStatus;
+    pub fn kh_ipc_export(device: *mut KhDevice, buffer: KhBufferRef, handle64: *mut u8) -> KhStatus;
+    pub fn kh_ipc_import(device: *mut KhDevice, handle64: *const u8, out: *mut *mut core::ffi::c_void) -> KhStatus;
+    pub fn kh_ipc_close(device: *mut KhDevice, ptr: *mut core::ffi::c_void) -> KhStatus;
+    pub fn kh_peer_exchange_create(
+        device: *mut KhDevice,
+        rank: u32,
+        world: u32,
+        num_rows: u32,
+        head_dim: u32,
+        inboxes: *const *mut core::ffi::c_void,
+        out: *mut *mut KhPeerExchange,
+    ) -> KhStatus;
+    pub fn kh_peer_exchange_destroy(exchange: *mut KhPeerExchange) -> KhStatus;
+    pub fn kh_peer_exchange_combine(
+        exchange: *mut KhPeerExchange,
+        stream: *mut KhStream,
+        num_partials: u32,
+        exp_sums: KhBufferRef,
+        max_logits: KhBufferRef,
+        partial_output: KhBufferRef,
         out_dtype: u32,
         output: KhBufferRef,
     ) -> KhStatus;
