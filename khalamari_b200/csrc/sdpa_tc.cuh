@@ -2,12 +2,19 @@
 // cores: tcgen05.mma with the accumulators in tensor memory. Same task ABI, rings, task warp and stream warp as
 // sdpa_map_kernel (sdpa_map.cuh); only the consumers differ.
 //
-//   S = Q K^T   tcgen05.mma kind::f16, M = 128 rows, N = 32 KV tokens, K = 16 head-dim elements per instruction.
+//   S = Q K^T   tcgen05.mma kind::f16, M = 128 rows, N = 48 KV tokens, K = 16 head-dim elements per instruction.
 //               A = the Q tile in tensor memory (copied there once per task). B = K rows in shared memory, K-major
 //               with the 128-byte swizzle exactly as the TMA copies leave them; one instruction takes row group g
-//               (8 token rows) of each of the stage's four pages, the only uniform stride 16-token pages offer.
-//   P           eight softmax warps in two groups that take alternate stages, one thread per row: tcgen05.ld brings
-//               the thread its row's 64 scores, so the row maximum and sum need no shuffles. P goes back to
+//               (8 token rows) of each of the stage's six pages, the only uniform stride 16-token pages offer.
+//               A stage (96 tokens) is therefore worked on as two half-stages of 48 scores: row groups 0 and 1.
+//               Stage size is a trade: an instruction costs about the same tensor-pipe cycles for N = 32, 48 and
+//               64, so more pages per stage mean fewer cycles per token, but the ring must hold three stages for
+//               the copies of a stage to start early enough, and three 8-page stages do not fit beside the Q
+//               tiles. (Measured on the prefill workload: 4 pages x 4 slots 22.3 ms; 8 pages x 2 slots 22.4 ms,
+//               16.9 ms without copies; boxes smaller than a whole page - 4 KB or 2 KB copies, which would allow
+//               other layouts - 26 ms.)
+//   P           eight softmax warps in two groups, one per half-stage (row group), one thread per row: tcgen05.ld
+//               brings the thread its row's 48 scores, so the row maximum and sum need no shuffles. P goes back to
 //               tensor memory as packed 16-bit pairs of the Q/output type (A and B operands of one MMA must share
 //               their type); bf16 probabilities are followed by their rounding remainder, as in the warp-level kernel.
 //   O += P V    A = P from tensor memory, B = the V rows in shared memory, MN-major (V is stored
@@ -27,7 +34,10 @@ namespace kh {
 template <int D, int P>
 struct TcGeometry {
     static_assert(D == 128 && P == 16, "the tensor-memory instance is built for head_dim 128 and 16-token pages");
-    static constexpr int kStageTokens = 64;  // four pages: Q K^T runs with N = 32 (row group g of every page)
+    static constexpr int kPagesPerStage = 6;
+    static constexpr int kStageTokens = 16 * kPagesPerStage;  // Q K^T runs with N = 8 x pages (row group g of every page)
+    static constexpr int kScoreTokens = 8 * kPagesPerStage;   // scores of a half-stage: one row group of all pages
+    static_assert(kScoreTokens % 16 == 0 && kScoreTokens <= 64, "a half-stage is a whole number of 16-token chunks");
     static constexpr int kBoxRows = 16;
     static constexpr int kBoxesPerPlane = kStageTokens / kBoxRows;
     static constexpr int kColumnHalves = D / 64;
@@ -93,7 +103,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
         : "r"(taddr));
 }
 
-// Results of tmem_ld32 may be used only after this.
+__device__ __forceinline__ void tmem_ld16(uint32_t (&r)[16], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+// Results of a tensor-memory load may be used only after this.
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -115,6 +133,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <typename T>
@@ -129,6 +153,7 @@ __global__ void __launch_bounds__(TcGeometry<D, P>::kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map, const MapParams p) {
     using G = TcGeometry<D, P>;
     constexpr int ST = G::kStageTokens;
+    constexpr int SC = G::kScoreTokens;
     constexpr int NS = G::kStages;
     constexpr int TQ = G::kTaskSlots;
     constexpr int NSW = G::kSoftmaxWarps;
@@ -207,10 +232,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     tmem_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base;
-    // Column c of a stage's scores is KV token tile_tok + 16 * page + 8 * g + r with g = c / 32, page = (c % 32) / 8,
-    // r = c % 8: one Q K^T instruction covers row group g (8 token rows) of all four pages, whose 8-row groups lie
-    // one page copy apart in shared memory (a uniform stride, which is what the operand descriptor can express).
-    const uint32_t tmem_s = tmem_base + 128;  // + 64 * buffer + 32 * g
+    // A stage is worked on as two half-stages: half-stage gr holds row group gr (token rows 8 gr .. 8 gr + 7) of
+    // each of the stage's pages, whose 8-row groups lie one page copy apart in shared memory (a uniform stride,
+    // which is what the operand descriptor can express). Column c of half-stage gr's scores is KV token
+    // tile_tok + 16 * (c / 8) + 8 * gr + c % 8. Half-stage gr uses score buffer gr, probability buffer gr and
+    // softmax group gr; with G the running stage number its barrier phases have parity G & 1, and the running
+    // half-stage number is 2 G + gr.
+    const uint32_t tmem_s = tmem_base + 128;  // + 64 * buffer
     const uint32_t tmem_p = tmem_base + 256;  // + 64 * buffer (+ 32 for the remainder) + 8 * (16-token chunk)
     const uint32_t tmem_q = tmem_base + 384;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
 
@@ -261,8 +289,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         // goes through the softmax warps' barriers, so no ordering between the two instruction streams is assumed.
         if (lane == 0) {
             constexpr uint32_t kFormat = umma_format<T>();
-            // D f32; A, B 16-bit; M = 128, N = 32, both operands K-major
-            const uint32_t idesc_qk = (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+            // D f32; A, B 16-bit; M = 128, N = 8 x pages, both operands K-major
+            const uint32_t idesc_qk =
+                (1u << 4) | (kFormat << 7) | (kFormat << 10) | ((uint32_t(SC) >> 3) << 17) | ((128u >> 4) << 24);
             // descriptor of a K operand at byte address 0 (stride between 8-row groups: one page copy); shared
             // memory addresses are below 2^18, so the 14-bit address field is a plain sum
             const uint64_t k_desc0 = umma_smem_desc(0, 16, G::kCopyBytes);
@@ -277,24 +306,24 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const uint32_t num_tiles = ts->num_tiles;
                 if (!mbar_wait(q_ready_bar + 8 * tslot, (taken / TQ) & 1, abort_flag, p)) break;
                 const uint32_t q_tmem = tmem_q + 64 * tslot;
-                for (uint32_t i = 0; i < num_tiles; ++i) {
+                for (uint32_t i = 0; i < num_tiles && ok; ++i) {
                     const uint32_t g = stage_base + i;
-                    const uint32_t slot = g % NS, sb = g & 1;
+                    const uint32_t slot = g % NS;
                     if (!mbar_wait(full_bar + 8 * slot, (g / NS) & 1, abort_flag, p)) { ok = false; break; }
-                    if (!mbar_wait(s_free_bar + 8 * sb, ((g >> 1) & 1) ^ 1, abort_flag, p)) { ok = false; break; }
-                    tmem_fence_after();
                     const uint64_t k_desc = k_desc0 + uint64_t((ring_addr + slot * G::kStageBytes) >> 4);
 #pragma unroll
                     for (int gr = 0; gr < 2; ++gr) {
+                        if (!mbar_wait(s_free_bar + 8 * gr, (g & 1) ^ 1, abort_flag, p)) { ok = false; break; }
+                        tmem_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < D / 16; ++kk) {
                             // A = the Q tile in tensor memory (read once per task from shared memory, not once per
-                            // instruction). B = K rows 8 * gr .. 8 * gr + 7 of the stage's four pages.
+                            // instruction). B = K rows 8 * gr .. 8 * gr + 7 of the stage's pages.
                             const uint64_t k = k_desc + uint64_t(((kk / 4) * G::kBoxBytes + gr * 1024 + (kk % 4) * 32) >> 4);
-                            umma_ts(tmem_s + 64 * sb + 32 * gr, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
+                            umma_ts(tmem_s + 64 * gr, q_tmem + 8 * kk, k, idesc_qk, kk > 0 ? 1u : 0u);
                         }
+                        umma_commit(s_full_bar + 8 * gr);
                     }
-                    umma_commit(s_full_bar + 8 * sb);
                 }
                 stage_base += num_tiles;
                 if (ok) mbar_arrive(task_empty_bar + 8 * tslot);  // done with the task's descriptor
@@ -324,28 +353,32 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const TaskSlot* ts = task_ring + tslot;
                 if (ts->done) break;
                 const uint32_t num_tiles = ts->num_tiles;
-                for (uint32_t i = 0; i < num_tiles; ++i) {
+                for (uint32_t i = 0; i < num_tiles && ok; ++i) {
                     const uint32_t g = stage_base + i;
-                    const uint32_t slot = g % NS, pb = g & 1;
-                    if (!mbar_wait(p_full_bar + 8 * pb, (g >> 1) & 1, abort_flag, p)) { ok = false; break; }
-                    if (i == 0 && pv_tasks > 0) {
-                        // this task's first product overwrites O: the previous task's epilogue must have read it
-                        if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p)) { ok = false; break; }
-                    }
-                    tmem_fence_after();
+                    const uint32_t slot = g % NS;
                     const uint64_t v_desc = v_desc0 + uint64_t((ring_addr + slot * G::kStageBytes + G::kPlaneBoxBytes) >> 4);
 #pragma unroll
-                    for (int j = 0; j < ST / 16; ++j) {
-                        // 16-token chunk j of the score columns: row group j / 2 of pages 2 * (j % 2) and + 1
-                        const uint64_t v = v_desc + uint64_t(((2 * (j % 2)) * G::kCopyBytes + (j / 2) * 1024) >> 4);
-                        umma_ts(tmem_o, tmem_p + 64 * pb + 8 * j, v, idesc_pv, (i == 0 && j == 0) ? 0u : 1u);
-                        // bf16 probabilities (8 significant bits) are followed by their rounding remainder; f16
-                        // probabilities (11 bits) need none
-                        if (kRemainder && !(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * pb + 32 + 8 * j, v, idesc_pv, 1u);
+                    for (int gr = 0; gr < 2; ++gr) {
+                        if (!mbar_wait(p_full_bar + 8 * gr, g & 1, abort_flag, p)) { ok = false; break; }
+                        if (i == 0 && gr == 0 && pv_tasks > 0) {
+                            // this task's first product overwrites O: the previous task's epilogue must have read it
+                            if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p)) { ok = false; break; }
+                        }
+                        tmem_fence_after();
+#pragma unroll
+                        for (int j = 0; j < SC / 16; ++j) {
+                            // 16-token chunk j of the half-stage's score columns: row group gr of pages 2 j and 2 j + 1
+                            const uint64_t v = v_desc + uint64_t(((2 * j) * G::kCopyBytes + gr * 1024) >> 4);
+                            umma_ts(tmem_o, tmem_p + 64 * gr + 8 * j, v, idesc_pv, (i == 0 && gr == 0 && j == 0) ? 0u : 1u);
+                            // bf16 probabilities (8 significant bits) are followed by their rounding remainder; f16
+                            // probabilities (11 bits) need none
+                            if (kRemainder && !(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * gr + 32 + 8 * j, v, idesc_pv, 1u);
+                        }
+                        // K and V of the stage are consumed once its second half-stage's products completed (its
+                        // Q K^T products completed before the probabilities could be computed)
+                        if (gr == 1) umma_commit(empty_bar + 8 * slot);
+                        umma_commit(pv_done_bar + 8 * gr);
                     }
-                    umma_commit(empty_bar + 8 * slot);  // K and V of the stage are consumed (its Q K^T completed
-                                                        // before the probabilities could be computed)
-                    umma_commit(pv_done_bar + 8 * pb);
                 }
                 if (num_tiles > 0) ++pv_tasks;
                 stage_base += num_tiles;
@@ -361,8 +394,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // ------------------------------ softmax and epilogue warps -----------------------------
         // Two groups of four warps; both cover the tile's 128 rows (a warp reaches the tensor-memory lanes of
-        // quadrant warp % 4) and take alternate stages: group w handles the stages whose running number has
-        // parity w, with score buffer w and probability buffer w. Per row, the maximum the probabilities are
+        // quadrant warp % 4) and take one half-stage of every stage each: group w handles row group w of the
+        // stage's pages (running half-stage number 2 G + w), with score buffer w and probability buffer w. Per row, the maximum the probabilities are
         // relative to lives in shared memory; the decision about it (cheap: tile maximum, compare, the rare
         // rescale of O) is made stage after stage in order - a group waits for the other group's decision on
         // the previous stage - while the expensive part (exponentials, rounding, stores) of consecutive stages
@@ -419,16 +452,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             float l_run = 0.0f;
             bool failed = false;
             for (uint32_t i = 0; i < t_num_tiles; ++i) {
-                const uint32_t g = stage_base + i;
-                if ((g & 1) != wg) continue;
+                const uint32_t g = 2 * (stage_base + i) + wg;  // running half-stage number
                 const uint32_t sb = wg;
+                const bool first = i == 0 && wg == 0;          // the task's first half-stage
                 if (!mbar_wait(s_full_bar + 8 * sb, (g >> 1) & 1, abort_flag, p)) { failed = true; break; }
                 tmem_fence_after();
                 // the row's 64 scores, kept as bit patterns in one register array (register pressure decides the
                 // speed of this loop: twelve warps leave 170 registers per thread)
-                uint32_t sraw[ST];
-                tmem_ld32(*reinterpret_cast<uint32_t(*)[32]>(&sraw[0]), tmem_s + 64 * sb + lane_base);
-                tmem_ld32(*reinterpret_cast<uint32_t(*)[32]>(&sraw[32]), tmem_s + 64 * sb + 32 + lane_base);
+                uint32_t sraw[SC];
+#pragma unroll
+                for (int c0 = 0; c0 < SC; c0 += 16) {
+                    tmem_ld16(*reinterpret_cast<uint32_t(*)[16]>(&sraw[c0]), tmem_s + 64 * sb + c0 + lane_base);
+                }
                 tmem_ld_wait();
                 tmem_fence_before();
                 __syncwarp();
@@ -439,18 +474,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 const bool cut = tile_tok < lo || tile_tok + ST > hi;
                 if (__any_sync(0xffffffffu, cut)) {
 #pragma unroll
-                    for (int j = 0; j < ST; ++j) {
-                        const uint32_t tok = tile_tok + ((j % 32) / 8) * 16 + (j / 32) * 8 + (j % 8);
+                    for (int j = 0; j < SC; ++j) {
+                        const uint32_t tok = tile_tok + (j / 8) * 16 + wg * 8 + (j % 8);
                         if (!(tok >= lo && tok < hi)) sraw[j] = 0xff800000u;  // -inf
                         tile_max = fmaxf(tile_max, __uint_as_float(sraw[j]));
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < ST; ++j) tile_max = fmaxf(tile_max, __uint_as_float(sraw[j]));
+                    for (int j = 0; j < SC; ++j) tile_max = fmaxf(tile_max, __uint_as_float(sraw[j]));
                 }
                 // ---- the decision about the row maximum, in stage order
                 float m_prev = -INFINITY;
-                if (i > 0) {
+                if (!first) {
                     const uint32_t gp = g - 1;  // handled by the other group
                     if (!mbar_wait(decided_bar + 8 * (wg ^ 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                     m_prev = row_max[row];
@@ -469,8 +504,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         l_run *= alpha;
                         m_ref = tile_max;
                     }
-                    if (i > 0) {
-                        // O holds this task's earlier stages: wait for the previous stage's products, then scale
+                    if (!first) {
+                        // O holds this task's earlier half-stages: wait for the previous one's products, then scale
                         const uint32_t gp = g - 1;
                         if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                         tmem_fence_after();
@@ -499,11 +534,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 }
                 tmem_fence_after();
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t packed_hi[16], packed_lo[kRemainder ? 16 : 1];  // rounded pairs and their rounding remainders
+                for (int chunk = 0; chunk < SC / 16; ++chunk) {
+                    uint32_t packed_hi[8], packed_lo[kRemainder ? 8 : 1];  // rounded pairs and their rounding remainders
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int c = 32 * half + 2 * j;
+                    for (int j = 0; j < 8; ++j) {
+                        const int c = 16 * chunk + 2 * j;
                         const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c]), p.scale_log2e, shift));
                         const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c + 1]), p.scale_log2e, shift));
                         l_run += p0 + p1;
@@ -513,18 +548,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                             packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
                         }
                     }
-                    tmem_st16(tmem_p + 64 * sb + 16 * half + lane_base, packed_hi);
-                    if constexpr (kRemainder) tmem_st16(tmem_p + 64 * sb + 32 + 16 * half + lane_base, packed_lo);
+                    tmem_st8(tmem_p + 64 * sb + 8 * chunk + lane_base, packed_hi);
+                    if constexpr (kRemainder) tmem_st8(tmem_p + 64 * sb + 32 + 8 * chunk + lane_base, packed_lo);
                 }
                 tmem_st_wait();
                 if (tile_tok + ST > t_kv_end) {
                     // V rows of tokens at or past kv_end may never have been loaded: clear them so that a zero
                     // probability times stale bits cannot produce NaN (generic-proxy writes, then a proxy fence
                     // before the tensor core reads them)
+                    // Each group clears the rows of its own row group: the rows its half-stage's products read.
                     const uint32_t first_bad = t_kv_end > tile_tok ? t_kv_end - tile_tok : 0;
-                    uint8_t* stage = ring + (g % NS) * G::kStageBytes;
-                    for (uint32_t idx = first_bad * (D / 8) + row; idx < uint32_t(ST) * (D / 8); idx += 128) {
-                        const uint32_t r = idx / (D / 8);
+                    uint8_t* stage = ring + ((g >> 1) % NS) * G::kStageBytes;
+                    for (uint32_t idx = row; idx < uint32_t(SC) * (D / 8); idx += 128) {
+                        const uint32_t own = idx / (D / 8);                        // row of this half-stage
+                        const uint32_t r = (own / 8) * 16 + wg * 8 + own % 8;      // token row of the stage
+                        if (r < first_bad) continue;
                         const uint32_t c = idx % (D / 8);
                         uint8_t* dst = stage + (r / G::kBoxRows) * G::kCopyBytes + G::kPlaneBoxBytes + (c / 8) * G::kBoxBytes +
                                        (r % G::kBoxRows) * 128 + (c % 8) * 16;
@@ -556,7 +594,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
             const uint32_t head = t_head_begin + row_head;
             const uint64_t index = (uint64_t(t_tmpl) * p.num_q_heads + head) * p.max_q_tokens + row_tok;
             if (t_num_tiles > 0) {
-                const uint32_t gl = stage_base - 1;
+                const uint32_t gl = 2 * (stage_base - 1) + 1;  // the task's last half-stage
                 if (!mbar_wait(pv_done_bar + 8 * (gl & 1), (gl >> 1) & 1, abort_flag, p)) break;
                 tmem_fence_after();
 #pragma unroll
