@@ -174,6 +174,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     uint32_t* tmem_slot = task_range + 2;
     volatile float* row_max = reinterpret_cast<volatile float*>(tmem_slot + 1);  // [128] maximum per row of the tile
     volatile float* row_sum = row_max + 128;                                     // [2][128] each group's row sum
+    // [2][4] per probability buffer and softmax warp: the half-stage's rounding remainders matter (see below)
+    volatile uint32_t* remainder_flag = reinterpret_cast<volatile uint32_t*>(row_sum + 256);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -365,6 +367,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                             if (!mbar_wait(o_free_bar, (pv_tasks - 1) & 1, abort_flag, p)) { ok = false; break; }
                         }
                         tmem_fence_after();
+                        // the softmax warps say whether this half-stage's rounding remainders carry weight
+                        const bool with_remainder =
+                            kRemainder && !(debug_bits(p) & 1024) &&
+                            (remainder_flag[4 * gr] | remainder_flag[4 * gr + 1] | remainder_flag[4 * gr + 2] |
+                             remainder_flag[4 * gr + 3]) != 0u;
 #pragma unroll
                         for (int j = 0; j < SC / 16; ++j) {
                             // 16-token chunk j of the half-stage's score columns: row group gr of pages 2 j and 2 j + 1
@@ -372,7 +379,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                             umma_ts(tmem_o, tmem_p + 64 * gr + 8 * j, v, idesc_pv, (i == 0 && gr == 0 && j == 0) ? 0u : 1u);
                             // bf16 probabilities (8 significant bits) are followed by their rounding remainder; f16
                             // probabilities (11 bits) need none
-                            if (kRemainder && !(debug_bits(p) & 1024)) umma_ts(tmem_o, tmem_p + 64 * gr + 32 + 8 * j, v, idesc_pv, 1u);
+                            if (kRemainder && with_remainder) umma_ts(tmem_o, tmem_p + 64 * gr + 32 + 8 * j, v, idesc_pv, 1u);
                         }
                         // K and V of the stage are consumed once its second half-stage's products completed (its
                         // Q K^T products completed before the probabilities could be computed)
@@ -405,6 +412,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
         const uint32_t row = quad * 32 + lane;           // row of the 128-row tile this thread owns
         const uint32_t lane_base = (quad * 32) << 16;    // this warp's quarter of the tensor-memory lanes
         uint32_t stage_base = 0;
+        bool remainder_zeroed = false;  // this warp's remainder columns of its probability buffer hold zeros
         for (uint32_t popped = 0;; ++popped) {
             const uint32_t tslot = popped % TQ;
             if (!mbar_wait(task_full_bar + 8 * tslot, (popped / TQ) & 1, abort_flag, p)) break;
@@ -533,6 +541,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                     if (!mbar_wait(pv_done_bar + 8 * (gp & 1), (gp >> 1) & 1, abort_flag, p)) { failed = true; break; }
                 }
                 tmem_fence_after();
+                // The rounding remainder of a bf16 probability is 2^-9 of it at most. Once a row's sum (so far, of
+                // this group's half-stages: a lower bound of the final normaliser) is 128 times the largest
+                // probability of this half-stage, what the remainders of the half-stage add to the output is below
+                // 2^-9 / sqrt(128) of a V element: the second product is skipped, for all 128 rows or none (the PV
+                // thread reads the four warps' flags). Rows with few or dominant tokens keep it.
+                bool remainder = false;
+                if constexpr (kRemainder) {
+                    const float p_max = tile_max == -INFINITY ? 0.0f : fast_exp2(fmaf(tile_max, p.scale_log2e, shift));
+                    remainder = __any_sync(0xffffffffu, valid && p_max * 128.0f > l_run);
+                    if (lane == 0) remainder_flag[4 * sb + quad] = remainder ? 1u : 0u;
+                }
 #pragma unroll
                 for (int chunk = 0; chunk < SC / 16; ++chunk) {
                     uint32_t packed_hi[8], packed_lo[kRemainder ? 8 : 1];  // rounded pairs and their rounding remainders
@@ -544,13 +563,22 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                         l_run += p0 + p1;
                         packed_hi[j] = pack2<T>(p0, p1);
                         if constexpr (kRemainder) {
-                            const float2 r = unpack2<T>(packed_hi[j]);
-                            packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
+                            if (remainder) {
+                                const float2 r = unpack2<T>(packed_hi[j]);
+                                packed_lo[j] = pack2<T>(p0 - r.x, p1 - r.y);
+                            } else {
+                                packed_lo[j] = 0u;
+                            }
                         }
                     }
                     tmem_st8(tmem_p + 64 * sb + 8 * chunk + lane_base, packed_hi);
-                    if constexpr (kRemainder) tmem_st8(tmem_p + 64 * sb + 32 + 8 * chunk + lane_base, packed_lo);
+                    if constexpr (kRemainder) {
+                        // another warp of the group may still ask for the second product: this warp's remainder
+                        // columns then have to hold zeros, which they keep until it stores remainders again
+                        if (remainder || !remainder_zeroed) tmem_st8(tmem_p + 64 * sb + 32 + 8 * chunk + lane_base, packed_lo);
+                    }
                 }
+                if constexpr (kRemainder) remainder_zeroed = !remainder;
                 tmem_st_wait();
                 if (tile_tok + ST > t_kv_end) {
                     // V rows of tokens at or past kv_end may never have been loaded: clear them so that a zero
