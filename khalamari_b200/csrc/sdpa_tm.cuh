@@ -358,8 +358,11 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 // stage's copy while the previous stage's copy is still in flight would return at once. So first
                 // wait until the previous stage of the slot has been RELEASED (its phase of the empty barrier: that
                 // phase cannot be followed by another one before this warp itself releases the slot), which
-                // implies that its copy has landed; then wait for this stage's copy.
-                if (my_stage >= uint32_t(NS) && !mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p)) continue;
+                // implies that its copy has landed; then wait for this stage's copy. (A ring whose depth is a multiple
+                // of the group count hands a slot to the same group every time: no first wait.)
+                if constexpr (NS % NG != 0) {
+                    if (my_stage >= uint32_t(NS) && !mbar_wait(empty_bar + 8 * slot, phase ^ 1, abort_flag, p)) continue;
+                }
                 if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, p)) continue;
                 if (debug_bits(p) & 1) {
                     __syncwarp();
