@@ -567,55 +567,70 @@ __device__ __forceinline__ TaskInfo shfl_task(const TaskInfo& t, int lane) {
     return r;
 }
 
-// Which tasks a CTA runs. Tasks are numbered template-major. With few enough templates every CTA scans them all
-// (12 bytes each) and takes one CONTIGUOUS run of tasks whose cost - KV tokens plus a fixed per-task term - is its
-// 1/gridDim share of the total: task k belongs to the CTA c with
+// Which tasks a CTA runs. Tasks are numbered template-major. With few enough templates the CTA's task warp scans
+// them all (12 bytes each) and takes one CONTIGUOUS run of tasks whose cost - KV tokens plus a fixed per-task term -
+// is its 1/gridDim share of the total: task k belongs to the CTA c with
 // c * W / grid <= cost of tasks [0, k) < (c + 1) * W / grid. No CTA carries more than its share plus one task,
 // where dealing tasks round-robin leaves the CTAs that drew the long slices several percent behind. Contiguous
-// tasks are also neighbours in the page table. Returns false above the template limit (tasks are then dealt
-// round-robin). Called by every thread of the CTA; `scan` is shared scratch of `threads` u64 that nothing else
-// uses until the call returns, `task_range` two shared words that receive [begin, end).
-__device__ __forceinline__ bool balanced_task_range(const MapParams& p, uint32_t num_templates, uint64_t* scan,
-                                                    uint32_t* task_range, uint32_t threads) {
-    if (num_templates > kBalanceMaxTemplates) return false;
+// tasks are also neighbours in the page table. Above kBalanceMaxTemplates tasks are dealt round-robin.
+// Called by the 32 lanes of the task warp only (a block-wide scan with two block barriers cost every launch about
+// 5 us before the first copy could be issued); `scratch` is shared memory for one u32 per template that nothing
+// else touches until the call returns (the K/V ring: no copy is issued before the first task is published);
+// returns [begin, end) in every lane.
+__device__ __forceinline__ void balanced_task_range_warp(const MapParams& p, uint32_t num_templates, int lane,
+                                                         uint32_t* scratch, uint32_t& begin, uint32_t& end) {
     const uint32_t cells = p.num_kv_heads * p.head_ranges;
-    const uint32_t chunk = (num_templates + threads - 1) / threads;
-    const uint32_t first = min(threadIdx.x * chunk, num_templates);
-    const uint32_t last = min(first + chunk, num_templates);
-    auto cost_of = [&](uint32_t t) -> uint64_t {
+    const uint64_t total_tasks = uint64_t(num_templates) * cells;
+    if (total_tasks <= gridDim.x) {
+        // at most one task per CTA (a small batch: the launch is latency, not bandwidth): nothing to balance and no
+        // reason to read the templates here
+        begin = blockIdx.x;
+        end = static_cast<uint32_t>(min(uint64_t(blockIdx.x) + 1, total_tasks));
+        return;
+    }
+    // every template's cost into shared memory, read from global memory once, coalesced and with many loads in flight
+    for (uint32_t t = lane; t < num_templates; t += 32) {
+        const uint32_t q_range = p.templates[t * 3];
         const uint32_t kv_begin = p.templates[t * 3 + 1];
         const uint32_t kv_end = p.templates[t * 3 + 2];
-        if (p.templates[t * 3] == 0xffffffffu || kv_end <= kv_begin) return 1;
-        return uint64_t(kv_end - kv_begin) + kTaskOverheadTokens;
-    };
+        scratch[t] = (q_range == 0xffffffffu || kv_end <= kv_begin) ? 1u : kv_end - kv_begin + kTaskOverheadTokens;
+    }
+    __syncwarp();
+    // lane l owns the contiguous chunk [first, last) of the templates
+    const uint32_t chunk = (num_templates + 31) / 32;
+    const uint32_t first = min(uint32_t(lane) * chunk, num_templates);
+    const uint32_t last = min(first + chunk, num_templates);
     uint64_t local = 0;
-    for (uint32_t t = first; t < last; ++t) local += cost_of(t);
-    scan[threadIdx.x] = local;
-    if (threadIdx.x == 0) {
-        task_range[0] = 0;
-        task_range[1] = 0;
+    for (uint32_t t = first; t < last; ++t) local += scratch[t];
+    uint64_t inclusive = local;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint64_t v = __shfl_up_sync(0xffffffffu, inclusive, d);
+        if (lane >= d) inclusive += v;
     }
-    __syncthreads();
-    uint64_t before = 0, total = 0;
-    for (uint32_t i = 0; i < threads; ++i) {
-        const uint64_t v = scan[i];
-        if (i < threadIdx.x) before += v;
-        total += v;
-    }
+    const uint64_t total = __shfl_sync(0xffffffffu, inclusive, 31);
     const uint64_t whole = total * cells;
     const uint64_t lo = whole / gridDim.x * blockIdx.x + whole % gridDim.x * blockIdx.x / gridDim.x;
     const uint64_t hi = whole / gridDim.x * (blockIdx.x + 1) + whole % gridDim.x * (blockIdx.x + 1) / gridDim.x;
-    // first task whose preceding cost reaches x: inside the template whose cost interval (S, E] holds x
-    uint64_t start = before * cells;
+    // first task whose preceding cost reaches x: inside the template whose cost interval (S, E] holds x; one lane
+    // at most finds each bound (none for a bound of 0: task 0)
+    uint32_t found_begin = 0, found_end = 0;
+    uint64_t start = (inclusive - local) * cells;
     for (uint32_t t = first; t < last; ++t) {
-        const uint64_t c = cost_of(t);
-        const uint64_t end = start + c * cells;
-        if (lo > start && lo <= end) task_range[0] = t * cells + uint32_t((lo - start + c - 1) / c);
-        if (hi > start && hi <= end) task_range[1] = t * cells + uint32_t((hi - start + c - 1) / c);
-        start = end;
+        const uint64_t c = scratch[t];
+        const uint64_t stop = start + c * cells;
+        if (lo > start && lo <= stop) found_begin = t * cells + uint32_t((lo - start + c - 1) / c);
+        if (hi > start && hi <= stop) found_end = t * cells + uint32_t((hi - start + c - 1) / c);
+        start = stop;
     }
-    __syncthreads();  // the scan scratch is read for the last time before this barrier
-    return true;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        found_begin = max(found_begin, __shfl_xor_sync(0xffffffffu, found_begin, d));
+        found_end = max(found_end, __shfl_xor_sync(0xffffffffu, found_end, d));
+    }
+    __syncwarp();  // the scratch is read for the last time before this
+    begin = found_begin;
+    end = found_end;
 }
 
 // What the producer-side warps of a kernel instance need: where the rings and barriers live, and which tasks this
@@ -650,8 +665,12 @@ __device__ __forceinline__ void run_task_warp(const MapParams& p, const CUtensor
     TaskSlot* const task_ring = c.task_ring;
     const uint32_t task_full_bar = c.task_full_bar, task_empty_bar = c.task_empty_bar, stream_full_bar = c.stream_full_bar;
     volatile uint32_t* const abort_flag = c.abort_flag;
-    const uint32_t task_base = c.task_base, task_step = c.task_step, task_limit = c.task_limit;
+    uint32_t task_base = c.task_base, task_limit = c.task_limit;
+    const uint32_t task_step = c.task_step;
     const bool balanced = c.balanced;
+    if (balanced) {
+        balanced_task_range_warp(p, c.active.templates, c.lane, reinterpret_cast<uint32_t*>(c.ring), task_base, task_limit);
+    }
     const int lane = c.lane;
     uint32_t pushed = 0;  // task-ring pushes so far
 
@@ -1176,12 +1195,13 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
 
-    uint32_t* task_range = const_cast<uint32_t*>(last_flag) + 1;  // [begin, end) of this CTA's run
-    const bool balanced =
-        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
-    const uint32_t task_base = balanced ? task_range[0] : blockIdx.x;
+    // one contiguous, cost-balanced run of tasks per CTA (the task warp works out which), or a round-robin deal
+    // (the scan keeps one word per template in the ring of K/V stages, before the first copy is issued)
+    constexpr uint32_t kScanTemplates = KVB == 1 ? uint32_t(G::kRawStages) * G::kRawStageBytes / 4 : uint32_t(NS) * G::kStageBytes / 4;
+    const bool balanced = active.templates <= kBalanceMaxTemplates && active.templates <= kScanTemplates;
+    const uint32_t task_base = blockIdx.x;
     const uint32_t task_step = balanced ? 1u : gridDim.x;
-    const uint32_t task_limit = balanced ? task_range[1] : total_tasks;
+    const uint32_t task_limit = total_tasks;
 
     ProducerContext producer{};
     producer.ring = ring;

@@ -170,8 +170,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
     constexpr int kNumBars = 2 * NS + 3 * TQ + 17;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
-    uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 1;
-    uint32_t* tmem_slot = task_range + 2;
+    uint32_t* tmem_slot = const_cast<uint32_t*>(abort_flag) + 3;
     volatile float* row_max = reinterpret_cast<volatile float*>(tmem_slot + 1);  // [128] maximum per row of the tile
     volatile float* row_sum = row_max + 128;                                     // [2][128] each group's row sum
     // [2][4] per probability buffer and softmax warp: the half-stage's rounding remainders matter (see below)
@@ -253,7 +252,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     // set (hundreds of MB) no longer fits the 126 MB L2. There are tens of tasks per CTA, so the deal balances.
     // The deal walks the tasks KV head by KV head (cell-major): at any moment the grid reads one or two K/V streams.
     const bool balanced = false;
-    (void)task_range;
 
     ProducerContext producer{};
     producer.ring = ring;
@@ -267,9 +265,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     producer.task_empty_bar = task_empty_bar;
     producer.stream_full_bar = stream_full_bar;
     producer.abort_flag = abort_flag;
-    producer.task_base = balanced ? task_range[0] : blockIdx.x;
-    producer.task_step = balanced ? 1u : gridDim.x;
-    producer.task_limit = balanced ? task_range[1] : total_tasks;
+    producer.task_base = blockIdx.x;
+    producer.task_step = gridDim.x;
+    producer.task_limit = total_tasks;
     producer.balanced = balanced;
     producer.allow_carry = false;  // the running state lives in tensor memory and is published per task
     producer.active = active;

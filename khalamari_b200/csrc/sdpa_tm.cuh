@@ -152,7 +152,6 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(task_ring) + G::kTaskBytes);
     constexpr int kNumBars = 2 * NS + 3 * TQ + 3;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + kNumBars);
-    uint32_t* task_range = const_cast<uint32_t*>(abort_flag) + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -190,8 +189,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
 
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
-    const bool balanced =
-        balanced_task_range(p, active.templates, reinterpret_cast<uint64_t*>(ring), task_range, G::kThreads);
+    // one contiguous, cost-balanced run of tasks per CTA (the task warp works out which), or a round-robin deal
+    // (the scan keeps one word per template in the ring of K/V stages, before the first copy is issued)
+    const bool balanced = active.templates <= kBalanceMaxTemplates && active.templates <= uint32_t(NS) * G::kStageBytes / 4;
 
     ProducerContext producer{};
     producer.ring = ring;
@@ -204,9 +204,9 @@ sdpa_tm_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     producer.task_empty_bar = task_empty_bar;
     producer.stream_full_bar = stream_full_bar;
     producer.abort_flag = abort_flag;
-    producer.task_base = balanced ? task_range[0] : blockIdx.x;
+    producer.task_base = blockIdx.x;
     producer.task_step = balanced ? 1u : gridDim.x;
-    producer.task_limit = balanced ? task_range[1] : total_tasks;
+    producer.task_limit = total_tasks;
     producer.balanced = balanced;
     producer.allow_carry = true;
     producer.active = active;
