@@ -263,14 +263,16 @@ class HostPipeline:
         num_tokens = int(cu_tokens[-1])
         nbytes = num_tokens * self.row_bytes
         self.copy_in.write(self.q[slot], 0, q_host.ptr, nbytes)  # runs while the host plans the batch
-        self.copy_in.record_event(self.q_ready[slot])
         attention.metadata = self.metadata[slot]
         selection = None
         if partition:
             variant = next(v for v in attention.selector.variants()
                            if v.kind == 0 and v.thread_block.max_q_tokens == 1)
             selection = attention.select_partitioned(variant, partition, False, token_indices, cu_tokens, num_tokens)
-        attention.prepare(req_slots, token_indices, cu_tokens, num_tokens, self.compute, selection)
+        # the metadata block follows the Q rows on the copy stream: the compute stream carries kernels only, so the
+        # kernels of consecutive steps run back to back
+        attention.prepare(req_slots, token_indices, cu_tokens, num_tokens, self.copy_in, selection)
+        self.copy_in.record_event(self.q_ready[slot])
         self.compute.wait_event(self.q_ready[slot])
         launches = attention.record_sdpa(self.compute, self.q[slot], kv_pages, page_ids, self.out[slot],
                                          gqa_layer_index)
