@@ -540,14 +540,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
                 }
                 tmem_fence_after();
                 // The rounding remainder of a bf16 probability is 2^-9 of it at most. Once a row's sum (so far, of
-                // this group's half-stages: a lower bound of the final normaliser) is 128 times the largest
+                // this group's half-stages: a lower bound of the final normaliser) is 64 times the largest
                 // probability of this half-stage, what the remainders of the half-stage add to the output is below
-                // 2^-9 / sqrt(128) of a V element: the second product is skipped, for all 128 rows or none (the PV
+                // 2^-9 / 8 of a V element: the second product is skipped, for all 128 rows or none (the PV
                 // thread reads the four warps' flags). Rows with few or dominant tokens keep it.
                 bool remainder = false;
                 if constexpr (kRemainder) {
                     const float p_max = tile_max == -INFINITY ? 0.0f : fast_exp2(fmaf(tile_max, p.scale_log2e, shift));
-                    remainder = __any_sync(0xffffffffu, valid && p_max * 128.0f > l_run);
+                    remainder = __any_sync(0xffffffffu, valid && p_max * 64.0f > l_run);
                     if (lane == 0) remainder_flag[4 * sb + quad] = remainder ? 1u : 0u;
                 }
 #pragma unroll
