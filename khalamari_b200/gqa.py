@@ -249,6 +249,7 @@ class HostPipeline:
         self.copied = [Event(attention.device) for _ in range(self.SLOTS)]
         self.in_flight = [False] * self.SLOTS
         self.submitted = 0
+        self._decode_variant = None
 
     def submit(self, q_host: PinnedArray, out_host: PinnedArray, kv_pages: Buffer, page_ids: Buffer, req_slots,
                token_indices, cu_tokens, gqa_layer_index: int = 0, partition: int | None = None):
@@ -266,9 +267,11 @@ class HostPipeline:
         attention.metadata = self.metadata[slot]
         selection = None
         if partition:
-            variant = next(v for v in attention.selector.variants()
-                           if v.kind == 0 and v.thread_block.max_q_tokens == 1)
-            selection = attention.select_partitioned(variant, partition, False, token_indices, cu_tokens, num_tokens)
+            if self._decode_variant is None:  # (the registry does not change: looked up once)
+                self._decode_variant = next(v for v in attention.selector.variants()
+                                            if v.kind == 0 and v.thread_block.max_q_tokens == 1)
+            selection = attention.select_partitioned(self._decode_variant, partition, False, token_indices, cu_tokens,
+                                                     num_tokens)
         # the metadata block follows the Q rows on the copy stream: the compute stream carries kernels only, so the
         # kernels of consecutive steps run back to back
         attention.prepare(req_slots, token_indices, cu_tokens, num_tokens, self.copy_in, selection)
