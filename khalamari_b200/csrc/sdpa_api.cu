@@ -78,6 +78,9 @@ template <typename T>
 __global__ void __launch_bounds__(kReduceMaxThreads) sdpa_reduce_kernel(const ReduceParams p) {
     __shared__ float4 shared_acc[kReduceMaxThreads];
     __shared__ float2 shared_stat[kReduceMaxThreads];
+    // Launched with programmatic stream serialization: the blocks may be scheduled while the kernel before (the map)
+    // is still running; everything that kernel wrote is visible after this wait, nothing is read before it.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t range = blockIdx.x;  // ranges on x: no 65,535 limit
     uint32_t num_active_ranges = p.num_active_ranges, num_active_tokens = p.num_active_tokens;
     if (p.active != nullptr) {
@@ -468,7 +471,19 @@ static void launch_reduce_typed(const ReduceParams& p, uint32_t num_ranges, cuda
         params.heads_per_block = 128 / slots;
         grid.y = (p.num_q_heads + params.heads_per_block - 1) / params.heads_per_block;
     }
-    sdpa_reduce_kernel<T><<<grid, threads, 0, stream>>>(params);
+    // programmatic dependent launch: the launch itself overlaps the tail of the map kernel that precedes it in the
+    // stream (the kernel waits for that kernel's completion before it reads anything)
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = dim3(threads, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    KH_CUDA(cudaLaunchKernelEx(&config, sdpa_reduce_kernel<T>, params));
 }
 
 static void launch_reduce(kh_dtype dtype, const ReduceParams& p, uint32_t num_ranges, cudaStream_t stream) {

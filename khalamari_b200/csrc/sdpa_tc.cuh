@@ -243,6 +243,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t tmem_p = tmem_base + 256;  // + 64 * buffer (+ 32 for the remainder) + 8 * (16-token chunk)
     const uint32_t tmem_q = tmem_base + 384;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
 
+    // a kernel launched behind this one with programmatic stream serialization (the reducer) may be scheduled as
+    // this kernel's blocks retire; it waits for this kernel's completion itself
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
     // Tasks are dealt round-robin (task i to CTA i mod grid), not in contiguous runs: the CTAs then work on
