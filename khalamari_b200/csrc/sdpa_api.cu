@@ -480,7 +480,8 @@ static void launch_reduce_typed(const ReduceParams& p, uint32_t num_ranges, cuda
     config.stream = stream;
     cudaLaunchAttribute attribute{};
     attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute.val.programmaticStreamSerializationAllowed = 1;
+    // (not for the merges of a fixed partial list - the cross-slice and cross-GPU combines: measured slower there)
+    attribute.val.programmaticStreamSerializationAllowed = p.cu != nullptr ? 1 : 0;
     config.attrs = &attribute;
     config.numAttrs = 1;
     KH_CUDA(cudaLaunchKernelEx(&config, sdpa_reduce_kernel<T>, params));

@@ -1192,9 +1192,13 @@ sdpa_map_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constan
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
-    // a kernel launched behind this one with programmatic stream serialization (the reducer) may be scheduled as
-    // this kernel's blocks retire; it waits for this kernel's completion itself
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A kernel launched behind this one with programmatic stream serialization (the reducer) may be scheduled as
+    // this kernel's blocks retire; it waits for this kernel's completion itself. Only where this block's shared
+    // memory leaves no room for a reducer block (12 KB) beside it: reducer blocks that became resident next to a
+    // still-running map block cost the one-sequence workload 8 us per step.
+    if constexpr (G::kSmemBytes + 14 * 1024 > 228 * 1024) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
 

@@ -243,9 +243,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant
     const uint32_t tmem_p = tmem_base + 256;  // + 64 * buffer (+ 32 for the remainder) + 8 * (16-token chunk)
     const uint32_t tmem_q = tmem_base + 384;  // + 64 * task slot: the Q tile, 16-bit pairs, 8 columns per k-step
 
-    // a kernel launched behind this one with programmatic stream serialization (the reducer) may be scheduled as
-    // this kernel's blocks retire; it waits for this kernel's completion itself
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A kernel launched behind this one with programmatic stream serialization (the reducer) may be scheduled as
+    // this kernel's blocks retire; it waits for this kernel's completion itself. Only where this block's shared
+    // memory leaves no room for a reducer block (12 KB) beside it: reducer blocks that became resident next to a
+    // still-running map block cost the one-sequence workload 8 us per step.
+    if constexpr (G::kSmemBytes + 14 * 1024 > 228 * 1024) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const ActiveCounts active = resolve_active(p);
     const uint32_t total_tasks = active.templates * p.num_kv_heads * p.head_ranges;
     // Tasks are dealt round-robin (task i to CTA i mod grid), not in contiguous runs: the CTAs then work on
