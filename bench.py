@@ -363,6 +363,9 @@ def run_ours(args):
     if args.uniform_context:
         spec["contexts"] = [args.uniform_context] * spec["batch"]
         spec["label"] += f" [uniform context {args.uniform_context}]"
+    if args.q_len:
+        spec["q_len"] = args.q_len
+        spec["label"] += f" [q_len {args.q_len}]"
     if args.kv_dtype == "fp8":
         spec["kv_elem"] = 1
         spec["label"] += " [K/V pages of FP8 E4M3FN]"
@@ -995,6 +998,8 @@ def main():
     parser.add_argument("--fused", action="store_true",
                         help="map and reduce in one launch (last-arriver merge) instead of the reference's two")
     parser.add_argument("--uniform-context", type=int, default=0, help="give every request this context length")
+    parser.add_argument("--q-len", type=int, default=0,
+                        help="new tokens per request (workload c3: 2 or 4 verify tokens; default: the workload's)")
     parser.add_argument("--kv-dtype", default="io", choices=["io", "fp8"],
                         help="element type of the K/V pages: the Q/output type (default) or FP8 E4M3FN")
     parser.add_argument("--context", type=int, default=0, help="workload c4: tokens of the one sequence")
